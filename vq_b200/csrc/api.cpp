@@ -1,0 +1,787 @@
+// api.cpp -- the extern "C" surface declared in include/vqb.h.
+//
+// Validation follows the reference's order and wording (src/pq.rs:87-102,147-156; src/opq.rs:99-114;
+// src/rvq.rs:96-98; src/sq.rs:51-68; src/bq.rs:47-54; src/exceptions.rs).  Host pointers are staged
+// through device buffers; device pointers are used in place.
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/vqb.h"
+#include "cuda_device.hpp"
+
+namespace vqb {
+void nccl_unique_id(uint8_t *out128);
+Comm *make_nccl_comm(CudaDevice &dev, const uint8_t *id_bytes, int rank, int world);
+} // namespace vqb
+
+using namespace vqb;
+
+struct vqb_ctx {
+    std::unique_ptr<CudaDevice> dev;
+    std::unique_ptr<Comm> comm;
+    std::mutex mu;
+    std::string err;
+};
+
+struct vqb_pq {
+    vqb_ctx *ctx;
+    size_t m, k, sd;
+    int metric;
+    double p;
+    float *codebooks; // device
+    std::vector<size_t> iters;
+};
+
+struct vqb_rvq {
+    vqb_ctx *ctx;
+    size_t stages, k, dim;
+    float epsilon;
+    int metric;
+    double p;
+    float *codebooks; // device, stages x k x dim
+};
+
+struct vqb_opq {
+    vqb_ctx *ctx;
+    size_t m, k, sd, dim;
+    int metric;
+    double p;
+    bool empty; // opq_iters == 0: identity rotation, no codebooks (src/opq.rs:119-124,197-204)
+    std::vector<float> rotation; // host copy, dim x dim row-major
+    float *rotation_d;
+    float *codebooks;
+};
+
+namespace {
+
+thread_local std::string g_err;
+
+int set_err(vqb_ctx *ctx, int code, const std::string &msg)
+{
+    if (ctx) ctx->err = msg;
+    g_err = msg;
+    return code;
+}
+
+template <typename F> int guarded(vqb_ctx *ctx, F &&f)
+{
+    try {
+        if (ctx) ctx->dev->make_current();
+        f();
+        return VQB_OK;
+    } catch (const Error &e) {
+        return set_err(ctx, e.code, e.what());
+    } catch (const std::bad_alloc &) {
+        return set_err(ctx, VQB_ERR_CUDA, "out of host memory");
+    } catch (const std::exception &e) {
+        return set_err(ctx, VQB_ERR_BAD_ARGUMENT, e.what());
+    } catch (...) {
+        return set_err(ctx, VQB_ERR_BAD_ARGUMENT, "unknown error");
+    }
+}
+
+bool metric_ok(int m) { return m >= 0 && m <= 6; }
+
+// A read-only input that lives on the device for the duration of a call.
+struct In {
+    CudaDevice &dev;
+    const void *d = nullptr;
+    void *owned = nullptr;
+    In(CudaDevice &dv, const void *p, size_t bytes) : dev(dv)
+    {
+        if (bytes == 0 || dev.is_device_pointer(p)) {
+            d = p;
+        } else {
+            owned = dev.alloc(bytes);
+            VQB_CUDA_CHECK(cudaMemcpyAsync(owned, p, bytes, cudaMemcpyHostToDevice, dev.stream()));
+            d = owned;
+        }
+    }
+    ~In() { dev.release(owned); }
+    template <typename T> const T *as() const { return static_cast<const T *>(d); }
+};
+
+// An output that is produced on the device and, when the caller's pointer is host memory, copied back.
+struct Out {
+    CudaDevice &dev;
+    void *d = nullptr;
+    void *host = nullptr;
+    size_t bytes = 0;
+    Out(CudaDevice &dv, void *p, size_t b) : dev(dv), bytes(b)
+    {
+        if (!p) return;
+        if (b == 0 || dev.is_device_pointer(p)) {
+            d = p;
+        } else {
+            host = p;
+            d = dev.alloc(b);
+        }
+    }
+    void finish()
+    {
+        if (host) {
+            dev.download(host, d, bytes);
+            dev.release(d);
+            host = nullptr;
+            d = nullptr;
+        }
+    }
+    ~Out()
+    {
+        if (host) dev.release(d);
+    }
+    template <typename T> T *as() const { return static_cast<T *>(d); }
+};
+
+void check_minkowski(int metric, double p)
+{
+    if (metric == VQB_MINKOWSKI && p <= 0.0) // src/distances.rs:155-163
+        throw Error(VQB_ERR_INVALID_METRIC_PARAMETER, "Invalid metric parameter for Minkowski: p must be positive");
+}
+
+std::string dim_mismatch(size_t expected, size_t found)
+{
+    return "Dimension mismatch: expected " + std::to_string(expected) + ", got " + std::to_string(found);
+}
+
+} // namespace
+
+extern "C" {
+
+const char *vqb_version(void) { return "vqb 0.1 (sm_100a)"; }
+
+int vqb_ctx_create(int device, vqb_ctx **out)
+{
+    if (!out) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "out is NULL");
+    *out = nullptr;
+    vqb_ctx *ctx = nullptr;
+    int rc = guarded(nullptr, [&] {
+        std::unique_ptr<vqb_ctx> c(new vqb_ctx);
+        c->dev.reset(new CudaDevice(device));
+        ctx = c.release();
+    });
+    if (rc == VQB_OK) *out = ctx;
+    return rc;
+}
+
+int vqb_ctx_destroy(vqb_ctx *ctx)
+{
+    if (!ctx) return VQB_OK;
+    try {
+        ctx->dev->make_current();
+        ctx->dev->synchronize();
+    } catch (...) {
+    }
+    ctx->comm.reset();
+    delete ctx;
+    return VQB_OK;
+}
+
+const char *vqb_last_error(const vqb_ctx *ctx) { return ctx ? ctx->err.c_str() : g_err.c_str(); }
+
+int vqb_ctx_set_stream(vqb_ctx *ctx, void *cuda_stream)
+{
+    if (!ctx) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "ctx is NULL");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    ctx->dev->set_stream(static_cast<cudaStream_t>(cuda_stream));
+    return VQB_OK;
+}
+
+int vqb_ctx_synchronize(vqb_ctx *ctx)
+{
+    if (!ctx) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "ctx is NULL");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] { ctx->dev->synchronize(); });
+}
+
+int vqb_ctx_launch_count(const vqb_ctx *ctx, uint64_t *out)
+{
+    if (!ctx || !out) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "NULL argument");
+    *out = ctx->dev->launches();
+    return VQB_OK;
+}
+
+int vqb_ctx_timing(vqb_ctx *ctx, int enable)
+{
+    if (!ctx) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "ctx is NULL");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] { ctx->dev->set_timing(enable != 0); });
+}
+
+int vqb_ctx_timing_report(vqb_ctx *ctx, char *buf, size_t cap)
+{
+    if (!ctx || !buf || cap == 0) return set_err(ctx, VQB_ERR_BAD_ARGUMENT, "NULL argument");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        std::string r = ctx->dev->timing_report();
+        if (r.size() + 1 > cap) throw Error(VQB_ERR_BAD_ARGUMENT, "report buffer too small");
+        std::memcpy(buf, r.c_str(), r.size() + 1);
+    });
+}
+
+int vqb_comm_unique_id(uint8_t *out)
+{
+    if (!out) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "out is NULL");
+    return guarded(nullptr, [&] { nccl_unique_id(out); });
+}
+
+int vqb_comm_init(vqb_ctx *ctx, const uint8_t *unique_id, int rank, int world)
+{
+    if (!ctx || !unique_id) return set_err(ctx, VQB_ERR_BAD_ARGUMENT, "NULL argument");
+    if (world < 1 || rank < 0 || rank >= world) return set_err(ctx, VQB_ERR_BAD_ARGUMENT, "rank/world out of range");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        ctx->comm.reset();
+        ctx->comm.reset(make_nccl_comm(*ctx->dev, unique_id, rank, world));
+    });
+}
+
+int vqb_comm_destroy(vqb_ctx *ctx)
+{
+    if (!ctx) return VQB_OK;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        ctx->dev->synchronize();
+        ctx->comm.reset();
+    });
+}
+
+int vqb_distance_rows(vqb_ctx *ctx, int metric, double p, const float *a, size_t da, const float *b, size_t db, size_t n,
+                      float *out)
+{
+    if (!ctx) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "ctx is NULL");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (!metric_ok(metric)) throw Error(VQB_ERR_BAD_ARGUMENT, "unknown metric");
+        if (da != db) throw Error(VQB_ERR_DIMENSION_MISMATCH, dim_mismatch(da, db)); // src/distances.rs:119-127
+        check_minkowski(metric, p);
+        if (n == 0) return;
+        if (!a || !b || !out) throw Error(VQB_ERR_BAD_ARGUMENT, "NULL data pointer");
+        CudaDevice &dev = *ctx->dev;
+        In ia(dev, a, sizeof(float) * n * da), ib(dev, b, sizeof(float) * n * da);
+        Out o(dev, out, sizeof(float) * n);
+        dev.distance_rows(metric, p, ia.as<float>(), ib.as<float>(), da, n, o.as<float>());
+        o.finish();
+    });
+}
+
+int vqb_lbg_fit(vqb_ctx *ctx, const float *x, size_t n, size_t d, size_t k, size_t max_iters, const uint64_t *init_idx,
+                vqb_draw_fn draw, void *user, int flags, float *centroids_out, size_t *iterations_out)
+{
+    if (!ctx) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "ctx is NULL");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        CudaDevice &dev = *ctx->dev;
+        if (n && !x) throw Error(VQB_ERR_BAD_ARGUMENT, "x is NULL");
+        In ix(dev, x, sizeof(float) * n * d);
+        Shape sh;
+        sh.n_local = n;
+        sh.ld = d;
+        sh.m = 1;
+        sh.sd = d;
+        sh.k = k;
+        Out o(dev, centroids_out, sizeof(float) * k * d);
+        float *cd = o.as<float>();
+        void *tmp = nullptr;
+        if (!cd) tmp = cd = (float *)dev.alloc(sizeof(float) * k * d);
+        size_t it = 0;
+        try {
+            lbg_fit(dev, ctx->comm.get(), sh, ix.as<float>(), max_iters, init_idx, draw, user, 0, flags, cd, &it);
+        } catch (...) {
+            dev.release(tmp);
+            throw;
+        }
+        dev.release(tmp);
+        if (iterations_out) *iterations_out = it;
+        o.finish();
+    });
+}
+
+// ---- PQ ----------------------------------------------------------------------------------------
+
+int vqb_pq_fit(vqb_ctx *ctx, const float *x, size_t n, size_t dim, size_t m, size_t k, size_t max_iters, int metric,
+               double p, const uint64_t *init_idx, vqb_draw_fn draw, void *user, int flags, vqb_pq **out)
+{
+    if (!ctx || !out) return set_err(ctx, VQB_ERR_BAD_ARGUMENT, "NULL argument");
+    *out = nullptr;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (!metric_ok(metric)) throw Error(VQB_ERR_BAD_ARGUMENT, "unknown metric");
+        const bool multi = ctx->comm && ctx->comm->world() > 1;
+        if (n == 0 && !multi) // src/pq.rs:87-89
+            throw Error(VQB_ERR_EMPTY_INPUT, "Empty input: at least one vector is required.");
+        if (m == 0) throw Error(VQB_ERR_INVALID_PARAMETER, "Invalid parameter: m must be greater than 0");
+        if (dim < m) // 91-96
+            throw Error(VQB_ERR_INVALID_PARAMETER, "Invalid parameter: Data dimension must be at least m");
+        if (dim % m != 0) // 97-102
+            throw Error(VQB_ERR_INVALID_PARAMETER, "Invalid parameter: Data dimension must be divisible by m");
+        if (n && !x) throw Error(VQB_ERR_BAD_ARGUMENT, "x is NULL");
+        CudaDevice &dev = *ctx->dev;
+        std::unique_ptr<vqb_pq> pq(new vqb_pq);
+        pq->ctx = ctx;
+        pq->m = m;
+        pq->k = k;
+        pq->sd = dim / m;
+        pq->metric = metric;
+        pq->p = p;
+        pq->iters.assign(m, 0);
+        pq->codebooks = (float *)dev.alloc(sizeof(float) * m * k * pq->sd);
+        try {
+            In ix(dev, x, sizeof(float) * n * dim);
+            Shape sh;
+            sh.n_local = n;
+            sh.ld = dim;
+            sh.m = m;
+            sh.sd = pq->sd;
+            sh.k = k;
+            lbg_fit(dev, ctx->comm.get(), sh, ix.as<float>(), max_iters, init_idx, draw, user, 0, flags, pq->codebooks,
+                    pq->iters.data());
+            dev.synchronize();
+        } catch (...) {
+            dev.release(pq->codebooks);
+            throw;
+        }
+        *out = pq.release();
+    });
+}
+
+int vqb_pq_from_codebooks(vqb_ctx *ctx, const float *codebooks, size_t m, size_t k, size_t sub_dim, int metric, double p,
+                          vqb_pq **out)
+{
+    if (!ctx || !out) return set_err(ctx, VQB_ERR_BAD_ARGUMENT, "NULL argument");
+    *out = nullptr;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (!metric_ok(metric)) throw Error(VQB_ERR_BAD_ARGUMENT, "unknown metric");
+        if (!codebooks || m == 0 || k == 0 || sub_dim == 0) throw Error(VQB_ERR_BAD_ARGUMENT, "empty codebooks");
+        CudaDevice &dev = *ctx->dev;
+        std::unique_ptr<vqb_pq> pq(new vqb_pq);
+        pq->ctx = ctx;
+        pq->m = m;
+        pq->k = k;
+        pq->sd = sub_dim;
+        pq->metric = metric;
+        pq->p = p;
+        pq->iters.assign(m, 0);
+        const size_t bytes = sizeof(float) * m * k * sub_dim;
+        pq->codebooks = (float *)dev.alloc(bytes);
+        if (dev.is_device_pointer(codebooks)) dev.copy(pq->codebooks, codebooks, bytes);
+        else dev.upload(pq->codebooks, codebooks, bytes);
+        dev.synchronize();
+        *out = pq.release();
+    });
+}
+
+int vqb_pq_quantize(vqb_pq *pq, const float *x, size_t n, size_t dim, uint16_t *out_f16, uint32_t *codes)
+{
+    if (!pq) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "pq is NULL");
+    vqb_ctx *ctx = pq->ctx;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        const size_t full = pq->m * pq->sd;
+        if (dim != full) throw Error(VQB_ERR_DIMENSION_MISMATCH, dim_mismatch(full, dim)); // src/pq.rs:147-156
+        check_minkowski(pq->metric, pq->p);
+        if (n == 0) return;
+        if (!x) throw Error(VQB_ERR_BAD_ARGUMENT, "x is NULL");
+        CudaDevice &dev = *ctx->dev;
+        In ix(dev, x, sizeof(float) * n * dim);
+        Out of(dev, out_f16, sizeof(uint16_t) * n * dim), oc(dev, codes, sizeof(uint32_t) * n * pq->m);
+        Shape sh;
+        sh.n_local = n;
+        sh.ld = dim;
+        sh.m = pq->m;
+        sh.sd = pq->sd;
+        sh.k = pq->k;
+        dev.pq_encode(sh, ix.as<float>(), pq->codebooks, pq->metric, pq->p, of.as<uint16_t>(), oc.as<uint32_t>(), nullptr);
+        of.finish();
+        oc.finish();
+    });
+}
+
+int vqb_pq_shape(const vqb_pq *pq, size_t *m, size_t *k, size_t *sub_dim)
+{
+    if (!pq) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "pq is NULL");
+    if (m) *m = pq->m;
+    if (k) *k = pq->k;
+    if (sub_dim) *sub_dim = pq->sd;
+    return VQB_OK;
+}
+
+int vqb_pq_codebooks(const vqb_pq *pq, float *out)
+{
+    if (!pq || !out) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "NULL argument");
+    vqb_ctx *ctx = pq->ctx;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        const size_t bytes = sizeof(float) * pq->m * pq->k * pq->sd;
+        if (ctx->dev->is_device_pointer(out)) ctx->dev->copy(out, pq->codebooks, bytes);
+        else ctx->dev->download(out, pq->codebooks, bytes);
+    });
+}
+
+int vqb_pq_iterations(const vqb_pq *pq, size_t *out)
+{
+    if (!pq || !out) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "NULL argument");
+    for (size_t s = 0; s < pq->m; ++s) out[s] = pq->iters[s];
+    return VQB_OK;
+}
+
+int vqb_pq_destroy(vqb_pq *pq)
+{
+    if (!pq) return VQB_OK;
+    vqb_ctx *ctx = pq->ctx;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    guarded(ctx, [&] { ctx->dev->release(pq->codebooks); });
+    delete pq;
+    return VQB_OK;
+}
+
+// ---- RVQ ---------------------------------------------------------------------------------------
+
+int vqb_rvq_fit(vqb_ctx *ctx, const float *x, size_t n, size_t dim, size_t stages, size_t k, size_t max_iters,
+                float epsilon, int metric, double p, vqb_init_fn init, vqb_draw_fn draw, void *user, int flags,
+                vqb_rvq **out)
+{
+    if (!ctx || !out) return set_err(ctx, VQB_ERR_BAD_ARGUMENT, "NULL argument");
+    *out = nullptr;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (!metric_ok(metric)) throw Error(VQB_ERR_BAD_ARGUMENT, "unknown metric");
+        const bool multi = ctx->comm && ctx->comm->world() > 1;
+        if (n == 0 && !multi) // src/rvq.rs:96-98
+            throw Error(VQB_ERR_EMPTY_INPUT, "Empty input: at least one vector is required.");
+        if (n && !x) throw Error(VQB_ERR_BAD_ARGUMENT, "x is NULL");
+        CudaDevice &dev = *ctx->dev;
+        std::unique_ptr<vqb_rvq> rq(new vqb_rvq);
+        rq->ctx = ctx;
+        rq->stages = 0;
+        rq->k = k;
+        rq->dim = dim;
+        rq->epsilon = epsilon;
+        rq->metric = metric;
+        rq->p = p;
+        rq->codebooks = (float *)dev.alloc(sizeof(float) * stages * k * dim);
+        float *res = (float *)dev.alloc(sizeof(float) * n * dim); // src/rvq.rs:103
+        try {
+            const size_t bytes = sizeof(float) * n * dim;
+            if (bytes) {
+                if (dev.is_device_pointer(x)) dev.copy(res, x, bytes);
+                else dev.upload(res, x, bytes);
+            }
+            rq->stages = rvq_fit(dev, ctx->comm.get(), res, n, dim, stages, k, max_iters, epsilon, metric, p, init, draw,
+                                 user, flags, rq->codebooks);
+            dev.synchronize();
+        } catch (...) {
+            dev.release(res);
+            dev.release(rq->codebooks);
+            throw;
+        }
+        dev.release(res);
+        *out = rq.release();
+    });
+}
+
+int vqb_rvq_from_codebooks(vqb_ctx *ctx, const float *codebooks, size_t stages, size_t k, size_t dim, float epsilon,
+                           int metric, double p, vqb_rvq **out)
+{
+    if (!ctx || !out) return set_err(ctx, VQB_ERR_BAD_ARGUMENT, "NULL argument");
+    *out = nullptr;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (!metric_ok(metric)) throw Error(VQB_ERR_BAD_ARGUMENT, "unknown metric");
+        if (dim == 0 || (stages > 0 && (k == 0 || !codebooks))) throw Error(VQB_ERR_BAD_ARGUMENT, "empty codebooks");
+        CudaDevice &dev = *ctx->dev;
+        std::unique_ptr<vqb_rvq> rq(new vqb_rvq);
+        rq->ctx = ctx;
+        rq->stages = stages;
+        rq->k = k;
+        rq->dim = dim;
+        rq->epsilon = epsilon;
+        rq->metric = metric;
+        rq->p = p;
+        const size_t bytes = sizeof(float) * stages * k * dim;
+        rq->codebooks = (float *)dev.alloc(bytes);
+        if (bytes) {
+            if (dev.is_device_pointer(codebooks)) dev.copy(rq->codebooks, codebooks, bytes);
+            else dev.upload(rq->codebooks, codebooks, bytes);
+        }
+        dev.synchronize();
+        *out = rq.release();
+    });
+}
+
+int vqb_rvq_quantize(vqb_rvq *rq, const float *x, size_t n, size_t dim, uint16_t *out_f16, uint32_t *codes)
+{
+    if (!rq) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "rvq is NULL");
+    vqb_ctx *ctx = rq->ctx;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (dim != rq->dim) throw Error(VQB_ERR_DIMENSION_MISMATCH, dim_mismatch(rq->dim, dim)); // src/rvq.rs:172-180
+        if (rq->stages > 0 && rq->k >= 2) check_minkowski(rq->metric, rq->p);
+        if (n == 0) return;
+        if (!x) throw Error(VQB_ERR_BAD_ARGUMENT, "x is NULL");
+        CudaDevice &dev = *ctx->dev;
+        Out of(dev, out_f16, sizeof(uint16_t) * n * dim), oc(dev, codes, sizeof(uint32_t) * n * rq->stages);
+        if (rq->stages == 0) { // no codebooks: the sum stays zero (src/rvq.rs:182-183,209-213)
+            if (of.d) dev.zero(of.d, sizeof(uint16_t) * n * dim);
+        } else {
+            In ix(dev, x, sizeof(float) * n * dim);
+            dev.rvq_quantize(ix.as<float>(), n, dim, rq->codebooks, rq->stages, rq->k, rq->epsilon, rq->metric, rq->p,
+                             of.as<uint16_t>(), oc.as<uint32_t>());
+        }
+        of.finish();
+        oc.finish();
+    });
+}
+
+int vqb_rvq_shape(const vqb_rvq *rq, size_t *stages, size_t *k, size_t *dim)
+{
+    if (!rq) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "rvq is NULL");
+    if (stages) *stages = rq->stages;
+    if (k) *k = rq->k;
+    if (dim) *dim = rq->dim;
+    return VQB_OK;
+}
+
+int vqb_rvq_codebooks(const vqb_rvq *rq, float *out)
+{
+    if (!rq || !out) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "NULL argument");
+    vqb_ctx *ctx = rq->ctx;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        const size_t bytes = sizeof(float) * rq->stages * rq->k * rq->dim;
+        if (ctx->dev->is_device_pointer(out)) ctx->dev->copy(out, rq->codebooks, bytes);
+        else ctx->dev->download(out, rq->codebooks, bytes);
+    });
+}
+
+int vqb_rvq_destroy(vqb_rvq *rq)
+{
+    if (!rq) return VQB_OK;
+    vqb_ctx *ctx = rq->ctx;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    guarded(ctx, [&] { ctx->dev->release(rq->codebooks); });
+    delete rq;
+    return VQB_OK;
+}
+
+// ---- OPQ ---------------------------------------------------------------------------------------
+
+int vqb_opq_fit(vqb_ctx *ctx, const float *x, size_t n, size_t dim, size_t m, size_t k, size_t max_iters,
+                size_t opq_iters, int metric, double p, const uint64_t *init_idx, vqb_draw_fn draw,
+                vqb_restart_fn restart, void *user, int flags, vqb_opq **out)
+{
+    if (!ctx || !out) return set_err(ctx, VQB_ERR_BAD_ARGUMENT, "NULL argument");
+    *out = nullptr;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (!metric_ok(metric)) throw Error(VQB_ERR_BAD_ARGUMENT, "unknown metric");
+        const bool multi = ctx->comm && ctx->comm->world() > 1;
+        if (n == 0 && !multi) // src/opq.rs:99-101
+            throw Error(VQB_ERR_EMPTY_INPUT, "Empty input: at least one vector is required.");
+        if (m == 0) throw Error(VQB_ERR_INVALID_PARAMETER, "Invalid parameter: m must be greater than 0");
+        if (dim < m) // 103-108
+            throw Error(VQB_ERR_INVALID_PARAMETER, "Invalid parameter: Dimension must be at least m");
+        if (dim % m != 0) // 109-114
+            throw Error(VQB_ERR_INVALID_PARAMETER, "Invalid parameter: Dimension must be divisible by m");
+        if (n && !x) throw Error(VQB_ERR_BAD_ARGUMENT, "x is NULL");
+        CudaDevice &dev = *ctx->dev;
+        std::unique_ptr<vqb_opq> oq(new vqb_opq);
+        oq->ctx = ctx;
+        oq->m = m;
+        oq->k = k;
+        oq->sd = dim / m;
+        oq->dim = dim;
+        oq->metric = metric;
+        oq->p = p;
+        oq->rotation.assign(dim * dim, 0.0f);
+        oq->codebooks = (float *)dev.alloc(sizeof(float) * m * k * oq->sd);
+        oq->rotation_d = (float *)dev.alloc(sizeof(float) * dim * dim);
+        try {
+            In ix(dev, x, sizeof(float) * n * dim);
+            bool trained = opq_fit(dev, ctx->comm.get(), ix.as<float>(), n, dim, m, k, max_iters, opq_iters, metric, p,
+                                   init_idx, draw, restart, user, flags, oq->rotation.data(), oq->codebooks);
+            oq->empty = !trained;
+            dev.upload(oq->rotation_d, oq->rotation.data(), sizeof(float) * dim * dim);
+            dev.synchronize();
+        } catch (...) {
+            dev.release(oq->codebooks);
+            dev.release(oq->rotation_d);
+            throw;
+        }
+        *out = oq.release();
+    });
+}
+
+int vqb_opq_from_parts(vqb_ctx *ctx, const float *rotation, const float *codebooks, size_t m, size_t k, size_t sub_dim,
+                       int metric, double p, vqb_opq **out)
+{
+    if (!ctx || !out) return set_err(ctx, VQB_ERR_BAD_ARGUMENT, "NULL argument");
+    *out = nullptr;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (!metric_ok(metric)) throw Error(VQB_ERR_BAD_ARGUMENT, "unknown metric");
+        if (!rotation || !codebooks || m == 0 || k == 0 || sub_dim == 0) throw Error(VQB_ERR_BAD_ARGUMENT, "empty parts");
+        CudaDevice &dev = *ctx->dev;
+        const size_t dim = m * sub_dim;
+        std::unique_ptr<vqb_opq> oq(new vqb_opq);
+        oq->ctx = ctx;
+        oq->m = m;
+        oq->k = k;
+        oq->sd = sub_dim;
+        oq->dim = dim;
+        oq->metric = metric;
+        oq->p = p;
+        oq->empty = false;
+        oq->rotation.assign(dim * dim, 0.0f);
+        oq->codebooks = (float *)dev.alloc(sizeof(float) * m * k * sub_dim);
+        oq->rotation_d = (float *)dev.alloc(sizeof(float) * dim * dim);
+        if (dev.is_device_pointer(rotation)) dev.download(oq->rotation.data(), rotation, sizeof(float) * dim * dim);
+        else std::memcpy(oq->rotation.data(), rotation, sizeof(float) * dim * dim);
+        dev.upload(oq->rotation_d, oq->rotation.data(), sizeof(float) * dim * dim);
+        const size_t bytes = sizeof(float) * m * k * sub_dim;
+        if (dev.is_device_pointer(codebooks)) dev.copy(oq->codebooks, codebooks, bytes);
+        else dev.upload(oq->codebooks, codebooks, bytes);
+        dev.synchronize();
+        *out = oq.release();
+    });
+}
+
+int vqb_opq_quantize(vqb_opq *oq, const float *x, size_t n, size_t dim, uint16_t *out_f16, uint32_t *codes)
+{
+    if (!oq) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "opq is NULL");
+    vqb_ctx *ctx = oq->ctx;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (dim != oq->dim) throw Error(VQB_ERR_DIMENSION_MISMATCH, dim_mismatch(oq->dim, dim)); // src/opq.rs:223-231
+        if (oq->empty) return; // no codebooks: the reference returns an empty vector (src/opq.rs:244-263)
+        check_minkowski(oq->metric, oq->p);
+        if (n == 0) return;
+        if (!x) throw Error(VQB_ERR_BAD_ARGUMENT, "x is NULL");
+        CudaDevice &dev = *ctx->dev;
+        In ix(dev, x, sizeof(float) * n * dim);
+        Out of(dev, out_f16, sizeof(uint16_t) * n * dim), oc(dev, codes, sizeof(uint32_t) * n * oq->m);
+        float *y = (float *)dev.alloc(sizeof(float) * n * dim);
+        try {
+            dev.rotate_rows(oq->rotation_d, dim, ix.as<float>(), n, y); // 232-234
+            Shape sh;
+            sh.n_local = n;
+            sh.ld = dim;
+            sh.m = oq->m;
+            sh.sd = oq->sd;
+            sh.k = oq->k;
+            dev.pq_encode(sh, y, oq->codebooks, oq->metric, oq->p, of.as<uint16_t>(), oc.as<uint32_t>(), nullptr);
+        } catch (...) {
+            dev.release(y);
+            throw;
+        }
+        dev.release(y);
+        of.finish();
+        oc.finish();
+    });
+}
+
+int vqb_opq_shape(const vqb_opq *oq, size_t *m, size_t *k, size_t *sub_dim)
+{
+    if (!oq) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "opq is NULL");
+    if (m) *m = oq->empty ? 0 : oq->m;
+    if (k) *k = oq->k;
+    if (sub_dim) *sub_dim = oq->sd;
+    return VQB_OK;
+}
+
+int vqb_opq_rotation(const vqb_opq *oq, float *out)
+{
+    if (!oq || !out) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "NULL argument");
+    vqb_ctx *ctx = oq->ctx;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        const size_t bytes = sizeof(float) * oq->dim * oq->dim;
+        if (ctx->dev->is_device_pointer(out)) ctx->dev->copy(out, oq->rotation_d, bytes);
+        else std::memcpy(out, oq->rotation.data(), bytes);
+    });
+}
+
+int vqb_opq_codebooks(const vqb_opq *oq, float *out)
+{
+    if (!oq || !out) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "NULL argument");
+    vqb_ctx *ctx = oq->ctx;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (oq->empty) return;
+        const size_t bytes = sizeof(float) * oq->m * oq->k * oq->sd;
+        if (ctx->dev->is_device_pointer(out)) ctx->dev->copy(out, oq->codebooks, bytes);
+        else ctx->dev->download(out, oq->codebooks, bytes);
+    });
+}
+
+int vqb_opq_destroy(vqb_opq *oq)
+{
+    if (!oq) return VQB_OK;
+    vqb_ctx *ctx = oq->ctx;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    guarded(ctx, [&] {
+        ctx->dev->release(oq->codebooks);
+        ctx->dev->release(oq->rotation_d);
+    });
+    delete oq;
+    return VQB_OK;
+}
+
+// ---- SQ / BQ -----------------------------------------------------------------------------------
+
+int vqb_sq_fit(float min, float max, size_t levels, float *step_out)
+{
+    if (max <= min) return set_err(nullptr, VQB_ERR_INVALID_PARAMETER, "Invalid parameter: max must be greater than min");
+    if (levels < 2) return set_err(nullptr, VQB_ERR_INVALID_PARAMETER, "Invalid parameter: levels must be at least 2");
+    if (levels > 256) return set_err(nullptr, VQB_ERR_INVALID_PARAMETER, "Invalid parameter: levels must be no more than 256");
+    if (step_out) *step_out = (max - min) / (float)(levels - 1); // src/sq.rs:69
+    return VQB_OK;
+}
+
+int vqb_sq_quantize(vqb_ctx *ctx, float min, float max, size_t levels, float step, const float *x, size_t n_elems,
+                    uint8_t *out)
+{
+    if (!ctx) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "ctx is NULL");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (levels < 2 || levels > 256) throw Error(VQB_ERR_INVALID_PARAMETER, "Invalid parameter: levels must be between 2 and 256");
+        if (n_elems == 0) return;
+        if (!x || !out) throw Error(VQB_ERR_BAD_ARGUMENT, "NULL data pointer");
+        CudaDevice &dev = *ctx->dev;
+        In ix(dev, x, sizeof(float) * n_elems);
+        Out o(dev, out, n_elems);
+        dev.sq_quantize(min, max, levels, step, ix.as<float>(), n_elems, o.as<uint8_t>());
+        o.finish();
+    });
+}
+
+int vqb_bq_fit(float threshold, uint8_t low, uint8_t high)
+{
+    (void)threshold;
+    if (low >= high)
+        return set_err(nullptr, VQB_ERR_INVALID_PARAMETER,
+                       "Invalid parameter: Low quantization level must be less than high quantization level");
+    return VQB_OK;
+}
+
+int vqb_bq_quantize(vqb_ctx *ctx, float threshold, uint8_t low, uint8_t high, const float *x, size_t n_elems, uint8_t *out)
+{
+    if (!ctx) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "ctx is NULL");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (n_elems == 0) return;
+        if (!x || !out) throw Error(VQB_ERR_BAD_ARGUMENT, "NULL data pointer");
+        CudaDevice &dev = *ctx->dev;
+        In ix(dev, x, sizeof(float) * n_elems);
+        Out o(dev, out, n_elems);
+        dev.bq_quantize(threshold, low, high, ix.as<float>(), n_elems, o.as<uint8_t>());
+        o.finish();
+    });
+}
+
+} // extern "C"

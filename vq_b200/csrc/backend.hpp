@@ -1,0 +1,120 @@
+// backend.hpp -- the device operations and the collective the training loops are written against.
+//
+// The LBG / RVQ / OPQ loops (driver.cpp) hold the control flow of the reference
+// (src/utils.rs:32-109, src/rvq.rs:87-154, src/opq.rs:90-205) and call the
+// operations below for everything that touches rows of data.  The shipped
+// library implements `Device` with sm_100a kernels (cuda_device.cu) and `Comm`
+// with NCCL (nccl_comm.cpp).  There is no other implementation in the library.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+
+namespace vqb {
+
+struct Error : std::runtime_error {
+    int code;
+    Error(int c, const std::string &msg) : std::runtime_error(msg), code(c) {}
+};
+
+// One (subspace, cluster) slot that takes the bits of one data row: the initial
+// sample (src/utils.rs:54) and the empty-cluster re-seed (src/utils.rs:100).
+struct RowPatch {
+    uint32_t subspace;
+    uint32_t cluster;
+    uint64_t row; // GLOBAL row index
+};
+
+// n_local rows of `ld` floats; subspace s covers columns [s*sd, (s+1)*sd); k centroids per subspace.
+struct Shape {
+    size_t n_local = 0, ld = 0, m = 0, sd = 0, k = 0;
+};
+
+class Comm {
+  public:
+    virtual ~Comm() {}
+    virtual int rank() const = 0;
+    virtual int world() const = 0;
+    // In-place all-reduce over device buffers, ordered on the device's stream.
+    virtual void allreduce_sum_f32(float *buf, size_t n) = 0;
+    virtual void allreduce_sum_f64(double *buf, size_t n) = 0;
+    virtual void allreduce_sum_u32(uint32_t *buf, size_t n) = 0;
+    virtual void allreduce_max_u32(uint32_t *buf, size_t n) = 0;
+    virtual void allreduce_sum_u64(uint64_t *buf, size_t n) = 0;
+};
+
+class Device {
+  public:
+    virtual ~Device() {}
+    // ---- memory (device side of the boundary) ----
+    virtual void *alloc(size_t bytes) = 0;
+    virtual void release(void *p) = 0;
+    virtual void upload(void *dst, const void *src, size_t bytes) = 0;   // host -> device, complete on return
+    virtual void download(void *dst, const void *src, size_t bytes) = 0; // device -> host, complete on return
+    virtual void copy(void *dst, const void *src, size_t bytes) = 0;     // device -> device
+    virtual void zero(void *dst, size_t bytes) = 0;
+    virtual size_t code_bytes(size_t k) const = 0; // bytes per stored assignment for k centroids
+
+    // centroids[patch.subspace][patch.cluster][:] = x[patch.row - row_begin][subspace columns] for
+    // every patch; rows outside [row_begin, row_begin + n_local) come from the rank that owns them
+    // (bit patterns are exchanged with a max-reduce over zero-filled slots, so -0.0 and NaN payloads survive).
+    virtual void patch_centroids(const Shape &sh, const float *x, uint64_t row_begin, const RowPatch *patches,
+                                 size_t n_patches, float *centroids, Comm *comm) = 0;
+    // Nearest centroid under squared Euclidean (src/utils.rs:59-73); codes are read as the previous
+    // assignment and overwritten; changed[s] becomes non-zero if any row of subspace s moved (76-80).
+    // Subspaces with active[s] == 0 are left untouched.
+    virtual void assign_train(const Shape &sh, const float *x, const float *centroids, void *codes,
+                              const uint32_t *active, uint32_t *changed) = 0;
+    // sums[s][j][:] = sum of the rows assigned to (s, j), counts[s][j] = how many (src/utils.rs:83-92,
+    // src/vector.rs:297-314).  ordered = ascending row order per cluster.
+    virtual void accumulate(const Shape &sh, const float *x, const void *codes, const uint32_t *active,
+                            bool ordered, float *sums, uint32_t *counts) = 0;
+    // centroids = sums / (counts as f32) where counts > 0 (src/vector.rs:315-316), active subspaces only.
+    virtual void finalize(const Shape &sh, const float *sums, const uint32_t *counts, const uint32_t *active,
+                          float *centroids) = 0;
+    // Residual update of one RVQ stage (src/rvq.rs:111-138): argmin with `metric`, res -= centroid in place,
+    // *norm_sum += sum over rows of sqrt(sum res^2) (f64, device scalar, not cleared here).
+    virtual void rvq_update(float *res, size_t n, size_t dim, const float *centroids, size_t k, int metric,
+                            double p, double *norm_sum) = 0;
+    // PQ encode (src/pq.rs:159-186 per row; also the OPQ reconstruction src/opq.rs:146-168 via out_f32).
+    virtual void pq_encode(const Shape &sh, const float *x, const float *codebooks, int metric, double p,
+                           uint16_t *out_f16, uint32_t *out_codes, float *out_f32) = 0;
+    // y[r] = R * x[r] (src/opq.rs:186-194, 232-234); R row-major dim x dim.
+    virtual void rotate_rows(const float *rot, size_t dim, const float *x, size_t n, float *y) = 0;
+    // a[i][j] += sum_r y[r][i] * x[r][j]  (A = Y * X^T, src/opq.rs:172-179), f64 dim x dim, cleared here.
+    virtual void cross_cov(const float *y, const float *x, size_t n, size_t dim, double *a) = 0;
+};
+
+// ---- training loops (driver.cpp) ------------------------------------------------------------
+
+typedef uint64_t (*DrawFn)(void *user, size_t stream, uint64_t n);
+typedef void (*InitFn)(void *user, size_t stage, uint64_t n, size_t k, uint64_t *out);
+typedef void (*RestartFn)(void *user);
+
+struct LbgResult {
+    size_t iterations[1];
+};
+
+// Batched lbg_quantize over the m subspaces of `sh` (m == 1, sd == ld for a full-width run).
+// init_idx: m x k global row indices.  stream0: draw-stream id of subspace 0 (subspace s asks stream0 + s).
+// centroids: device, m x k x sd, written.  iterations: host, m entries (may be null).
+void lbg_fit(Device &dev, Comm *comm, const Shape &sh, const float *x, size_t max_iters, const uint64_t *init_idx,
+             DrawFn draw, void *user, size_t stream0, int flags, float *centroids, size_t *iterations);
+
+// src/rvq.rs:87-154.  res: device copy of the data, overwritten with the final residuals.
+// codebooks: device, stages x k x dim.  Returns the number of stages produced.
+size_t rvq_fit(Device &dev, Comm *comm, float *res, size_t n_local, size_t dim, size_t stages, size_t k,
+               size_t max_iters, float epsilon, int metric, double p, InitFn init, DrawFn draw, void *user,
+               int flags, float *codebooks);
+
+// src/opq.rs:90-205.  x: device original rows; rotation: HOST dim x dim row-major out; codebooks: device m x k x sd.
+// Returns false when opq_iters == 0 (identity rotation, no codebooks).
+bool opq_fit(Device &dev, Comm *comm, const float *x, size_t n_local, size_t dim, size_t m, size_t k,
+             size_t max_iters, size_t opq_iters, int metric, double p, const uint64_t *init_idx, DrawFn draw,
+             RestartFn restart, void *user, int flags, float *rotation_host, float *codebooks);
+
+// Thin one-sided Jacobi SVD of a square matrix (f64): a = u * diag(s) * v^T, all row-major n x n.
+void jacobi_svd(const double *a, size_t n, double *u, double *s, double *v);
+
+} // namespace vqb

@@ -1,0 +1,778 @@
+// cuda_device.cu -- sm_100a implementation of vqb::Device: centroid accumulation and update, row
+// patches, rotation / cross-covariance for OPQ, row-wise distances and the element-wise quantizers.
+// The nearest-centroid kernels live in assign_reg.cuh / assign_generic.cuh (launched from assign_launch.cu).
+#include "cuda_device.hpp"
+
+#include <algorithm>
+#include <vector>
+
+#include "assign_generic.cuh"
+#include "assign_reg.cuh"
+#include "kernels_common.cuh"
+
+namespace vqb {
+
+// ------------------------------------------------------------------------------------------------
+// context plumbing
+// ------------------------------------------------------------------------------------------------
+CudaDevice::CudaDevice(int device) : device_(device)
+{
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0)
+        throw Error(102, std::string("no CUDA device available: ") + (e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0"));
+    if (device < 0 || device >= count) throw Error(102, "CUDA device index out of range");
+    VQB_CUDA_CHECK(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    VQB_CUDA_CHECK(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        throw Error(102, std::string("this library contains sm_100a code only; device is ") + prop.name);
+    sm_count_ = prop.multiProcessorCount;
+    smem_limit_ = prop.sharedMemPerBlockOptin;
+    VQB_CUDA_CHECK(cudaStreamCreateWithFlags(&own_stream_, cudaStreamNonBlocking));
+    stream_ = own_stream_;
+    cudaMemPool_t pool;
+    if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
+        unsigned long long keep = ~0ull; // keep freed blocks cached; repeated fits reuse them
+        cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    }
+}
+
+CudaDevice::~CudaDevice()
+{
+    if (own_stream_) {
+        cudaSetDevice(device_);
+        cudaStreamSynchronize(own_stream_);
+        cudaStreamDestroy(own_stream_);
+    }
+}
+
+void CudaDevice::set_timing(bool on)
+{
+    if (!on) {
+        for (auto &sp : spans_) {
+            cudaEventDestroy(sp.a);
+            cudaEventDestroy(sp.b);
+        }
+        spans_.clear();
+    }
+    timing_ = on;
+}
+
+void CudaDevice::timing_begin(const char *name)
+{
+    Span sp;
+    sp.name = name;
+    VQB_CUDA_CHECK(cudaEventCreate(&sp.a));
+    VQB_CUDA_CHECK(cudaEventCreate(&sp.b));
+    VQB_CUDA_CHECK(cudaEventRecord(sp.a, stream_));
+    spans_.push_back(sp);
+}
+
+void CudaDevice::timing_end()
+{
+    if (!spans_.empty()) cudaEventRecord(spans_.back().b, stream_);
+}
+
+std::string CudaDevice::timing_report()
+{
+    VQB_CUDA_CHECK(cudaStreamSynchronize(stream_));
+    std::map<std::string, std::pair<uint64_t, double>> agg;
+    for (auto &sp : spans_) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, sp.a, sp.b) == cudaSuccess) {
+            auto &e = agg[sp.name];
+            e.first += 1;
+            e.second += ms;
+        }
+        cudaEventDestroy(sp.a);
+        cudaEventDestroy(sp.b);
+    }
+    spans_.clear();
+    std::string out = "{";
+    bool first = true;
+    for (auto &kv : agg) {
+        if (!first) out += ", ";
+        first = false;
+        out += "\"" + kv.first + "\": {\"launches\": " + std::to_string(kv.second.first) + ", \"ms\": " + std::to_string(kv.second.second) + "}";
+    }
+    return out + "}";
+}
+
+void CudaDevice::make_current() const { VQB_CUDA_CHECK(cudaSetDevice(device_)); }
+
+void CudaDevice::synchronize() { VQB_CUDA_CHECK(cudaStreamSynchronize(stream_)); }
+
+bool CudaDevice::is_device_pointer(const void *p) const
+{
+    if (!p) return false;
+    cudaPointerAttributes attr;
+    cudaError_t e = cudaPointerGetAttributes(&attr, p);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+}
+
+void *CudaDevice::alloc(size_t bytes)
+{
+    void *p = nullptr;
+    VQB_CUDA_CHECK(cudaMallocAsync(&p, bytes ? bytes : 1, stream_));
+    return p;
+}
+
+void CudaDevice::release(void *p)
+{
+    if (p) cudaFreeAsync(p, stream_);
+}
+
+void CudaDevice::upload(void *dst, const void *src, size_t bytes)
+{
+    if (!bytes) return;
+    VQB_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, stream_));
+    VQB_CUDA_CHECK(cudaStreamSynchronize(stream_));
+}
+
+void CudaDevice::download(void *dst, const void *src, size_t bytes)
+{
+    if (!bytes) return;
+    VQB_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, stream_));
+    VQB_CUDA_CHECK(cudaStreamSynchronize(stream_));
+}
+
+void CudaDevice::copy(void *dst, const void *src, size_t bytes)
+{
+    if (!bytes) return;
+    VQB_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, stream_));
+}
+
+void CudaDevice::zero(void *dst, size_t bytes)
+{
+    if (!bytes) return;
+    VQB_CUDA_CHECK(cudaMemsetAsync(dst, 0, bytes, stream_));
+}
+
+static inline unsigned blocks_for(size_t items, int threads, size_t cap = 1u << 20)
+{
+    size_t b = (items + threads - 1) / threads;
+    return (unsigned)std::max<size_t>(1, std::min(b, cap));
+}
+
+// ------------------------------------------------------------------------------------------------
+// row patches: initial sample (src/utils.rs:54) and empty-cluster re-seed (src/utils.rs:100)
+// ------------------------------------------------------------------------------------------------
+__global__ void patch_fill_kernel(const float *x, unsigned long long n_local, unsigned long long ld, int sd,
+                                  unsigned long long row_begin, const RowPatch *patches, unsigned long long n_patches,
+                                  uint32_t *stage)
+{
+    const unsigned long long total = n_patches * sd;
+    for (unsigned long long t = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; t < total;
+         t += (unsigned long long)gridDim.x * blockDim.x) {
+        const unsigned long long pi = t / sd;
+        const int d = (int)(t % sd);
+        const RowPatch pt = patches[pi];
+        uint32_t bits = 0;
+        if (pt.row >= row_begin && pt.row - row_begin < n_local)
+            bits = __float_as_uint(x[(pt.row - row_begin) * ld + (size_t)pt.subspace * sd + d]);
+        stage[t] = bits;
+    }
+}
+
+__global__ void patch_scatter_kernel(const uint32_t *stage, const RowPatch *patches, unsigned long long n_patches, int k,
+                                     int sd, float *centroids)
+{
+    const unsigned long long total = n_patches * sd;
+    for (unsigned long long t = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; t < total;
+         t += (unsigned long long)gridDim.x * blockDim.x) {
+        const unsigned long long pi = t / sd;
+        const int d = (int)(t % sd);
+        const RowPatch pt = patches[pi];
+        centroids[((size_t)pt.subspace * k + pt.cluster) * sd + d] = __uint_as_float(stage[t]);
+    }
+}
+
+void CudaDevice::patch_centroids(const Shape &sh, const float *x, uint64_t row_begin, const RowPatch *patches,
+                                 size_t n_patches, float *centroids, Comm *comm)
+{
+    if (n_patches == 0) return;
+    RowPatch *pd = (RowPatch *)alloc(sizeof(RowPatch) * n_patches);
+    uint32_t *stage = (uint32_t *)alloc(sizeof(uint32_t) * n_patches * sh.sd);
+    upload(pd, patches, sizeof(RowPatch) * n_patches);
+    const size_t total = n_patches * sh.sd;
+    KernelScope ks(*this, "patch_centroids");
+    patch_fill_kernel<<<blocks_for(total, 256, 4096), 256, 0, stream_>>>(x, sh.n_local, sh.ld, (int)sh.sd, row_begin, pd,
+                                                                       n_patches, stage);
+    VQB_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+    if (comm && comm->world() > 1) comm->allreduce_max_u32(stage, total);
+    patch_scatter_kernel<<<blocks_for(total, 256, 4096), 256, 0, stream_>>>(stage, pd, n_patches, (int)sh.k, (int)sh.sd,
+                                                                          centroids);
+    VQB_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+    release(stage);
+    release(pd);
+}
+
+// ------------------------------------------------------------------------------------------------
+// assignment (training) and encode: thin wrappers over the kernel launchers
+// ------------------------------------------------------------------------------------------------
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+void CudaDevice::assign_train(const Shape &sh, const float *x, const float *centroids, void *codes,
+                              const uint32_t *active, uint32_t *changed)
+{
+    if (sh.n_local == 0) return;
+    AssignParams p = {};
+    p.x = x;
+    p.n = sh.n_local;
+    p.ld = sh.ld;
+    p.m = (int)sh.m;
+    p.k = (int)sh.k;
+    p.sd = (int)sh.sd;
+    p.centroids = centroids;
+    p.codes = codes;
+    p.active = active;
+    p.changed = changed;
+    p.x_vec4 = aligned16(x) && (sh.ld % 4 == 0) && (sh.sd % 4 == 0);
+    if (launch_assign_reg(*this, p, M_SQ, true, code_bytes(sh.k))) return;
+    GenericParams g = {};
+    g.x = x;
+    g.n = sh.n_local;
+    g.ld = sh.ld;
+    g.m = (int)sh.m;
+    g.k = (int)sh.k;
+    g.sd = (int)sh.sd;
+    g.centroids = centroids;
+    g.codes = codes;
+    g.active = active;
+    g.changed = changed;
+    launch_assign_generic(*this, g, M_SQ, G_TRAIN, code_bytes(sh.k));
+}
+
+void CudaDevice::pq_encode(const Shape &sh, const float *x, const float *codebooks, int metric, double pm,
+                           uint16_t *out_f16, uint32_t *out_codes, float *out_f32)
+{
+    if (sh.n_local == 0) return;
+    const size_t dim = sh.m * sh.sd;
+    AssignParams p = {};
+    p.x = x;
+    p.n = sh.n_local;
+    p.ld = sh.ld;
+    p.m = (int)sh.m;
+    p.k = (int)sh.k;
+    p.sd = (int)sh.sd;
+    p.centroids = codebooks;
+    p.out_f16 = out_f16;
+    p.out_codes = out_codes;
+    p.out_f32 = out_f32;
+    p.pv = (float)pm;
+    p.x_vec4 = aligned16(x) && (sh.ld % 4 == 0) && (sh.sd % 4 == 0);
+    p.out_vec = (!out_f16 || (aligned16(out_f16) && dim % 8 == 0)) && (!out_f32 || (aligned16(out_f32) && dim % 4 == 0));
+    if (launch_assign_reg(*this, p, metric, false, 4)) return;
+    GenericParams g = {};
+    g.x = x;
+    g.n = sh.n_local;
+    g.ld = sh.ld;
+    g.m = (int)sh.m;
+    g.k = (int)sh.k;
+    g.sd = (int)sh.sd;
+    g.centroids = codebooks;
+    g.out_f16 = out_f16;
+    g.out_codes = out_codes;
+    g.out_f32 = out_f32;
+    g.pv = (float)pm;
+    launch_assign_generic(*this, g, metric, G_ENCODE, 4);
+}
+
+void CudaDevice::rvq_update(float *res, size_t n, size_t dim, const float *centroids, size_t k, int metric, double pm,
+                            double *norm_sum)
+{
+    if (n == 0) return;
+    GenericParams g = {};
+    g.x = res;
+    g.res = res;
+    g.n = n;
+    g.ld = dim;
+    g.m = 1;
+    g.k = (int)k;
+    g.sd = (int)dim;
+    g.centroids = centroids;
+    g.pv = (float)pm;
+    g.norm_sum = norm_sum;
+    launch_assign_generic(*this, g, metric, G_RVQ_UPDATE, 4);
+}
+
+void CudaDevice::rvq_quantize(const float *x, size_t n, size_t dim, const float *codebooks, size_t stages, size_t k,
+                              float epsilon, int metric, double pm, uint16_t *out_f16, uint32_t *out_codes)
+{
+    if (n == 0) return;
+    if (out_codes) VQB_CUDA_CHECK(cudaMemsetAsync(out_codes, 0xFF, sizeof(uint32_t) * n * stages, stream_));
+    GenericParams g = {};
+    g.x = x;
+    g.n = n;
+    g.ld = dim;
+    g.m = 1;
+    g.k = (int)k;
+    g.sd = (int)dim;
+    g.centroids = codebooks;
+    g.pv = (float)pm;
+    g.out_f16 = out_f16;
+    g.out_codes = out_codes;
+    g.stages = (int)stages;
+    g.epsilon = epsilon;
+    launch_assign_generic(*this, g, metric, G_RVQ_QUANT, 4);
+}
+
+// ------------------------------------------------------------------------------------------------
+// cluster sums and counts (src/utils.rs:83-92 + src/vector.rs:297-314)
+// ------------------------------------------------------------------------------------------------
+// FAST, narrow subspaces: one thread per (row, subspace); shared-memory sums laid out [s][d][code] so
+// that the 32 lanes of a warp (different rows, arbitrary codes) spread over the banks.
+template <typename CodeT>
+__global__ void accum_small_kernel(const float *x, unsigned long long n, unsigned long long ld, int m, int k, int sd,
+                                   int group, const CodeT *codes, const uint32_t *active, float *sums, uint32_t *counts)
+{
+    extern __shared__ __align__(16) float smem[];
+    const int g0 = blockIdx.y * group;
+    const int gcount = min(group, m - g0);
+    float *ssum = smem;                                               // [gcount][sd][k]
+    uint32_t *scnt = reinterpret_cast<uint32_t *>(smem + (size_t)group * sd * k); // [gcount][k]
+    for (int t = threadIdx.x; t < gcount * sd * k; t += blockDim.x) ssum[t] = 0.0f;
+    for (int t = threadIdx.x; t < gcount * k; t += blockDim.x) scnt[t] = 0u;
+    __syncthreads();
+    const unsigned long long total = n * gcount;
+    for (unsigned long long pidx = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; pidx < total;
+         pidx += (unsigned long long)gridDim.x * blockDim.x) {
+        const unsigned long long row = pidx / gcount;
+        const int sl = (int)(pidx % gcount);
+        const int s = g0 + sl;
+        if (active && active[s] == 0) continue;
+        const int code = (int)codes[row * m + s];
+        const float *xp = x + row * ld + (size_t)s * sd;
+        float *dst = ssum + (size_t)sl * sd * k + code;
+        for (int d = 0; d < sd; ++d) atomicAdd(dst + (size_t)d * k, xp[d]);
+        atomicAdd(scnt + sl * k + code, 1u);
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < gcount * k * sd; t += blockDim.x) {
+        const int sl = t / (k * sd), rem = t % (k * sd);
+        const int j = rem / sd, d = rem % sd;
+        if (scnt[sl * k + j] != 0u) atomicAdd(sums + ((size_t)(g0 + sl) * k + j) * sd + d, ssum[((size_t)sl * sd + d) * k + j]);
+    }
+    for (int t = threadIdx.x; t < gcount * k; t += blockDim.x)
+        if (scnt[t] != 0u) atomicAdd(counts + (size_t)g0 * k + t, scnt[t]);
+}
+
+// FAST, wide rows: one warp per (row, subspace), lanes over dimensions; sums laid out [code][d].
+// With shared == false the atomics go straight to global memory (codebook too large for shared memory).
+template <typename CodeT, bool SHARED>
+__global__ void accum_wide_kernel(const float *x, unsigned long long n, unsigned long long ld, int m, int k, int sd,
+                                  const CodeT *codes, const uint32_t *active, float *sums, uint32_t *counts)
+{
+    extern __shared__ __align__(16) float smem[];
+    const int s = blockIdx.y;
+    if (active && active[s] == 0) return;
+    float *ssum = smem;                                                    // [k][sd]
+    uint32_t *scnt = reinterpret_cast<uint32_t *>(smem + (size_t)k * sd); // [k]
+    float *gsum = sums + (size_t)s * k * sd;
+    uint32_t *gcnt = counts + (size_t)s * k;
+    if (SHARED) {
+        for (int t = threadIdx.x; t < k * sd; t += blockDim.x) ssum[t] = 0.0f;
+        for (int t = threadIdx.x; t < k; t += blockDim.x) scnt[t] = 0u;
+        __syncthreads();
+    }
+    const int lane = threadIdx.x & 31;
+    const unsigned long long warps = (unsigned long long)gridDim.x * (blockDim.x >> 5);
+    for (unsigned long long row = blockIdx.x * (unsigned long long)(blockDim.x >> 5) + (threadIdx.x >> 5); row < n; row += warps) {
+        const int code = (int)codes[row * m + s];
+        const float *xp = x + row * ld + (size_t)s * sd;
+        float *dst = (SHARED ? ssum : gsum) + (size_t)code * sd;
+        for (int d = lane; d < sd; d += 32) atomicAdd(dst + d, xp[d]);
+        if (lane == 0) atomicAdd((SHARED ? scnt : gcnt) + code, 1u);
+    }
+    if (SHARED) {
+        __syncthreads();
+        for (int t = threadIdx.x; t < k * sd; t += blockDim.x)
+            if (scnt[t / sd] != 0u) atomicAdd(gsum + t, ssum[t]);
+        for (int t = threadIdx.x; t < k; t += blockDim.x)
+            if (scnt[t] != 0u) atomicAdd(gcnt + t, scnt[t]);
+    }
+}
+
+// ORDERED: one thread per (cluster, dimension) walks all rows in ascending order and adds the members
+// of its cluster, which is exactly the serial branch of mean_vector (src/vector.rs:305-313).
+template <typename CodeT>
+__global__ void __launch_bounds__(256) accum_ordered_kernel(const float *x, unsigned long long n, unsigned long long ld, int m,
+                                                            int k, int sd, const CodeT *codes, const uint32_t *active,
+                                                            float *sums, uint32_t *counts)
+{
+    __shared__ CodeT sc[2048];
+    const int s = blockIdx.y;
+    if (active && active[s] == 0) return;
+    const int sdc = min(sd, 256);            // dimensions handled per pass
+    const int cpb = max(1, 256 / sdc);       // clusters per block
+    const int jl = threadIdx.x / sdc, dl = threadIdx.x % sdc;
+    const int j = blockIdx.x * cpb + jl;
+    for (int d0 = 0; d0 < sd; d0 += sdc) {
+        const int d = d0 + dl;
+        const bool mine = (jl < cpb) && (j < k) && (d < sd);
+        float acc = 0.0f;
+        uint32_t cnt = 0;
+        for (unsigned long long r0 = 0; r0 < n; r0 += 2048) {
+            const int cn = (int)min((unsigned long long)2048, n - r0);
+            __syncthreads();
+            for (int t = threadIdx.x; t < cn; t += blockDim.x) sc[t] = codes[(r0 + t) * m + s];
+            __syncthreads();
+            if (mine) {
+                const float *xp = x + r0 * ld + (size_t)s * sd + d;
+                for (int r = 0; r < cn; ++r)
+                    if ((int)sc[r] == j) {
+                        acc = __fadd_rn(acc, xp[(size_t)r * ld]);
+                        ++cnt;
+                    }
+            }
+        }
+        if (mine) {
+            sums[((size_t)s * k + j) * sd + d] = acc;
+            if (d == 0) counts[(size_t)s * k + j] = cnt;
+        }
+    }
+}
+
+template <typename CodeT>
+static void accumulate_t(CudaDevice &dev, const Shape &sh, const float *x, const CodeT *codes, const uint32_t *active,
+                         bool ordered, float *sums, uint32_t *counts)
+{
+    const int m = (int)sh.m, k = (int)sh.k, sd = (int)sh.sd;
+    cudaStream_t st = dev.stream();
+    if (ordered) {
+        const int sdc = std::min(sd, 256), cpb = std::max(1, 256 / sdc);
+        dim3 grid((k + cpb - 1) / cpb, m);
+        KernelScope ks(dev, "accumulate_ordered");
+        accum_ordered_kernel<CodeT><<<grid, 256, 0, st>>>(x, sh.n_local, sh.ld, m, k, sd, codes, active, sums, counts);
+        VQB_CUDA_CHECK(cudaGetLastError());
+        dev.count_launch();
+        return;
+    }
+    if (sh.n_local == 0) return;
+    const size_t budget = dev.smem_limit() - 1024;
+    const size_t per_sub = (size_t)k * (sd + 1) * sizeof(float);
+    if (sd <= 32 && per_sub <= budget) {
+        int group = (int)std::min<size_t>(m, budget / per_sub);
+        const size_t smem = (size_t)group * per_sub;
+        auto kernel = accum_small_kernel<CodeT>;
+        VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        const int threads = 1024;
+        const unsigned long long pairs = (unsigned long long)sh.n_local * group;
+        unsigned gx = (unsigned)std::min<unsigned long long>((pairs + threads - 1) / threads, (unsigned long long)dev.sm_count());
+        dim3 grid(std::max(1u, gx), (m + group - 1) / group);
+        KernelScope ks(dev, "accumulate_fast");
+        kernel<<<grid, threads, smem, st>>>(x, sh.n_local, sh.ld, m, k, sd, group, codes, active, sums, counts);
+        VQB_CUDA_CHECK(cudaGetLastError());
+        dev.count_launch();
+        return;
+    }
+    const int threads = 512;
+    KernelScope ks(dev, "accumulate_fast");
+    if (per_sub <= budget) {
+        auto kernel = accum_wide_kernel<CodeT, true>;
+        VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)per_sub));
+        unsigned gx = (unsigned)std::min<unsigned long long>((sh.n_local + 15) / 16, (unsigned long long)std::max(1, dev.sm_count() / m));
+        dim3 grid(std::max(1u, gx), m);
+        kernel<<<grid, threads, per_sub, st>>>(x, sh.n_local, sh.ld, m, k, sd, codes, active, sums, counts);
+    } else {
+        unsigned gx = (unsigned)std::min<unsigned long long>((sh.n_local + 15) / 16, (unsigned long long)dev.sm_count() * 4);
+        dim3 grid(std::max(1u, gx), m);
+        accum_wide_kernel<CodeT, false><<<grid, threads, 0, st>>>(x, sh.n_local, sh.ld, m, k, sd, codes, active, sums, counts);
+    }
+    VQB_CUDA_CHECK(cudaGetLastError());
+    dev.count_launch();
+}
+
+void CudaDevice::accumulate(const Shape &sh, const float *x, const void *codes, const uint32_t *active, bool ordered,
+                            float *sums, uint32_t *counts)
+{
+    zero(sums, sizeof(float) * sh.m * sh.k * sh.sd);
+    zero(counts, sizeof(uint32_t) * sh.m * sh.k);
+    const size_t cb = code_bytes(sh.k);
+    if (cb == 1) accumulate_t<uint8_t>(*this, sh, x, (const uint8_t *)codes, active, ordered, sums, counts);
+    else if (cb == 2) accumulate_t<uint16_t>(*this, sh, x, (const uint16_t *)codes, active, ordered, sums, counts);
+    else accumulate_t<uint32_t>(*this, sh, x, (const uint32_t *)codes, active, ordered, sums, counts);
+}
+
+// centroid = sum / (count as f32), IEEE division (src/vector.rs:315-316); empty clusters keep their old
+// value until the host patches them (src/utils.rs:99-101).
+__global__ void finalize_kernel(const float *sums, const uint32_t *counts, const uint32_t *active, int k, int sd,
+                                unsigned long long total, float *centroids)
+{
+    for (unsigned long long t = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; t < total;
+         t += (unsigned long long)gridDim.x * blockDim.x) {
+        const unsigned long long cj = t / sd;
+        const int s = (int)(cj / k);
+        if (active && active[s] == 0) continue;
+        const uint32_t c = counts[cj];
+        if (c != 0u) centroids[t] = __fdiv_rn(sums[t], __uint2float_rn(c));
+    }
+}
+
+void CudaDevice::finalize(const Shape &sh, const float *sums, const uint32_t *counts, const uint32_t *active,
+                          float *centroids)
+{
+    const size_t total = sh.m * sh.k * sh.sd;
+    if (!total) return;
+    KernelScope ks(*this, "finalize");
+    finalize_kernel<<<blocks_for(total, 256, 2048), 256, 0, stream_>>>(sums, counts, active, (int)sh.k, (int)sh.sd, total, centroids);
+    VQB_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+}
+
+// ------------------------------------------------------------------------------------------------
+// OPQ: y = R x per row (src/opq.rs:186-194, 232-234) and A = Y X^T (src/opq.rs:172-179)
+// ------------------------------------------------------------------------------------------------
+// 64x64 output tile per CTA, 4x4 per thread, 16-wide steps over the contraction index.
+__global__ void __launch_bounds__(256) rotate_rows_kernel(const float *rot, int dim, const float *x, unsigned long long n, float *y)
+{
+    __shared__ float xs[16][64 + 1]; // [jj][row]
+    __shared__ float rs[16][64 + 1]; // [jj][out]
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const unsigned long long row0 = (unsigned long long)blockIdx.y * 64;
+    const int out0 = blockIdx.x * 64;
+    float acc[4][4] = {};
+    for (int j0 = 0; j0 < dim; j0 += 16) {
+        for (int t = threadIdx.x; t < 64 * 16; t += 256) {
+            const int r = t >> 4, jj = t & 15;
+            const unsigned long long row = row0 + r;
+            const int j = j0 + jj;
+            xs[jj][r] = (row < n && j < dim) ? x[row * dim + j] : 0.0f;
+            const int o = out0 + r;
+            rs[jj][r] = (o < dim && j < dim) ? rot[(size_t)o * dim + j] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                a[i] = xs[jj][ty * 4 + i];
+                b[i] = rs[jj][tx * 4 + i];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int l = 0; l < 4; ++l) acc[i][l] = fmaf(a[i], b[l], acc[i][l]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const unsigned long long row = row0 + ty * 4 + i;
+        if (row >= n) continue;
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const int o = out0 + tx * 4 + l;
+            if (o < dim) y[row * dim + o] = acc[i][l];
+        }
+    }
+}
+
+void CudaDevice::rotate_rows(const float *rot, size_t dim, const float *x, size_t n, float *y)
+{
+    if (n == 0 || dim == 0) return;
+    const unsigned long long row_tiles = (n + 63) / 64;
+    // gridDim.y is limited to 65535: walk the rows in slabs
+    const unsigned long long slab = 65535ull;
+    for (unsigned long long t0 = 0; t0 < row_tiles; t0 += slab) {
+        const unsigned long long tiles = std::min(slab, row_tiles - t0);
+        const unsigned long long r0 = t0 * 64;
+        const unsigned long long rows = std::min<unsigned long long>(n - r0, tiles * 64);
+        dim3 grid((unsigned)((dim + 63) / 64), (unsigned)tiles);
+        KernelScope ks(*this, "rotate_rows");
+        rotate_rows_kernel<<<grid, 256, 0, stream_>>>(rot, (int)dim, x + r0 * dim, rows, y + r0 * dim);
+        VQB_CUDA_CHECK(cudaGetLastError());
+        count_launch();
+    }
+}
+
+// Each CTA reduces `rows_per_cta` rows into a 64x64 tile of A in f32 and adds it to the f64 result.
+__global__ void __launch_bounds__(256) cross_cov_kernel(const float *y, const float *x, unsigned long long n, int dim,
+                                                        unsigned long long rows_per_cta, double *a)
+{
+    __shared__ float ys[16][64 + 4];
+    __shared__ float xs[16][64 + 4];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int i0 = blockIdx.y * 64, j0 = blockIdx.x * 64;
+    const unsigned long long r_begin = (unsigned long long)blockIdx.z * rows_per_cta;
+    const unsigned long long r_end = min(n, r_begin + rows_per_cta);
+    float acc[4][4] = {};
+    for (unsigned long long r0 = r_begin; r0 < r_end; r0 += 16) {
+        for (int t = threadIdx.x; t < 16 * 64; t += 256) {
+            const int rr = t >> 6, c = t & 63;
+            const unsigned long long row = r0 + rr;
+            const bool ok = row < r_end;
+            ys[rr][c] = (ok && i0 + c < dim) ? y[row * dim + i0 + c] : 0.0f;
+            xs[rr][c] = (ok && j0 + c < dim) ? x[row * dim + j0 + c] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int rr = 0; rr < 16; ++rr) {
+            float p[4], q[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                p[i] = ys[rr][ty * 4 + i];
+                q[i] = xs[rr][tx * 4 + i];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int l = 0; l < 4; ++l) acc[i][l] = fmaf(p[i], q[l], acc[i][l]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const int ii = i0 + ty * 4 + i, jj = j0 + tx * 4 + l;
+            if (ii < dim && jj < dim) atomicAdd(a + (size_t)ii * dim + jj, (double)acc[i][l]);
+        }
+}
+
+void CudaDevice::cross_cov(const float *y, const float *x, size_t n, size_t dim, double *a)
+{
+    zero(a, sizeof(double) * dim * dim);
+    if (n == 0 || dim == 0) return;
+    const unsigned long long rows_per_cta = 2048;
+    const unsigned long long splits = (n + rows_per_cta - 1) / rows_per_cta;
+    const unsigned long long slab = 65535ull;
+    const unsigned tiles = (unsigned)((dim + 63) / 64);
+    for (unsigned long long z0 = 0; z0 < splits; z0 += slab) {
+        const unsigned long long zs = std::min(slab, splits - z0);
+        const unsigned long long r0 = z0 * rows_per_cta;
+        const unsigned long long rows = std::min<unsigned long long>(n - r0, zs * rows_per_cta);
+        dim3 grid(tiles, tiles, (unsigned)zs);
+        KernelScope ks(*this, "cross_cov");
+        cross_cov_kernel<<<grid, 256, 0, stream_>>>(y + r0 * dim, x + r0 * dim, rows, (int)dim, rows_per_cta, a);
+        VQB_CUDA_CHECK(cudaGetLastError());
+        count_launch();
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Distance::compute per row pair (src/distances.rs:115-172)
+// ------------------------------------------------------------------------------------------------
+template <int METRIC>
+__global__ void distance_rows_kernel(const float *a, const float *b, int d, unsigned long long n, float pv, float *out)
+{
+    for (unsigned long long r = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; r < n;
+         r += (unsigned long long)gridDim.x * blockDim.x) {
+        const float *pa = a + r * d, *pb = b + r * d;
+        float na = 0.0f;
+        if (METRIC == M_COSINE) na = norm_chain(pa, d, 1);
+        DistAcc<METRIC> acc;
+        acc.init();
+        for (int i = 0; i < d; ++i) acc.step(pa[i], pb[i], pv);
+        out[r] = acc.finish(pv, na);
+    }
+}
+
+void CudaDevice::distance_rows(int metric, double p, const float *a, const float *b, size_t d, size_t n, float *out)
+{
+    if (n == 0) return;
+    const unsigned grid = blocks_for(n, 128, 4096);
+    const float pv = (float)p;
+#define VQB_DR(M) distance_rows_kernel<M><<<grid, 128, 0, stream_>>>(a, b, (int)d, n, pv, out)
+    switch (metric) {
+    case M_SQ: VQB_DR(M_SQ); break;
+    case M_EUCLID: VQB_DR(M_EUCLID); break;
+    case M_COSINE: VQB_DR(M_COSINE); break;
+    case M_MANHATTAN: VQB_DR(M_MANHATTAN); break;
+    case M_CHEBYSHEV: VQB_DR(M_CHEBYSHEV); break;
+    case M_MINKOWSKI: VQB_DR(M_MINKOWSKI); break;
+    case M_HAMMING: VQB_DR(M_HAMMING); break;
+    default: throw Error(90, "unknown metric");
+    }
+#undef VQB_DR
+    VQB_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+}
+
+// ------------------------------------------------------------------------------------------------
+// ScalarQuantizer / BinaryQuantizer (src/sq.rs:117-127, src/bq.rs:94-100): pure streaming kernels,
+// 16 values per thread step (4 x 128-bit loads, one 128-bit store), 5 bytes of traffic per value.
+// ------------------------------------------------------------------------------------------------
+struct SqOp {
+    float mn, mx, step;
+    unsigned last;
+    __device__ __forceinline__ unsigned operator()(float v) const
+    {
+        const float c = (v < mn) ? mn : ((v > mx) ? mx : v); // NaN passes through both tests
+        const float q = __fdiv_rn(__fsub_rn(c, mn), step);
+        const unsigned idx = __float2uint_rz(roundf(q)); // round half away from zero; saturating, NaN -> 0 (`as usize`)
+        return min(idx, last);
+    }
+};
+
+struct BqOp {
+    float thr;
+    unsigned low, high;
+    __device__ __forceinline__ unsigned operator()(float v) const { return (v >= thr) ? high : low; }
+};
+
+__device__ __forceinline__ float4 ld_stream(const float4 *p)
+{
+    float4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+
+template <typename Op>
+__global__ void __launch_bounds__(256) elementwise_u8_kernel(const float *__restrict__ x, unsigned long long n, Op op,
+                                                             uint8_t *__restrict__ out, int vec)
+{
+    const unsigned long long tid = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x;
+    const unsigned long long nthreads = (unsigned long long)gridDim.x * blockDim.x;
+    if (vec) {
+        const unsigned long long n16 = n / 16;
+        const float4 *x4 = reinterpret_cast<const float4 *>(x);
+        uint4 *o4 = reinterpret_cast<uint4 *>(out);
+        for (unsigned long long i = tid; i < n16; i += nthreads) {
+            float4 v[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) v[t] = ld_stream(x4 + 4 * i + t);
+            unsigned w[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) w[t] = op(v[t].x) | (op(v[t].y) << 8) | (op(v[t].z) << 16) | (op(v[t].w) << 24);
+            __stcs(o4 + i, make_uint4(w[0], w[1], w[2], w[3]));
+        }
+        for (unsigned long long i = n16 * 16 + tid; i < n; i += nthreads) out[i] = (uint8_t)op(x[i]);
+    } else {
+        for (unsigned long long i = tid; i < n; i += nthreads) out[i] = (uint8_t)op(x[i]);
+    }
+}
+
+template <typename Op> static void launch_elementwise(CudaDevice &dev, const char *name, const float *x, size_t n, Op op, uint8_t *out)
+{
+    if (n == 0) return;
+    const int vec = aligned16(x) && aligned16(out);
+    const size_t items = vec ? (n + 15) / 16 : n;
+    const unsigned grid = (unsigned)std::max<size_t>(1, std::min<size_t>((items + 255) / 256, (size_t)dev.sm_count() * 32));
+    KernelScope ks(dev, name);
+    elementwise_u8_kernel<Op><<<grid, 256, 0, dev.stream()>>>(x, n, op, out, vec);
+    VQB_CUDA_CHECK(cudaGetLastError());
+    dev.count_launch();
+}
+
+void CudaDevice::sq_quantize(float mn, float mx, size_t levels, float step, const float *x, size_t n, uint8_t *out)
+{
+    SqOp op{mn, mx, step, (unsigned)(levels - 1)};
+    launch_elementwise(*this, "sq_quantize", x, n, op, out);
+}
+
+void CudaDevice::bq_quantize(float threshold, uint8_t low, uint8_t high, const float *x, size_t n, uint8_t *out)
+{
+    BqOp op{threshold, low, high};
+    launch_elementwise(*this, "bq_quantize", x, n, op, out);
+}
+
+} // namespace vqb

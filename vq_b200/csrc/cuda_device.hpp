@@ -1,0 +1,110 @@
+// cuda_device.hpp -- the sm_100a implementation of vqb::Device plus the element-wise quantizers.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "backend.hpp"
+
+namespace vqb {
+
+#define VQB_CUDA_CHECK(expr)                                                                                       \
+    do {                                                                                                           \
+        cudaError_t _e = (expr);                                                                                   \
+        if (_e != cudaSuccess)                                                                                     \
+            throw ::vqb::Error(100, std::string("CUDA error: ") + cudaGetErrorString(_e) + " at " + __FILE__ + ":" + \
+                                        std::to_string(__LINE__));                                                 \
+    } while (0)
+
+class CudaDevice : public Device {
+  public:
+    explicit CudaDevice(int device);
+    ~CudaDevice() override;
+
+    void *alloc(size_t bytes) override;
+    void release(void *p) override;
+    void upload(void *dst, const void *src, size_t bytes) override;
+    void download(void *dst, const void *src, size_t bytes) override;
+    void copy(void *dst, const void *src, size_t bytes) override;
+    void zero(void *dst, size_t bytes) override;
+    size_t code_bytes(size_t k) const override { return k <= 256 ? 1 : (k <= 65536 ? 2 : 4); }
+
+    void patch_centroids(const Shape &sh, const float *x, uint64_t row_begin, const RowPatch *patches, size_t n_patches,
+                         float *centroids, Comm *comm) override;
+    void assign_train(const Shape &sh, const float *x, const float *centroids, void *codes, const uint32_t *active,
+                      uint32_t *changed) override;
+    void accumulate(const Shape &sh, const float *x, const void *codes, const uint32_t *active, bool ordered,
+                    float *sums, uint32_t *counts) override;
+    void finalize(const Shape &sh, const float *sums, const uint32_t *counts, const uint32_t *active,
+                  float *centroids) override;
+    void rvq_update(float *res, size_t n, size_t dim, const float *centroids, size_t k, int metric, double p,
+                    double *norm_sum) override;
+    void pq_encode(const Shape &sh, const float *x, const float *codebooks, int metric, double p, uint16_t *out_f16,
+                   uint32_t *out_codes, float *out_f32) override;
+    void rotate_rows(const float *rot, size_t dim, const float *x, size_t n, float *y) override;
+    void cross_cov(const float *y, const float *x, size_t n, size_t dim, double *a) override;
+
+    // Not part of the training loops:
+    void rvq_quantize(const float *x, size_t n, size_t dim, const float *codebooks, size_t stages, size_t k,
+                      float epsilon, int metric, double p, uint16_t *out_f16, uint32_t *out_codes);
+    void distance_rows(int metric, double p, const float *a, const float *b, size_t d, size_t n, float *out);
+    void sq_quantize(float mn, float mx, size_t levels, float step, const float *x, size_t n, uint8_t *out);
+    void bq_quantize(float threshold, uint8_t low, uint8_t high, const float *x, size_t n, uint8_t *out);
+
+    void set_stream(cudaStream_t s) { stream_ = s ? s : own_stream_; }
+    cudaStream_t stream() const { return stream_; }
+    void synchronize();
+    int device() const { return device_; }
+    int sm_count() const { return sm_count_; }
+    size_t smem_limit() const { return smem_limit_; }
+    uint64_t launches() const { return launches_.load(); }
+    void count_launch(uint64_t n = 1) { launches_ += n; }
+    void make_current() const;
+    // Optional per-kernel timing with CUDA events on the launching stream (off by default).
+    void set_timing(bool on);
+    bool timing() const { return timing_; }
+    void timing_begin(const char *name);
+    void timing_end();
+    // {"name": {"launches": L, "ms": T}, ...}; clears the record.
+    std::string timing_report();
+    // True when p points to device memory usable by kernels on this GPU.
+    bool is_device_pointer(const void *p) const;
+
+  private:
+    int device_;
+    int sm_count_ = 148;
+    size_t smem_limit_ = 0;
+    cudaStream_t own_stream_ = nullptr, stream_ = nullptr;
+    std::atomic<uint64_t> launches_{0};
+    bool timing_ = false;
+    struct Span {
+        const char *name;
+        cudaEvent_t a, b;
+    };
+    std::vector<Span> spans_;
+};
+
+// Brackets one kernel launch for the optional timing record.
+struct KernelScope {
+    CudaDevice &dev;
+    KernelScope(CudaDevice &d, const char *name) : dev(d)
+    {
+        if (dev.timing()) dev.timing_begin(name);
+    }
+    ~KernelScope()
+    {
+        if (dev.timing()) dev.timing_end();
+    }
+};
+
+// assign_launch.cu
+struct AssignParams;
+struct GenericParams;
+// Returns false when the register kernel does not cover this shape/metric.
+bool launch_assign_reg(CudaDevice &dev, const AssignParams &p, int metric, bool train, size_t code_bytes);
+void launch_assign_generic(CudaDevice &dev, GenericParams &p, int metric, int mode, size_t code_bytes);
+
+} // namespace vqb

@@ -1,0 +1,283 @@
+// driver.cpp -- host control flow of codebook training, written against Device/Comm (backend.hpp).
+//
+// Follows the reference's loops step for step:
+//   lbg_fit  <- lbg_quantize                      src/utils.rs:32-109  (batched over PQ subspaces, src/pq.rs:106-121)
+//   rvq_fit  <- ResidualQuantizer::fit            src/rvq.rs:87-154
+//   opq_fit  <- OptimizedProductQuantizer::fit    src/opq.rs:90-205
+// Everything that touches rows of data is a Device call; every exchange between ranks is a Comm call.
+#include "backend.hpp"
+
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+#include "../../include/vqb.h"
+
+namespace vqb {
+
+namespace {
+
+struct DevBuf {
+    Device &dev;
+    void *p = nullptr;
+    DevBuf(Device &d, size_t bytes) : dev(d) { p = dev.alloc(bytes ? bytes : 1); }
+    ~DevBuf() { dev.release(p); }
+    DevBuf(const DevBuf &) = delete;
+    DevBuf &operator=(const DevBuf &) = delete;
+    template <typename T> T *as() const { return static_cast<T *>(p); }
+};
+
+// Total rows over all ranks and the global index of this rank's first row (shards are contiguous
+// blocks in rank order).
+void global_rows(Device &dev, Comm *comm, size_t n_local, uint64_t *n_global, uint64_t *row_begin)
+{
+    *n_global = n_local;
+    *row_begin = 0;
+    if (!comm || comm->world() <= 1) return;
+    const int w = comm->world();
+    std::vector<uint64_t> per(w, 0);
+    per[comm->rank()] = n_local;
+    DevBuf buf(dev, sizeof(uint64_t) * w);
+    dev.upload(buf.p, per.data(), sizeof(uint64_t) * w);
+    comm->allreduce_sum_u64(buf.as<uint64_t>(), w);
+    dev.download(per.data(), buf.p, sizeof(uint64_t) * w);
+    uint64_t total = 0;
+    for (int r = 0; r < w; ++r) {
+        if (r == comm->rank()) *row_begin = total;
+        total += per[r];
+    }
+    *n_global = total;
+}
+
+bool use_ordered(int flags, uint64_t n_global)
+{
+    if (flags == VQB_ACCUM_ORDERED) return true;
+    if (flags == VQB_ACCUM_FAST) return false;
+    return n_global <= 65536;
+}
+
+} // namespace
+
+void lbg_fit(Device &dev, Comm *comm, const Shape &sh, const float *x, size_t max_iters, const uint64_t *init_idx,
+             DrawFn draw, void *user, size_t stream0, int flags, float *centroids, size_t *iterations)
+{
+    const size_t m = sh.m, k = sh.k, sd = sh.sd;
+    uint64_t n_global = 0, row_begin = 0;
+    global_rows(dev, comm, sh.n_local, &n_global, &row_begin);
+    if (k == 0) // src/utils.rs:39-44
+        throw Error(VQB_ERR_INVALID_PARAMETER, "Invalid parameter: k must be greater than 0");
+    if (n_global < k) // src/utils.rs:45-50
+        throw Error(VQB_ERR_INVALID_PARAMETER, "Invalid parameter: Not enough data points for k clusters");
+    if (!init_idx) throw Error(VQB_ERR_BAD_ARGUMENT, "init_idx is NULL");
+    const bool multi = comm && comm->world() > 1;
+    const bool ordered = use_ordered(flags, n_global);
+
+    // initial sample: k rows per subspace (src/utils.rs:52-54)
+    std::vector<RowPatch> patches;
+    patches.reserve(m * k);
+    for (size_t s = 0; s < m; ++s)
+        for (size_t j = 0; j < k; ++j) {
+            uint64_t r = init_idx[s * k + j];
+            if (r >= n_global) throw Error(VQB_ERR_INVALID_PARAMETER, "Invalid parameter: initial row index out of range");
+            patches.push_back(RowPatch{(uint32_t)s, (uint32_t)j, r});
+        }
+    dev.patch_centroids(sh, x, row_begin, patches.data(), patches.size(), centroids, comm);
+    if (iterations)
+        for (size_t s = 0; s < m; ++s) iterations[s] = 0;
+    if (max_iters == 0) return; // src/utils.rs:57 never runs
+
+    const size_t cb = dev.code_bytes(k);
+    DevBuf codes(dev, sh.n_local * m * cb);
+    dev.zero(codes.p, sh.n_local * m * cb); // src/utils.rs:55: previous assignments start at 0
+    DevBuf sums(dev, sizeof(float) * m * k * sd);
+    DevBuf cc(dev, sizeof(uint32_t) * (m * k + m)); // counts[m][k] then changed[m]
+    DevBuf act(dev, sizeof(uint32_t) * m);
+    uint32_t *counts_d = cc.as<uint32_t>();
+    uint32_t *changed_d = counts_d + m * k;
+    std::vector<uint32_t> active(m, 1), cc_h(m * k + m);
+
+    for (size_t it = 0; it < max_iters; ++it) {
+        bool any = false;
+        for (size_t s = 0; s < m; ++s) any = any || active[s];
+        if (!any) break;
+        dev.upload(act.p, active.data(), sizeof(uint32_t) * m);
+        dev.zero(changed_d, sizeof(uint32_t) * m);
+        dev.assign_train(sh, x, centroids, codes.p, act.as<uint32_t>(), changed_d);               // 59-80
+        dev.accumulate(sh, x, codes.p, act.as<uint32_t>(), ordered, sums.as<float>(), counts_d); // 83-92
+        if (multi) {
+            comm->allreduce_sum_f32(sums.as<float>(), m * k * sd);
+            comm->allreduce_sum_u32(counts_d, m * k + m);
+        }
+        dev.finalize(sh, sums.as<float>(), counts_d, act.as<uint32_t>(), centroids); // 95-99
+        dev.download(cc_h.data(), cc.p, sizeof(uint32_t) * (m * k + m));
+        patches.clear();
+        for (size_t s = 0; s < m; ++s) {
+            if (!active[s]) continue;
+            if (iterations) iterations[s] += 1;
+            for (size_t j = 0; j < k; ++j) // ascending j, one draw per empty cluster (95-101)
+                if (cc_h[s * k + j] == 0) {
+                    if (!draw) throw Error(VQB_ERR_CALLBACK, "an empty cluster needs a draw callback");
+                    uint64_t r = draw(user, stream0 + s, n_global);
+                    if (r >= n_global) throw Error(VQB_ERR_CALLBACK, "draw callback returned a row index out of range");
+                    patches.push_back(RowPatch{(uint32_t)s, (uint32_t)j, r});
+                }
+        }
+        if (!patches.empty())
+            dev.patch_centroids(sh, x, row_begin, patches.data(), patches.size(), centroids, comm);
+        for (size_t s = 0; s < m; ++s)
+            if (active[s] && cc_h[m * k + s] == 0) active[s] = 0; // 104-106: stop after the update
+    }
+}
+
+size_t rvq_fit(Device &dev, Comm *comm, float *res, size_t n_local, size_t dim, size_t stages, size_t k,
+               size_t max_iters, float epsilon, int metric, double p, InitFn init, DrawFn draw, void *user,
+               int flags, float *codebooks)
+{
+    uint64_t n_global = 0, row_begin = 0;
+    global_rows(dev, comm, n_local, &n_global, &row_begin);
+    const bool multi = comm && comm->world() > 1;
+    Shape sh;
+    sh.n_local = n_local;
+    sh.ld = dim;
+    sh.m = 1;
+    sh.sd = dim;
+    sh.k = k;
+    DevBuf norm(dev, sizeof(double));
+    std::vector<uint64_t> idx(k ? k : 1, 0);
+    size_t done = 0;
+    for (size_t stage = 0; stage < stages; ++stage) { // src/rvq.rs:105
+        float *cb = codebooks + stage * k * dim;
+        if (k > 0 && n_global >= k) {
+            if (!init) throw Error(VQB_ERR_BAD_ARGUMENT, "init callback is NULL");
+            init(user, stage, n_global, k, idx.data());
+        }
+        lbg_fit(dev, comm, sh, res, max_iters, idx.data(), draw, user, stage, flags, cb, nullptr); // 107
+        ++done;
+        if (k >= 2 && metric == VQB_MINKOWSKI && p <= 0.0) // first distance.compute call (rvq.rs:118)
+            throw Error(VQB_ERR_INVALID_METRIC_PARAMETER, "Invalid metric parameter for Minkowski: p must be positive");
+        dev.zero(norm.p, sizeof(double));
+        dev.rvq_update(res, n_local, dim, cb, k, metric, p, norm.as<double>()); // 111-138
+        if (multi) comm->allreduce_sum_f64(norm.as<double>(), 1);
+        double total = 0.0;
+        dev.download(&total, norm.p, sizeof(double));
+        float avg = (float)(total / (double)n_global);
+        if (avg < epsilon) break; // 139-141
+    }
+    return done; // 145
+}
+
+bool opq_fit(Device &dev, Comm *comm, const float *x, size_t n_local, size_t dim, size_t m, size_t k,
+             size_t max_iters, size_t opq_iters, int metric, double p, const uint64_t *init_idx, DrawFn draw,
+             RestartFn restart, void *user, int flags, float *rotation_host, float *codebooks)
+{
+    for (size_t i = 0; i < dim; ++i)
+        for (size_t j = 0; j < dim; ++j) rotation_host[i * dim + j] = (i == j) ? 1.0f : 0.0f; // src/opq.rs:119
+    if (opq_iters == 0) return false;
+    const bool multi = comm && comm->world() > 1;
+    Shape sh;
+    sh.n_local = n_local;
+    sh.ld = dim;
+    sh.m = m;
+    sh.sd = dim / m;
+    sh.k = k;
+    const size_t bytes = sizeof(float) * n_local * dim;
+    DevBuf rotated(dev, bytes), rec(dev, bytes);
+    DevBuf a_d(dev, sizeof(double) * dim * dim), rot_d(dev, sizeof(float) * dim * dim);
+    dev.copy(rotated.p, x, bytes); // src/opq.rs:121
+    std::vector<double> a(dim * dim), u(dim * dim), sv(dim), v(dim * dim);
+    for (size_t it = 0; it < opq_iters; ++it) { // 124
+        if (restart) restart(user);             // the reference builds fresh StdRng(seed + i) here (140)
+        lbg_fit(dev, comm, sh, rotated.as<float>(), max_iters, init_idx, draw, user, 0, flags, codebooks, nullptr);
+        if (k >= 2 && metric == VQB_MINKOWSKI && p <= 0.0)
+            throw Error(VQB_ERR_INVALID_METRIC_PARAMETER, "Invalid metric parameter for Minkowski: p must be positive");
+        dev.pq_encode(sh, rotated.as<float>(), codebooks, metric, p, nullptr, nullptr, rec.as<float>()); // 146-168
+        dev.cross_cov(rec.as<float>(), rotated.as<float>(), n_local, dim, a_d.as<double>());            // 172-179
+        if (multi) comm->allreduce_sum_f64(a_d.as<double>(), dim * dim);
+        dev.download(a.data(), a_d.p, sizeof(double) * dim * dim);
+        jacobi_svd(a.data(), dim, u.data(), sv.data(), v.data()); // 180-182
+        for (size_t i = 0; i < dim; ++i)                          // rotation = V * U^T (183)
+            for (size_t j = 0; j < dim; ++j) {
+                double acc = 0.0;
+                for (size_t t = 0; t < dim; ++t) acc += v[i * dim + t] * u[j * dim + t];
+                rotation_host[i * dim + j] = (float)acc;
+            }
+        dev.upload(rot_d.p, rotation_host, sizeof(float) * dim * dim);
+        dev.rotate_rows(rot_d.as<float>(), dim, x, n_local, rotated.as<float>()); // 186-194, from the ORIGINAL rows
+    }
+    return true;
+}
+
+// One-sided (Hestenes) Jacobi SVD in f64.  Columns with a vanishing singular value get an orthonormal
+// completion so that U stays orthogonal (V * U^T must be a rotation even for rank-deficient input).
+void jacobi_svd(const double *a, size_t n, double *u, double *s, double *v)
+{
+    std::vector<double> g(a, a + n * n); // g = a * v, columns converge to u * sigma
+    for (size_t i = 0; i < n; ++i)
+        for (size_t j = 0; j < n; ++j) v[i * n + j] = (i == j) ? 1.0 : 0.0;
+    const double eps = 1e-15;
+    for (int sweep = 0; sweep < 60; ++sweep) {
+        bool rotated = false;
+        for (size_t p = 0; p + 1 < n; ++p)
+            for (size_t q = p + 1; q < n; ++q) {
+                double alpha = 0, beta = 0, gamma = 0;
+                for (size_t i = 0; i < n; ++i) {
+                    double gp = g[i * n + p], gq = g[i * n + q];
+                    alpha += gp * gp;
+                    beta += gq * gq;
+                    gamma += gp * gq;
+                }
+                if (std::fabs(gamma) <= eps * std::sqrt(alpha * beta) || gamma == 0.0) continue;
+                rotated = true;
+                double zeta = (beta - alpha) / (2.0 * gamma);
+                double t = (zeta >= 0 ? 1.0 : -1.0) / (std::fabs(zeta) + std::sqrt(1.0 + zeta * zeta));
+                double c = 1.0 / std::sqrt(1.0 + t * t), sn = c * t;
+                for (size_t i = 0; i < n; ++i) {
+                    double gp = g[i * n + p], gq = g[i * n + q];
+                    g[i * n + p] = c * gp - sn * gq;
+                    g[i * n + q] = sn * gp + c * gq;
+                    double vp = v[i * n + p], vq = v[i * n + q];
+                    v[i * n + p] = c * vp - sn * vq;
+                    v[i * n + q] = sn * vp + c * vq;
+                }
+            }
+        if (!rotated) break;
+    }
+    double smax = 0.0;
+    for (size_t j = 0; j < n; ++j) {
+        double nn = 0;
+        for (size_t i = 0; i < n; ++i) nn += g[i * n + j] * g[i * n + j];
+        s[j] = std::sqrt(nn);
+        if (s[j] > smax) smax = s[j];
+    }
+    std::vector<char> filled(n, 0);
+    for (size_t j = 0; j < n; ++j)
+        if (s[j] > smax * 1e-13 && s[j] > 0.0) {
+            for (size_t i = 0; i < n; ++i) u[i * n + j] = g[i * n + j] / s[j];
+            filled[j] = 1;
+        }
+    for (size_t j = 0; j < n; ++j) { // complete the null space, Gram-Schmidt over unit vectors
+        if (filled[j]) continue;
+        s[j] = 0.0;
+        for (size_t e = 0; e < n; ++e) {
+            std::vector<double> w(n, 0.0);
+            w[e] = 1.0;
+            for (int pass = 0; pass < 2; ++pass)
+                for (size_t c = 0; c < n; ++c) {
+                    if (!filled[c]) continue;
+                    double d = 0;
+                    for (size_t i = 0; i < n; ++i) d += w[i] * u[i * n + c];
+                    for (size_t i = 0; i < n; ++i) w[i] -= d * u[i * n + c];
+                }
+            double nn = 0;
+            for (size_t i = 0; i < n; ++i) nn += w[i] * w[i];
+            if (nn > 1e-6) {
+                nn = std::sqrt(nn);
+                for (size_t i = 0; i < n; ++i) u[i * n + j] = w[i] / nn;
+                filled[j] = 1;
+                break;
+            }
+        }
+    }
+}
+
+} // namespace vqb
