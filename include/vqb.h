@@ -86,9 +86,12 @@ int vqb_ctx_destroy(vqb_ctx *ctx);
 /* Message of the last failing call on `ctx` (or of the last failing call on
  * this thread that had no context, when ctx == NULL). */
 const char *vqb_last_error(const vqb_ctx *ctx);
-/* Run all work of `ctx` on the caller's CUDA stream (cudaStream_t); NULL = the
- * context's own stream. */
+/* Run all work of `ctx` on the caller's CUDA stream (cudaStream_t).  NULL is the
+ * CUDA default stream (what a framework's "current stream" usually is), NOT "no
+ * stream": work is then ordered with everything else on that stream. */
 int vqb_ctx_set_stream(vqb_ctx *ctx, void *cuda_stream);
+/* Back to the context's own (non-blocking) stream, the state after creation. */
+int vqb_ctx_reset_stream(vqb_ctx *ctx);
 int vqb_ctx_synchronize(vqb_ctx *ctx);
 /* Number of kernels this context has launched so far. */
 int vqb_ctx_launch_count(const vqb_ctx *ctx, uint64_t *out);

@@ -11,13 +11,24 @@ class RecordingSeeder:
 
     def __init__(self, seed):
         self.seed = seed
+        self._pq_args = None
         self.reset()
 
     def reset(self):
+        """Fresh RNG streams, re-consuming the initial sample if one was drawn (the reference re-creates
+        StdRng(seed + i) at every OPQ outer iteration, src/opq.rs:140)."""
         self.s = LbgSeeder(self.seed)
         self.draws = []
+        if getattr(self, "_pq_args", None):
+            n, m, k = self._pq_args
+            for i in range(m):
+                self.s.init_indices(i, n, k)
+
+    def __call__(self, stream, n):
+        return self.draw(stream, n)
 
     def init_pq(self, n, m, k):
+        self._pq_args = (n, m, k)
         return np.stack([self.s.init_indices(i, n, k) for i in range(m)])
 
     def init_stage(self, stage, n, k):
@@ -27,6 +38,15 @@ class RecordingSeeder:
         r = self.s.draw(stream, n)
         self.draws.append((stream, r))
         return r
+
+
+def by_stream(draws):
+    """Per-stream draw sequences: the oracle finishes one subspace before the next while the library advances all
+    subspaces together, so only the order WITHIN a stream (one reference RNG each) is comparable."""
+    out = {}
+    for stream, r in draws:
+        out.setdefault(stream, []).append(r)
+    return out
 
 
 def near_tie_mismatches(oracle, codebooks, x, codes_a, codes_b, metric, p=0.0):

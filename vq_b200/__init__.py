@@ -137,7 +137,9 @@ class Context:
             pass
 
     def set_stream(self, cuda_stream: int | None):
-        rc = _lib.load().vqb_ctx_set_stream(self.handle, C.c_void_p(cuda_stream or 0))
+        """Run on the given cudaStream_t handle (0 = the CUDA default stream); None = the context's own stream."""
+        L = _lib.load()
+        rc = L.vqb_ctx_reset_stream(self.handle) if cuda_stream is None else L.vqb_ctx_set_stream(self.handle, C.c_void_p(cuda_stream))
         if rc:
             _raise(rc, self.handle)
 
@@ -169,6 +171,7 @@ class Context:
         host-memory inputs; None returns to the default behaviour (caller's torch stream for CUDA tensors, the
         context's own stream for host arrays)."""
         self._sticky = cuda_stream
+        self._pinned = cuda_stream is not None
         self.set_stream(cuda_stream)
 
     def init_comm(self, unique_id: bytes, rank: int, world: int):
@@ -234,7 +237,7 @@ class _Arr:
             self.shape = tuple(t.shape)
             self.ptr = t.data_ptr()
             self.device = t.device
-            if getattr(ctx, "_sticky", None) is None:
+            if not getattr(ctx, "_pinned", False):
                 ctx.set_stream(torch.cuda.current_stream(t.device).cuda_stream)
         else:
             if _is_torch(x):
@@ -243,7 +246,7 @@ class _Arr:
             self.keep = a
             self.shape = a.shape
             self.ptr = a.ctypes.data
-            if getattr(ctx, "_sticky", None) is None:
+            if not getattr(ctx, "_pinned", False):
                 ctx.set_stream(None)
         self.single = len(self.shape) == 1
         if want_2d:

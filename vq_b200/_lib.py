@@ -28,6 +28,7 @@ SIGNATURES = {
     "vqb_ctx_destroy": (C.c_int, [_P]),
     "vqb_last_error": (C.c_char_p, [_P]),
     "vqb_ctx_set_stream": (C.c_int, [_P, _P]),
+    "vqb_ctx_reset_stream": (C.c_int, [_P]),
     "vqb_ctx_synchronize": (C.c_int, [_P]),
     "vqb_ctx_launch_count": (C.c_int, [_P, C.POINTER(C.c_uint64)]),
     "vqb_ctx_timing": (C.c_int, [_P, C.c_int]),

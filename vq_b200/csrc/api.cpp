@@ -191,6 +191,14 @@ int vqb_ctx_set_stream(vqb_ctx *ctx, void *cuda_stream)
     return VQB_OK;
 }
 
+int vqb_ctx_reset_stream(vqb_ctx *ctx)
+{
+    if (!ctx) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "ctx is NULL");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    ctx->dev->reset_stream();
+    return VQB_OK;
+}
+
 int vqb_ctx_synchronize(vqb_ctx *ctx)
 {
     if (!ctx) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "ctx is NULL");

@@ -54,7 +54,8 @@ class CudaDevice : public Device {
     void sq_quantize(float mn, float mx, size_t levels, float step, const float *x, size_t n, uint8_t *out);
     void bq_quantize(float threshold, uint8_t low, uint8_t high, const float *x, size_t n, uint8_t *out);
 
-    void set_stream(cudaStream_t s) { stream_ = s ? s : own_stream_; }
+    void set_stream(cudaStream_t s) { stream_ = s; } // nullptr = the CUDA default stream
+    void reset_stream() { stream_ = own_stream_; }
     cudaStream_t stream() const { return stream_; }
     void synchronize();
     int device() const { return device_; }
