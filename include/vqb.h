@@ -175,6 +175,24 @@ int vqb_opq_from_parts(vqb_ctx *ctx, const float *rotation /* dim x dim row-majo
 /* OptimizedProductQuantizer::quantize for n rows, src/opq.rs:222-264. */
 int vqb_opq_quantize(vqb_opq *opq, const float *x, size_t n, size_t dim, uint16_t *out_f16,
                      uint32_t *codes);
+/* OPQ encode that allocates nothing.  No counterpart in the reference (which has no device memory to manage).
+ * For embedders that own all of HBM through their own pool, or that must not enter the CUDA allocator from a
+ * request loop: the rotated rows that vqb_opq_quantize keeps in pool memory live here in a fixed array inside
+ * the library image (VQB_OPQ_STATIC_MAX_FLOATS floats = 4 MiB, resident on every GPU that loads the library,
+ * for the life of the process).
+ *   - x, out_f16 and codes must be DEVICE pointers (either output may be NULL, not both); host pointers are
+ *     refused because staging them would allocate;
+ *   - n * dim must not exceed VQB_OPQ_STATIC_MAX_FLOATS, otherwise VQB_ERR_UNSUPPORTED with a message;
+ *   - per-kernel timing (vqb_ctx_timing) must be off;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first
+ *     call before starting any stream capture;
+ *   - all calls, from all quantizers of the process, share the one array per GPU and it keeps whatever the last
+ *     call wrote; each call overwrites the part it reads, so nothing needs clearing, but two calls whose GPU work
+ *     overlaps (different streams or contexts on one GPU) race on it -- keep them on one stream.
+ * Results are identical to vqb_opq_quantize. */
+#define VQB_OPQ_STATIC_MAX_FLOATS (1u << 20)
+int vqb_opq_quantize_static(vqb_opq *opq, const float *x, size_t n, size_t dim, uint16_t *out_f16,
+                            uint32_t *codes);
 int vqb_opq_shape(const vqb_opq *opq, size_t *m, size_t *k, size_t *sub_dim);
 int vqb_opq_rotation(const vqb_opq *opq, float *out /* dim x dim row-major */);
 int vqb_opq_codebooks(const vqb_opq *opq, float *out /* m x k x sub_dim */);

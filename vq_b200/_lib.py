@@ -57,6 +57,7 @@ SIGNATURES = {
                               C.c_int, C.POINTER(_P)]),
     "vqb_opq_from_parts": (C.c_int, [_P, _P, _P, _SZ, _SZ, _SZ, C.c_int, C.c_double, C.POINTER(_P)]),
     "vqb_opq_quantize": (C.c_int, [_P, _P, _SZ, _SZ, _P, _P]),
+    "vqb_opq_quantize_static": (C.c_int, [_P, _P, _SZ, _SZ, _P, _P]),
     "vqb_opq_shape": (C.c_int, [_P, C.POINTER(_SZ), C.POINTER(_SZ), C.POINTER(_SZ)]),
     "vqb_opq_rotation": (C.c_int, [_P, _P]),
     "vqb_opq_codebooks": (C.c_int, [_P, _P]),

@@ -12,6 +12,7 @@
 
 #include "../../include/vqb.h"
 #include "cuda_device.hpp"
+#include "opq_parts.hpp"
 
 namespace vqb {
 void nccl_unique_id(uint8_t *out128);
@@ -149,6 +150,26 @@ std::string dim_mismatch(size_t expected, size_t found)
 }
 
 } // namespace
+
+namespace vqb {
+OpqParts opq_parts(vqb_opq *oq)
+{
+    OpqParts v;
+    v.dev = oq->ctx->dev.get();
+    v.mu = &oq->ctx->mu;
+    v.err = &oq->ctx->err;
+    v.rotation = oq->rotation_d;
+    v.codebooks = oq->codebooks;
+    v.m = oq->m;
+    v.k = oq->k;
+    v.sd = oq->sd;
+    v.dim = oq->dim;
+    v.metric = oq->metric;
+    v.p = oq->p;
+    v.empty = oq->empty;
+    return v;
+}
+} // namespace vqb
 
 extern "C" {
 
