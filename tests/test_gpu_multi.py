@@ -1,0 +1,49 @@
+"""Two GPUs, one process each: rows sharded, centroid sums/counts all-reduced by NCCL inside the library."""
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from tests.util import RecordingSeeder
+from vq_b200 import synth
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def test_two_gpu_fit_matches_the_oracle(oracle, tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    prefix = os.path.join(str(tmp_path), "out")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE="2", NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "multi_gpu_worker.py"), prefix],
+                              env=dict(env, RANK=str(r), LOCAL_RANK=str(r)), stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+             for r in range(2)]
+    for p in procs:
+        out, _ = p.communicate(timeout=600)
+        assert p.returncode == 0, out.decode()[-3000:]
+    res = [np.load(f"{prefix}.rank{r}.npz") for r in range(2)]
+    n, dim, m, k = 40001, 32, 4, 64
+    x_int = np.random.default_rng(3).integers(0, 40, (n, dim)).astype(np.float32)
+    x_flt = synth.uniform01(n, dim, 5)
+    so = RecordingSeeder(9)
+    init = so.init_pq(n, m, k)
+    cb_int, it_int = oracle.pq_fit(x_int, m, k, 6, init, so.draw)
+    so2 = RecordingSeeder(9)
+    cb_flt, it_flt = oracle.pq_fit(x_flt, m, k, 6, so2.init_pq(n, m, k), so2.draw)
+    for r in res:
+        assert np.array_equal(r["cb_int"], cb_int) and np.array_equal(r["it_int"], it_int)
+        rel = np.linalg.norm(r["cb_flt"] - cb_flt, axis=2) / np.linalg.norm(cb_flt, axis=2)
+        assert rel.max() <= 1e-3
+    assert np.array_equal(res[0]["cb_flt"], res[1]["cb_flt"])
+    codes = np.concatenate([res[0]["codes_int"], res[1]["codes_int"]]).astype(np.uint32)
+    _o, codes_o = oracle.pq_quantize(cb_int, x_int, oracle.EUCLIDEAN)
+    assert np.array_equal(codes, codes_o)
