@@ -106,6 +106,7 @@ def cpu_reference(rows: int, steps: int, warmup: int):
     from vq_b200 import synth
     from vq_b200.seeding import LbgSeeder
     oracle.build()
+    oracle.use_all_host_threads()
     x = synth.uniform01(rows, DIM, DATA_SEED)
     times = []
     for it in range(warmup + steps):
@@ -223,6 +224,8 @@ def run_ours(args):
         f, e, pq, out = one_step(x_dev, True)
         fit_s.append(max_over_ranks(f))
         enc_s.append(max_over_ranks(e))
+        if os.environ.get("VQB_BENCH_DEBUG"):
+            print(f"[rank {rank}] fit {f * 1e3:.3f} ms encode {e * 1e3:.3f} ms", file=sys.stderr, flush=True)
     launches = ctx.launch_count() - launches0
     kernels = ctx.timing_report()
     ctx.timing(False)
@@ -274,7 +277,7 @@ def run_ours(args):
     dominant = max(kernels, key=lambda kname: kernels[kname]["ms"]) if kernels else None
     roofline = roof("assign_train", TRAIN_BYTES_PER_VEC)
     cb_rows = 32768
-    cpu = None if args.kernels_only else cpu_reference(cb_rows, 1, 0)
+    cpu = None if (args.kernels_only or world > 1) else cpu_reference(cb_rows, 1, 0)  # rank 0 at N=1 only
     e2e_step = sum(e2e_s) / len(e2e_s) if e2e_s else float("nan")
     line = {
         "metric": METRIC_NAME, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),

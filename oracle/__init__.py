@@ -83,6 +83,8 @@ def lib():
         L.vqo_mse_f16.restype = C.c_double
         L.vqo_mse_f16.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t]
         L.vqo_num_threads.restype = C.c_int
+        L.vqo_set_num_threads.restype = None
+        L.vqo_set_num_threads.argtypes = [C.c_int]
         _lib = L
     return _lib
 
@@ -102,6 +104,13 @@ def _ptr(a: np.ndarray):
 
 def num_threads() -> int:
     return int(lib().vqo_num_threads())
+
+
+def use_all_host_threads() -> int:
+    """Undo a launcher's OMP_NUM_THREADS=1 (torchrun sets it): one thread per CPU this process may run on."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().vqo_set_num_threads(int(n))
+    return num_threads()
 
 
 def f32_to_f16_bits(x) -> np.ndarray:

@@ -61,6 +61,16 @@ static int fail(int code, const char *msg)
     return code;
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; the CPU baseline wants all host threads. */
+void vqo_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int vqo_num_threads(void)
 {
 #ifdef _OPENMP

@@ -26,8 +26,8 @@ def main():
     x_flt = synth.uniform01(n, dim, 5)
     begin, end = shard_bounds(n, rank, world)
     res = {}
-    for name, x in (("int", x_int), ("flt", x_flt)):
-        pq = vq.ProductQuantizer.fit(torch.from_numpy(x[begin:end]).cuda(), m, k, 6, vq.Distance.Euclidean, 9, ctx=ctx,
+    for name, x, iters in (("int", x_int, 6), ("flt", x_flt, 1)):
+        pq = vq.ProductQuantizer.fit(torch.from_numpy(x[begin:end]).cuda(), m, k, iters, vq.Distance.Euclidean, 9, ctx=ctx,
                                      accumulate=vq.ACCUM_FAST)
         res[f"cb_{name}"] = pq.codebooks
         res[f"it_{name}"] = pq.iterations

@@ -1,6 +1,9 @@
 // assign_launch.cu -- picks and launches the nearest-centroid kernels (assign_reg.cuh, assign_generic.cuh).
 #include <algorithm>
 
+#include <cstdlib>
+
+#include "assign_filter.cuh"
 #include "assign_generic.cuh"
 #include "assign_reg.cuh"
 #include "cuda_device.hpp"
@@ -14,10 +17,42 @@ template <typename K> void set_smem(K kernel, size_t bytes)
     VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
 }
 
+// VQB_EXACT_SCAN=1 forces the plain exact scan (for A/B comparisons); results are identical either way.
+bool use_filter()
+{
+    static const bool off = [] {
+        const char *e = std::getenv("VQB_EXACT_SCAN");
+        return e && *e && *e != '0';
+    }();
+    return !off;
+}
+
+template <int SD, int V, int METRIC, typename CodeT, bool TRAIN, bool FILTER>
+void launch_reg_t(CudaDevice &dev, const AssignParams &p, size_t smem);
+
 template <int SD, int V, int METRIC, typename CodeT, bool TRAIN>
 void launch_reg_t(CudaDevice &dev, const AssignParams &p, size_t smem)
 {
-    auto kernel = assign_reg_kernel<SD, V, METRIC, CodeT, TRAIN>;
+    if ((METRIC == M_SQ || METRIC == M_EUCLID) && use_filter())
+        launch_reg_t<SD, V, (METRIC == M_EUCLID ? M_EUCLID : M_SQ), CodeT, TRAIN, true>(dev, p, smem);
+    else
+        launch_reg_t<SD, V, METRIC, CodeT, TRAIN, false>(dev, p, smem);
+}
+
+template <int SD, int V, int METRIC, typename CodeT, bool TRAIN, bool FILTER> struct KernelPick {
+    static auto get() { return assign_reg_kernel<SD, V, METRIC, CodeT, TRAIN>; }
+};
+template <int SD, int V, typename CodeT, bool TRAIN> struct KernelPick<SD, V, M_SQ, CodeT, TRAIN, true> {
+    static auto get() { return assign_filter_kernel<SD, V, M_SQ, CodeT, TRAIN>; }
+};
+template <int SD, int V, typename CodeT, bool TRAIN> struct KernelPick<SD, V, M_EUCLID, CodeT, TRAIN, true> {
+    static auto get() { return assign_filter_kernel<SD, V, M_EUCLID, CodeT, TRAIN>; }
+};
+
+template <int SD, int V, int METRIC, typename CodeT, bool TRAIN, bool FILTER>
+void launch_reg_t(CudaDevice &dev, const AssignParams &p, size_t smem)
+{
+    auto kernel = KernelPick<SD, V, METRIC, CodeT, TRAIN, FILTER>::get();
     set_smem(kernel, smem);
     const int threads = 512;
     int occ = 1;
@@ -66,7 +101,8 @@ bool launch_assign_reg(CudaDevice &dev, const AssignParams &p_in, int metric, bo
     if (!(met == M_SQ || met == M_EUCLID || met == M_COSINE || met == M_MANHATTAN)) return false;
     AssignParams p = p_in;
     // subspaces per CTA: a power of two dividing the 16 warps, as many as fit in shared memory
-    const size_t per_sub = (size_t)p.k * p.sd * sizeof(float) + (met == M_COSINE ? (size_t)p.k * sizeof(float) : 0);
+    // codebook + one float per centroid (cosine: norm; Euclidean filter: half squared norm) + one float per subspace
+    const size_t per_sub = (size_t)p.k * p.sd * sizeof(float) + (met == M_MANHATTAN ? 0 : (size_t)p.k * sizeof(float)) + sizeof(float);
     const size_t budget = dev.smem_limit() - 1024;
     int g = 16;
     while (g > 1 && (g / 2 >= p.m || (size_t)g * per_sub > budget)) g /= 2;

@@ -92,6 +92,51 @@ __device__ __forceinline__ float reg_dist(const float (&x)[SD], const float (&c)
     }
 }
 
+// Writes the outcome for one (row, subspace): the new assignment while training (noting whether it moved), or
+// the code / f16 / f32 image of the chosen centroid while encoding (src/pq.rs:176-180).
+template <int SD, typename CodeT, bool TRAIN>
+__device__ __forceinline__ void store_result(const AssignParams &P, unsigned long long row, int s, int idx, const float *cbs, bool &moved)
+{
+    const int dim = P.m * SD;
+    if (TRAIN) {
+        CodeT *cp = reinterpret_cast<CodeT *>(P.codes) + row * P.m + s;
+        const CodeT nc = (CodeT)idx;
+        if (*cp != nc) moved = true;
+        *cp = nc;
+    } else {
+        if (P.out_codes) P.out_codes[row * P.m + s] = (uint32_t)idx;
+        const float *cw = cbs + (size_t)idx * SD;
+        if (P.out_f16) {
+            uint16_t *o = P.out_f16 + row * dim + (size_t)s * SD;
+            if (P.out_vec && SD % 8 == 0) {
+#pragma unroll
+                for (int i = 0; i < SD / 8; ++i) {
+                    float4 a = reinterpret_cast<const float4 *>(cw)[2 * i], b = reinterpret_cast<const float4 *>(cw)[2 * i + 1];
+                    uint4 pk;
+                    pk.x = f32_to_f16_bits(a.x) | ((uint32_t)f32_to_f16_bits(a.y) << 16);
+                    pk.y = f32_to_f16_bits(a.z) | ((uint32_t)f32_to_f16_bits(a.w) << 16);
+                    pk.z = f32_to_f16_bits(b.x) | ((uint32_t)f32_to_f16_bits(b.y) << 16);
+                    pk.w = f32_to_f16_bits(b.z) | ((uint32_t)f32_to_f16_bits(b.w) << 16);
+                    reinterpret_cast<uint4 *>(o)[i] = pk;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < SD; ++i) o[i] = f32_to_f16_bits(cw[i]);
+            }
+        }
+        if (P.out_f32) {
+            float *o = P.out_f32 + row * dim + (size_t)s * SD;
+            if (P.out_vec && SD % 4 == 0) {
+#pragma unroll
+                for (int i = 0; i < SD / 4; ++i) reinterpret_cast<float4 *>(o)[i] = reinterpret_cast<const float4 *>(cw)[i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < SD; ++i) o[i] = cw[i];
+            }
+        }
+    }
+}
+
 template <int SD, int V, int METRIC, typename CodeT, bool TRAIN>
 __global__ void __launch_bounds__(512, 1) assign_reg_kernel(const AssignParams P)
 {
@@ -124,7 +169,6 @@ __global__ void __launch_bounds__(512, 1) assign_reg_kernel(const AssignParams P
     const float *cns = cnorm + (size_t)s_local * k;
     const unsigned long long rows_per_block = 32ull * V;
     const unsigned long long n_blocks = (P.n + rows_per_block - 1) / rows_per_block;
-    const int dim = P.m * SD;
     bool moved = false;
 
     for (unsigned long long blk = (unsigned long long)blockIdx.x * rbw + (warp / G); blk < n_blocks;
@@ -202,44 +246,7 @@ __global__ void __launch_bounds__(512, 1) assign_reg_kernel(const AssignParams P
 #pragma unroll
         for (int v = 0; v < V; ++v) {
             unsigned long long row = row0 + 32ull * v;
-            if (row >= P.n) continue;
-            if (TRAIN) {
-                CodeT *cp = reinterpret_cast<CodeT *>(P.codes) + row * P.m + s;
-                const CodeT nc = (CodeT)idx[v];
-                if (*cp != nc) moved = true;
-                *cp = nc;
-            } else {
-                if (P.out_codes) P.out_codes[row * P.m + s] = (uint32_t)idx[v];
-                const float *cw = cbs + (size_t)idx[v] * SD;
-                if (P.out_f16) {
-                    uint16_t *o = P.out_f16 + row * dim + (size_t)s * SD;
-                    if (P.out_vec && SD % 8 == 0) {
-#pragma unroll
-                        for (int i = 0; i < SD / 8; ++i) {
-                            float4 a = reinterpret_cast<const float4 *>(cw)[2 * i], b = reinterpret_cast<const float4 *>(cw)[2 * i + 1];
-                            uint4 pk;
-                            pk.x = f32_to_f16_bits(a.x) | ((uint32_t)f32_to_f16_bits(a.y) << 16);
-                            pk.y = f32_to_f16_bits(a.z) | ((uint32_t)f32_to_f16_bits(a.w) << 16);
-                            pk.z = f32_to_f16_bits(b.x) | ((uint32_t)f32_to_f16_bits(b.y) << 16);
-                            pk.w = f32_to_f16_bits(b.z) | ((uint32_t)f32_to_f16_bits(b.w) << 16);
-                            reinterpret_cast<uint4 *>(o)[i] = pk;
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < SD; ++i) o[i] = f32_to_f16_bits(cw[i]);
-                    }
-                }
-                if (P.out_f32) {
-                    float *o = P.out_f32 + row * dim + (size_t)s * SD;
-                    if (P.out_vec && SD % 4 == 0) {
-#pragma unroll
-                        for (int i = 0; i < SD / 4; ++i) reinterpret_cast<float4 *>(o)[i] = reinterpret_cast<const float4 *>(cw)[i];
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < SD; ++i) o[i] = cw[i];
-                    }
-                }
-            }
+            if (row < P.n) store_result<SD, CodeT, TRAIN>(P, row, s, idx[v], cbs, moved);
         }
     }
     if (TRAIN) {
