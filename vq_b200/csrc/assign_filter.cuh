@@ -26,16 +26,67 @@ namespace vqb {
 
 #define VQB_FILTER_COEF 3.814697265625e-06f /* 64 * 2^-24 */
 
-template <int SD> __device__ __forceinline__ float fma_score(const float (&x)[SD], const float (&c)[SD], float hn)
+// Packed pair of f32 in one 64-bit register (sm_100 issues one FFMA2 for two FMAs).
+typedef unsigned long long f32x2;
+
+__device__ __forceinline__ f32x2 pack2(float lo, float hi)
 {
-    // two interleaved chains (even / odd dimensions) so that consecutive FFMAs are independent
-    float a0 = hn, a1 = 0.0f;
+    f32x2 r;
+    asm("mov.b64 %0, {%1,%2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c)
+{
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+__device__ __forceinline__ float hsum2(f32x2 v)
+{
+    float lo, hi;
+    asm("mov.b64 {%0,%1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+    return lo + hi;
+}
+
+__device__ __forceinline__ float min3f(float a, float b, float c)
+{
+    float r;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+// S = hn - x.c with the dimensions split into (even, odd) lanes of packed FMAs; nx holds (-x[2t], -x[2t+1]),
+// c the centroid's packed pairs, h0 = (hn, 0).  The same instruction sequence is used by the scan and by the
+// re-check, so a given (row, centroid) always yields the same bits.
+template <int SD> __device__ __forceinline__ float fma_score(const f32x2 (&nx)[SD / 2], const f32x2 (&c)[SD / 2], f32x2 h0)
+{
+    f32x2 acc = h0;
 #pragma unroll
-    for (int i = 0; i < SD; i += 2) {
-        a0 = fmaf(-x[i], c[i], a0);
-        a1 = fmaf(-x[i + 1], c[i + 1], a1);
+    for (int t = 0; t < SD / 2; ++t) acc = fma2(nx[t], c[t], acc);
+    return hsum2(acc);
+}
+
+template <int SD> __device__ __forceinline__ void load_centroid2(f32x2 (&c)[SD / 2], const float *p)
+{
+    if (SD % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < SD / 4; ++i) {
+            const ulonglong2 q = reinterpret_cast<const ulonglong2 *>(p)[i];
+            c[2 * i] = q.x;
+            c[2 * i + 1] = q.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < SD / 2; ++i) c[i] = reinterpret_cast<const unsigned long long *>(p)[i];
     }
-    return a0 + a1;
+}
+
+template <int SD> __device__ __forceinline__ void unpack_centroid(float (&c)[SD], const f32x2 (&c2)[SD / 2])
+{
+#pragma unroll
+    for (int t = 0; t < SD / 2; ++t) asm("mov.b64 {%0,%1}, %2;" : "=f"(c[2 * t]), "=f"(c[2 * t + 1]) : "l"(c2[t]));
 }
 
 template <int SD, int V, int METRIC, typename CodeT, bool TRAIN>
@@ -103,32 +154,56 @@ __global__ void __launch_bounds__(512, 1) assign_filter_kernel(const AssignParam
             }
         }
 
+        f32x2 nx[V][SD / 2];
+#pragma unroll
+        for (int v = 0; v < V; ++v)
+#pragma unroll
+            for (int t = 0; t < SD / 2; ++t) nx[v][t] = pack2(-x[v][2 * t], -x[v][2 * t + 1]);
+
         float best[V], second[V];
         int idx[V];
         bool force[V]; // centroid 0 not comparable (NaN score): the reference's scan depends on it, so re-examine
         {
-            float c[SD];
-            load_centroid<SD>(c, cbs);
-            const float h = hns[0];
+            f32x2 c[SD / 2];
+            load_centroid2<SD>(c, cbs);
+            const f32x2 h0 = pack2(hns[0], 0.0f);
 #pragma unroll
             for (int v = 0; v < V; ++v) {
-                const float s0 = fma_score<SD>(x[v], c, h);
+                const float s0 = fma_score<SD>(nx[v], c, h0);
                 force[v] = !(s0 == s0);
                 best[v] = VQB_INF;
                 second[v] = VQB_INF;
                 idx[v] = 0;
             }
         }
-#pragma unroll 2
-        for (int j = 0; j < k; ++j) {
-            float c[SD];
-            load_centroid<SD>(c, cbs + (size_t)j * SD);
-            const float h = hns[j];
+        // two centroids per step: lo/hi of the pair, then one update of (best, second, idx)
+        int j = 0;
+        for (; j + 2 <= k; j += 2) {
+            f32x2 ca[SD / 2], cb2[SD / 2];
+            load_centroid2<SD>(ca, cbs + (size_t)j * SD);
+            load_centroid2<SD>(cb2, cbs + (size_t)(j + 1) * SD);
+            const f32x2 ha = pack2(hns[j], 0.0f), hb = pack2(hns[j + 1], 0.0f);
 #pragma unroll
             for (int v = 0; v < V; ++v) {
-                const float sc = fma_score<SD>(x[v], c, h);
+                const float sa = fma_score<SD>(nx[v], ca, ha);
+                const float sb = fma_score<SD>(nx[v], cb2, hb);
+                const float lo = fminf(sa, sb), hi = fmaxf(sa, sb);
+                const int jlo = (sb < sa) ? j + 1 : j; // equal scores keep the lower index
+                const bool lt = lo < best[v];
+                second[v] = min3f(second[v], fmaxf(best[v], lo), hi); // second smallest of {best, second, lo, hi}
+                best[v] = fminf(best[v], lo);
+                idx[v] = lt ? jlo : idx[v];
+            }
+        }
+        for (; j < k; ++j) {
+            f32x2 c[SD / 2];
+            load_centroid2<SD>(c, cbs + (size_t)j * SD);
+            const f32x2 h0 = pack2(hns[j], 0.0f);
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                const float sc = fma_score<SD>(nx[v], c, h0);
                 const bool lt = sc < best[v];
-                second[v] = fmaxf(best[v], fminf(second[v], sc)); // second smallest of {best, second, sc}
+                second[v] = fmaxf(best[v], fminf(second[v], sc));
                 best[v] = fminf(best[v], sc);
                 idx[v] = lt ? j : idx[v];
             }
@@ -146,20 +221,22 @@ __global__ void __launch_bounds__(512, 1) assign_filter_kernel(const AssignParam
             if (force[v] || !(second[v] > limit)) { // also taken when anything is NaN or infinite
                 float bd = VQB_INF;
                 int bi = -1;
-                for (int j = 0; j < k; ++j) {
-                    float c[SD];
-                    load_centroid<SD>(c, cbs + (size_t)j * SD);
-                    const float sc = fma_score<SD>(x[v], c, hns[j]);
+                for (int jj = 0; jj < k; ++jj) {
+                    f32x2 c2[SD / 2];
+                    load_centroid2<SD>(c2, cbs + (size_t)jj * SD);
+                    const float sc = fma_score<SD>(nx[v], c2, pack2(hns[jj], 0.0f));
                     if (!(sc > limit)) { // candidate (or not comparable): exact distance, reference order
+                        float c[SD];
+                        unpack_centroid<SD>(c, c2);
                         float d = reg_dist<SD, M_SQ>(x[v], c, 0.0f, 0.0f, 0.0f);
                         if (METRIC == M_EUCLID) d = __fsqrt_rn(d);
-                        if (j == 0) { // the reference's scan starts here, whatever the value (even NaN)
+                        if (jj == 0) { // the reference's scan starts here, whatever the value (even NaN)
                             bd = d;
                             bi = 0;
                         } else {
                             // if centroid 0 was skipped it is provably farther than the winner, so starting the
                             // strict-'<' scan from +inf at the first candidate gives the same answer
-                            argmin_update(d, j, bd, bi);
+                            argmin_update(d, jj, bd, bi);
                         }
                     }
                 }
