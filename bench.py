@@ -301,8 +301,117 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_secondary(args):
+    """Other BASELINE.json configurations on one GPU (measurement aid; the headline line is the default workload).
+    sq / bq: 10,000,000 x 128 values in [-1,1), SQ [0,1] x 256 levels, BQ threshold 0.
+    rvq: 1,000,000 x 128 Gaussian mixture (64 components, sigma 0.05), 8 stages, k=256, 10 iterations, Euclidean.
+    opq: 1,000,000 x 128 correlated rows, m=16, k=256, 10 outer x 5 LBG iterations."""
+    import torch
+
+    import vq_b200 as vq
+    from vq_b200 import synth
+
+    torch.cuda.set_device(0)
+    ctx = vq.Context(0)
+    stream = torch.cuda.current_stream()
+    ctx.use_stream(stream.cuda_stream)
+    peak, peak_kind = measured_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    w = args.workload
+    rows = args.rows or (10_000_000 if w in ("sq", "bq") else 1_000_000)
+
+    def timed(fn):
+        flush.fill_(1)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        out = fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 1e3, out
+
+    sampler = ClockSampler(0)
+    extra = {}
+    if w in ("sq", "bq"):
+        g = torch.Generator(device="cuda")
+        g.manual_seed(1)
+        x = torch.empty((rows, DIM), device="cuda", dtype=torch.float32)
+        x.uniform_(-1.0, 1.0, generator=g)
+        q = vq.ScalarQuantizer.fit(0.0, 1.0, 256, ctx=ctx) if w == "sq" else vq.BinaryQuantizer.fit(0.0, 0, 1, ctx=ctx)
+        step = lambda: q.quantize(x)  # noqa: E731
+        kname, bytes_per_vec, cfg = f"{w}_quantize", 5 * DIM, f"{w}_10m_x128"
+        host = synth.uniform(1 << 20, DIM, 1, -1.0, 1.0)
+        import oracle
+        oracle.use_all_host_threads()
+        t0 = time.perf_counter()
+        for _ in range(3):
+            (oracle.sq_quantize(0.0, 1.0, 256, q.step, host) if w == "sq" else oracle.bq_quantize(0.0, 0, 1, host))
+        cpu = {"value": 3 * host.shape[0] / (time.perf_counter() - t0) / 1e6, "unit": UNIT, "cores": oracle.num_threads(),
+               "kind": "port", "sample": f"{host.shape[0]} rows x 128, 3 passes"}
+        xp = torch.empty((min(rows, 2_000_000), DIM), dtype=torch.float32, pin_memory=True)
+        xp.copy_(x[: xp.shape[0]])
+        e2e_fn = lambda: q.quantize(xp.numpy())  # noqa: E731
+        e2e_rows, h2d, d2h = xp.shape[0], xp.numel() * 4, xp.numel()
+    else:
+        if w == "rvq":
+            xh = synth.gaussian_mixture(rows, DIM, 11)
+            fit = lambda xx: vq.ResidualQuantizer.fit(xx, 8, K, ITERS, 0.01, vq.Distance.Euclidean, FIT_SEED, ctx=ctx)  # noqa: E731
+            kname, bytes_per_vec, cfg = "assign_train", 512, "rvq_1m_x128_8stages_k256_10iters_fit_plus_encode"
+        else:
+            xh = synth.correlated(rows, DIM, 3)
+            fit = lambda xx: vq.OptimizedProductQuantizer.fit(xx, M, K, 5, 10, vq.Distance.Euclidean, FIT_SEED, ctx=ctx)  # noqa: E731
+            kname, bytes_per_vec, cfg = "assign_train", TRAIN_BYTES_PER_VEC, "opq_1m_x128_m16_k256_10outer_x_5iters_fit_plus_encode"
+        x = torch.from_numpy(xh).cuda()
+
+        def step():
+            t_fit, qz = timed(lambda: fit(x))
+            t_enc, out = timed(lambda: qz.quantize(x))
+            extra["train_s"], extra["encode_s"] = t_fit, t_enc
+            return out
+        cpu, e2e_fn, e2e_rows, h2d, d2h = None, None, 0, 0, 0
+
+    for _ in range(max(1, min(3, args.warmup)) if w in ("rvq", "opq") else max(3, args.warmup)):
+        step()
+    sampler.start()
+    ctx.timing(True)
+    ctx.timing_report()
+    l0 = ctx.launch_count()
+    times = []
+    for _ in range(args.steps):
+        if w in ("sq", "bq"):
+            t, _o = timed(step)
+        else:
+            step()
+            t = extra["train_s"] + extra["encode_s"]
+        times.append(t)
+    launches = ctx.launch_count() - l0
+    kernels = ctx.timing_report()
+    ctx.timing(False)
+    clocks = sampler.stop()
+    step_s = sum(times) / len(times)
+    e2e = None
+    if e2e_fn is not None:
+        ts = [timed(e2e_fn)[0] for _ in range(4)][1:]
+        e2e = {"value": e2e_rows / (sum(ts) / len(ts)) / 1e6, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "rows": e2e_rows}
+    kk = kernels.get(kname)
+    roofline = None
+    if kk and kk["launches"]:
+        avg = kk["ms"] / kk["launches"] / 1e3
+        ach = bytes_per_vec * rows / avg / 1e9
+        roofline = {"bound": "hbm", "kernel": kname, "achieved": ach, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                    "frac": ach / peak, "traffic": None, "launches": kk["launches"], "avg_ms": avg * 1e3}
+    line = {"metric": f"{w}_throughput", "value": rows / step_s / 1e6, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": cfg, "rows": rows, "dim": DIM, "l2": "256 MiB flush write before every timed call"},
+            "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, **extra}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="pq", choices=["pq", "sq", "bq", "rvq", "opq"],
+                    help="pq (default) is the headline benchmark; the others measure the remaining configurations on one GPU")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -311,7 +420,9 @@ def main():
                     help="skip the end-to-end and CPU-baseline legs (for profiler captures; not a valid bench line)")
     ap.add_argument("--rows", type=int, default=0, help="override the row count (default: 1,000,000; reference arm: 32768-row sample)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload != "pq":
+        run_secondary(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
