@@ -116,6 +116,13 @@ int vqb_comm_destroy(vqb_ctx *ctx);
 int vqb_distance_rows(vqb_ctx *ctx, int metric, double p, const float *a, size_t da, const float *b,
                       size_t db, size_t n, float *out);
 
+/* Diagnostic for the tensor-core path used by full-width k-means (residual quantizer): the raw tcgen05 TF32 dot
+ * products x_r . c_j (dots_out: n x 256, columns >= k are 0; may be NULL) and shortlist statistics
+ * stats_out[3] = {rows, shortlisted candidates, rows that needed a full exact scan}.  Requires 32 <= dim <= 128,
+ * dim % 32 == 0, 2 <= k <= 256.  No counterpart in the reference. */
+int vqb_dense_dots(vqb_ctx *ctx, const float *x, size_t n, size_t dim, const float *codebook, size_t k,
+                   float *dots_out, unsigned long long *stats_out);
+
 /* ---- lbg_quantize (src/utils.rs:32-109) on `n` rows of width d:
  * init_idx = k row indices, centroids_out = k x d (host or device). ------- */
 int vqb_lbg_fit(vqb_ctx *ctx, const float *x, size_t n, size_t d, size_t k, size_t max_iters,

@@ -298,6 +298,21 @@ int vqb_distance_rows(vqb_ctx *ctx, int metric, double p, const float *a, size_t
     });
 }
 
+int vqb_dense_dots(vqb_ctx *ctx, const float *x, size_t n, size_t dim, const float *codebook, size_t k, float *dots_out,
+                   unsigned long long *stats_out)
+{
+    if (!ctx) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "ctx is NULL");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (!x || !codebook || !stats_out || n == 0) throw Error(VQB_ERR_BAD_ARGUMENT, "NULL or empty argument");
+        CudaDevice &dev = *ctx->dev;
+        In ix(dev, x, sizeof(float) * n * dim), ic(dev, codebook, sizeof(float) * k * dim);
+        Out od(dev, dots_out, sizeof(float) * n * 256);
+        dev.dense_debug(ix.as<float>(), n, dim, ic.as<float>(), k, od.as<float>(), stats_out);
+        od.finish();
+    });
+}
+
 int vqb_lbg_fit(vqb_ctx *ctx, const float *x, size_t n, size_t d, size_t k, size_t max_iters, const uint64_t *init_idx,
                 vqb_draw_fn draw, void *user, int flags, float *centroids_out, size_t *iterations_out)
 {

@@ -61,6 +61,13 @@ class Device {
     // (bit patterns are exchanged with a max-reduce over zero-filled slots, so -0.0 and NaN payloads survive).
     virtual void patch_centroids(const Shape &sh, const float *x, uint64_t row_begin, const RowPatch *patches,
                                  size_t n_patches, float *centroids, Comm *comm) = 0;
+    // Called once per lbg_fit before the first assignment: `x` stays unchanged until the next call, so the device
+    // may precompute per-row data (the tensor-core path keeps row norms).  Default: nothing.
+    virtual void prepare_rows(const Shape &sh, const float *x)
+    {
+        (void)sh;
+        (void)x;
+    }
     // Nearest centroid under squared Euclidean (src/utils.rs:59-73); codes are read as the previous
     // assignment and overwritten; changed[s] becomes non-zero if any row of subspace s moved (76-80).
     // Subspaces with active[s] == 0 are left untouched.

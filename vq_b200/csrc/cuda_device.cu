@@ -6,8 +6,11 @@
 #include <algorithm>
 #include <vector>
 
+#include <cstdlib>
+
 #include "assign_generic.cuh"
 #include "assign_reg.cuh"
+#include "dense_tc.hpp"
 #include "kernels_common.cuh"
 
 namespace vqb {
@@ -31,6 +34,10 @@ CudaDevice::CudaDevice(int device) : device_(device)
     smem_limit_ = prop.sharedMemPerBlockOptin;
     VQB_CUDA_CHECK(cudaStreamCreateWithFlags(&own_stream_, cudaStreamNonBlocking));
     stream_ = own_stream_;
+    {
+        const char *e = std::getenv("VQB_NO_TENSOR"); // VQB_NO_TENSOR=1: CUDA-core kernels only (A/B comparisons)
+        tensor_enabled_ = !(e && *e && *e != '0');
+    }
     cudaMemPool_t pool;
     if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
         unsigned long long keep = ~0ull; // keep freed blocks cached; repeated fits reuse them
@@ -43,6 +50,11 @@ CudaDevice::~CudaDevice()
     if (own_stream_) {
         cudaSetDevice(device_);
         cudaStreamSynchronize(own_stream_);
+        cudaFree(rownorm_);
+        cudaFree(hn_scratch_);
+        cudaFree(cand_);
+        cudaFree(tc_stats_);
+        cudaFree(tc_error_);
         cudaStreamDestroy(own_stream_);
     }
 }
@@ -139,6 +151,69 @@ void CudaDevice::download(void *dst, const void *src, size_t bytes)
     if (!bytes) return;
     VQB_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, stream_));
     VQB_CUDA_CHECK(cudaStreamSynchronize(stream_));
+    check_tc_error();
+}
+
+// ------------------------------------------------------------------------------------------------
+// tensor-core path plumbing (kernels in dense_tc.cu / resolve.cu)
+// ------------------------------------------------------------------------------------------------
+void CudaDevice::ensure_tc_buffers(size_t n)
+{
+    if (!hn_scratch_) {
+        VQB_CUDA_CHECK(cudaMalloc(&hn_scratch_, 260 * sizeof(float)));
+        VQB_CUDA_CHECK(cudaMalloc(&tc_stats_, 3 * sizeof(unsigned long long)));
+        VQB_CUDA_CHECK(cudaMalloc(&tc_error_, sizeof(int)));
+        VQB_CUDA_CHECK(cudaMemsetAsync(tc_stats_, 0, 3 * sizeof(unsigned long long), stream_));
+        VQB_CUDA_CHECK(cudaMemsetAsync(tc_error_, 0, sizeof(int), stream_));
+    }
+    if (n > rows_cap_) {
+        VQB_CUDA_CHECK(cudaStreamSynchronize(stream_));
+        cudaFree(rownorm_);
+        cudaFree(cand_);
+        rownorm_ = nullptr;
+        cand_ = nullptr;
+        rows_cap_ = 0;
+        VQB_CUDA_CHECK(cudaMalloc(&rownorm_, n * sizeof(float)));
+        VQB_CUDA_CHECK(cudaMalloc(&cand_, n * DENSE_MASK_WORDS * sizeof(uint32_t)));
+        rows_cap_ = n;
+    }
+}
+
+// Called at host synchronisation points: a tensor-core kernel whose bounded wait expired leaves a code here.
+void CudaDevice::check_tc_error()
+{
+    if (!tc_error_) return;
+    int code = 0;
+    VQB_CUDA_CHECK(cudaMemcpyAsync(&code, tc_error_, sizeof(int), cudaMemcpyDeviceToHost, stream_));
+    VQB_CUDA_CHECK(cudaStreamSynchronize(stream_));
+    if (code != 0) {
+        cudaMemsetAsync(tc_error_, 0, sizeof(int), stream_);
+        throw Error(100, "tensor-core kernel gave up waiting (stage " + std::to_string(code) + "); set VQB_NO_TENSOR=1 to use the CUDA-core path");
+    }
+}
+
+void CudaDevice::prepare_rows(const Shape &sh, const float *x)
+{
+    prepared_x_ = nullptr;
+    if (!tensor_enabled_ || sh.m != 1 || sh.ld != sh.sd || sh.n_local == 0) return;
+    if (!dense_tc_applicable(sh.n_local, sh.sd, sh.k, M_SQ, x)) return;
+    ensure_tc_buffers(sh.n_local);
+    dense_row_norms(*this, x, sh.n_local, sh.sd, rownorm_);
+    prepared_x_ = x;
+    prepared_n_ = sh.n_local;
+    prepared_dim_ = sh.sd;
+}
+
+void CudaDevice::dense_debug(const float *x, size_t n, size_t dim, const float *codebook, size_t k, float *dots,
+                             unsigned long long *stats3)
+{
+    if (!dense_tc_applicable(n, dim, k, M_SQ, x)) throw Error(103, "shape not covered by the tensor-core path");
+    ensure_tc_buffers(n);
+    VQB_CUDA_CHECK(cudaMemsetAsync(tc_stats_, 0, 3 * sizeof(unsigned long long), stream_));
+    dense_row_norms(*this, x, n, dim, rownorm_);
+    dense_shortlist(*this, x, n, dim, codebook, k, rownorm_, hn_scratch_, cand_, tc_stats_, tc_error_, dots);
+    download(stats3, tc_stats_, 3 * sizeof(unsigned long long));
+    prepared_x_ = nullptr;
 }
 
 void CudaDevice::copy(void *dst, const void *src, size_t bytes)
@@ -223,6 +298,23 @@ void CudaDevice::assign_train(const Shape &sh, const float *x, const float *cent
                               const uint32_t *active, uint32_t *changed)
 {
     if (sh.n_local == 0) return;
+    if (prepared_x_ == x && prepared_n_ == sh.n_local && prepared_dim_ == sh.sd && sh.m == 1 &&
+        dense_tc_applicable(sh.n_local, sh.sd, sh.k, M_SQ, x)) {
+        // full-width k-means step: tensor-core shortlist, then the exact decision among the candidates
+        dense_shortlist(*this, x, sh.n_local, sh.sd, centroids, sh.k, rownorm_, hn_scratch_, cand_, nullptr, tc_error_, nullptr);
+        ResolveParams r = {};
+        r.x = x;
+        r.n = sh.n_local;
+        r.dim = (int)sh.sd;
+        r.k = (int)sh.k;
+        r.codebook = centroids;
+        r.cand = cand_;
+        r.euclid = 0;
+        r.codes = codes;
+        r.changed = changed;
+        launch_resolve(*this, r, R_TRAIN, code_bytes(sh.k));
+        return;
+    }
     AssignParams p = {};
     p.x = x;
     p.n = sh.n_local;
@@ -289,6 +381,24 @@ void CudaDevice::rvq_update(float *res, size_t n, size_t dim, const float *centr
                             double *norm_sum)
 {
     if (n == 0) return;
+    if (tensor_enabled_ && prepared_x_ == res && prepared_n_ == n && prepared_dim_ == dim && dense_tc_applicable(n, dim, k, metric, res)) {
+        // the rows have not changed since the stage's k-means announced them, so their norms are still valid
+        dense_shortlist(*this, res, n, dim, centroids, k, rownorm_, hn_scratch_, cand_, nullptr, tc_error_, nullptr);
+        ResolveParams r = {};
+        r.x = res;
+        r.res = res;
+        r.n = n;
+        r.dim = (int)dim;
+        r.k = (int)k;
+        r.codebook = centroids;
+        r.cand = cand_;
+        r.euclid = (metric == M_EUCLID);
+        r.norm_sum = norm_sum;
+        launch_resolve(*this, r, R_RVQ_UPDATE, 4);
+        prepared_x_ = nullptr; // the residuals changed
+        return;
+    }
+    prepared_x_ = nullptr;
     GenericParams g = {};
     g.x = res;
     g.res = res;
@@ -303,11 +413,63 @@ void CudaDevice::rvq_update(float *res, size_t n, size_t dim, const float *centr
     launch_assign_generic(*this, g, metric, G_RVQ_UPDATE, 4);
 }
 
+__global__ void f32_to_f16_kernel(const float *in, unsigned long long n, uint16_t *out)
+{
+    for (unsigned long long i = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; i < n; i += (unsigned long long)gridDim.x * blockDim.x)
+        out[i] = f32_to_f16_bits(in[i]);
+}
+
+void CudaDevice::f32_to_f16_rows(const float *in, size_t n, uint16_t *out)
+{
+    if (n == 0) return;
+    KernelScope ks(*this, "f32_to_f16");
+    f32_to_f16_kernel<<<blocks_for(n, 256, (size_t)sm_count_ * 16), 256, 0, stream_>>>(in, n, out);
+    VQB_CUDA_CHECK(cudaGetLastError());
+    count_launch();
+}
+
 void CudaDevice::rvq_quantize(const float *x, size_t n, size_t dim, const float *codebooks, size_t stages, size_t k,
                               float epsilon, int metric, double pm, uint16_t *out_f16, uint32_t *out_codes)
 {
     if (n == 0) return;
     if (out_codes) VQB_CUDA_CHECK(cudaMemsetAsync(out_codes, 0xFF, sizeof(uint32_t) * n * stages, stream_));
+    if (tensor_enabled_ && dense_tc_applicable(n, dim, k, metric, x)) {
+        // stage by stage: norms of the current residuals, tensor-core shortlist, exact resolve that subtracts the chosen
+        // centroid, adds it to the running sum and retires rows whose residual norm fell below epsilon
+        ensure_tc_buffers(n);
+        prepared_x_ = nullptr;
+        float *res = (float *)alloc(sizeof(float) * n * dim), *qsum = (float *)alloc(sizeof(float) * n * dim);
+        uint8_t *done = (uint8_t *)alloc(n);
+        copy(res, x, sizeof(float) * n * dim);
+        zero(qsum, sizeof(float) * n * dim);
+        zero(done, n);
+        for (size_t st = 0; st < stages; ++st) {
+            const float *cb = codebooks + st * k * dim;
+            dense_row_norms(*this, res, n, dim, rownorm_);
+            dense_shortlist(*this, res, n, dim, cb, k, rownorm_, hn_scratch_, cand_, nullptr, tc_error_, nullptr);
+            ResolveParams r = {};
+            r.x = res;
+            r.res = res;
+            r.n = n;
+            r.dim = (int)dim;
+            r.k = (int)k;
+            r.codebook = cb;
+            r.cand = cand_;
+            r.euclid = (metric == M_EUCLID);
+            r.qsum = qsum;
+            r.done = done;
+            r.out_codes = out_codes;
+            r.stage = (int)st;
+            r.stages = (int)stages;
+            r.epsilon = epsilon;
+            launch_resolve(*this, r, R_RVQ_STAGE, 4);
+        }
+        if (out_f16) f32_to_f16_rows(qsum, n * dim, out_f16);
+        release(done);
+        release(qsum);
+        release(res);
+        return;
+    }
     GenericParams g = {};
     g.x = x;
     g.n = n;
@@ -702,13 +864,29 @@ void CudaDevice::distance_rows(int metric, double p, const float *a, const float
 // 16 values per thread step (4 x 128-bit loads, one 128-bit store), 5 bytes of traffic per value.
 // ------------------------------------------------------------------------------------------------
 struct SqOp {
-    float mn, mx, step;
+    float mn, mx, step, inv; // inv = fl(1 / step)
     unsigned last;
-    __device__ __forceinline__ unsigned operator()(float v) const
+    // The reference's arithmetic, operation by operation (src/sq.rs:117-127).
+    __device__ __forceinline__ unsigned exact(float v) const
     {
         const float c = (v < mn) ? mn : ((v > mx) ? mx : v); // NaN passes through both tests
         const float q = __fdiv_rn(__fsub_rn(c, mn), step);
         const unsigned idx = __float2uint_rz(roundf(q)); // round half away from zero; saturating, NaN -> 0 (`as usize`)
+        return min(idx, last);
+    }
+    // Same result with a multiply instead of the IEEE division: q' = (c - min) * inv differs from the reference's
+    // quotient q by at most 3.1 * 2^-24 * q (< 2e-4 for q < 1024), so whenever q' is farther than 2e-4 from a
+    // half-integer, round(q) is the integer nearest to q'; that integer is read from the mantissa after adding
+    // 1.5 * 2^23.  Values close to a half-integer (or out of range) take the exact path.  NaN clamps to min here and
+    // yields level 0, which is also what the reference's saturating cast gives.
+    __device__ __forceinline__ unsigned operator()(float v) const
+    {
+        const float c = fminf(fmaxf(v, mn), mx);
+        const float qp = __fmul_rn(__fsub_rn(c, mn), inv);
+        const float t = __fadd_rn(qp, 12582912.0f);
+        const float diff = __fsub_rn(qp, __fsub_rn(t, 12582912.0f));
+        if (!(fabsf(diff) < 0.4998f && qp < 1024.0f)) return exact(v);
+        const unsigned idx = (unsigned)(__float_as_int(t) - 0x4B400000);
         return min(idx, last);
     }
 };
@@ -765,7 +943,7 @@ template <typename Op> static void launch_elementwise(CudaDevice &dev, const cha
 
 void CudaDevice::sq_quantize(float mn, float mx, size_t levels, float step, const float *x, size_t n, uint8_t *out)
 {
-    SqOp op{mn, mx, step, (unsigned)(levels - 1)};
+    SqOp op{mn, mx, step, 1.0f / step, (unsigned)(levels - 1)};
     launch_elementwise(*this, "sq_quantize", x, n, op, out);
 }
 

@@ -32,6 +32,7 @@ class CudaDevice : public Device {
     void zero(void *dst, size_t bytes) override;
     size_t code_bytes(size_t k) const override { return k <= 256 ? 1 : (k <= 65536 ? 2 : 4); }
 
+    void prepare_rows(const Shape &sh, const float *x) override;
     void patch_centroids(const Shape &sh, const float *x, uint64_t row_begin, const RowPatch *patches, size_t n_patches,
                          float *centroids, Comm *comm) override;
     void assign_train(const Shape &sh, const float *x, const float *centroids, void *codes, const uint32_t *active,
@@ -50,6 +51,7 @@ class CudaDevice : public Device {
     // Not part of the training loops:
     void rvq_quantize(const float *x, size_t n, size_t dim, const float *codebooks, size_t stages, size_t k,
                       float epsilon, int metric, double p, uint16_t *out_f16, uint32_t *out_codes);
+    void f32_to_f16_rows(const float *in, size_t n, uint16_t *out);
     void distance_rows(int metric, double p, const float *a, const float *b, size_t d, size_t n, float *out);
     void sq_quantize(float mn, float mx, size_t levels, float step, const float *x, size_t n, uint8_t *out);
     void bq_quantize(float threshold, uint8_t low, uint8_t high, const float *x, size_t n, uint8_t *out);
@@ -71,6 +73,8 @@ class CudaDevice : public Device {
     void timing_end();
     // {"name": {"launches": L, "ms": T}, ...}; clears the record.
     std::string timing_report();
+    // Diagnostic: raw tensor-core dot products (n x 256) and shortlist statistics {rows, candidates, full scans}.
+    void dense_debug(const float *x, size_t n, size_t dim, const float *codebook, size_t k, float *dots, unsigned long long *stats3);
     // True when p points to device memory usable by kernels on this GPU.
     bool is_device_pointer(const void *p) const;
 
@@ -80,6 +84,17 @@ class CudaDevice : public Device {
     size_t smem_limit_ = 0;
     cudaStream_t own_stream_ = nullptr, stream_ = nullptr;
     std::atomic<uint64_t> launches_{0};
+    // tensor-core path state (dense_tc.cu): row norms of the rows announced by prepare_rows, shortlist scratch
+    bool tensor_enabled_ = true;
+    const float *prepared_x_ = nullptr;
+    size_t prepared_n_ = 0, prepared_dim_ = 0;
+    float *rownorm_ = nullptr, *hn_scratch_ = nullptr;
+    uint32_t *cand_ = nullptr;
+    size_t rows_cap_ = 0;
+    unsigned long long *tc_stats_ = nullptr;
+    int *tc_error_ = nullptr;
+    void ensure_tc_buffers(size_t n);
+    void check_tc_error();
     bool timing_ = false;
     struct Span {
         const char *name;

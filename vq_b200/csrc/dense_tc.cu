@@ -1,0 +1,503 @@
+// dense_tc.cu -- full-width nearest-centroid search on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
+//
+// The residual quantizer's k-means and encode (src/rvq.rs:107,111-128,186-202) compare every row with every centroid
+// over the full dimension: a dense n x k x dim contraction.  This file ranks centroids with
+//        S_j = |c_j|^2/2 - x.c_j          (|x - c_j|^2 = |x|^2 + 2 S_j)
+// where the dot products come from tcgen05.mma (TF32 inputs, f32 accumulation in tensor memory), keeps for every row
+// the SHORTLIST of centroids whose S lies within a proven error bound of the smallest one, and hands the shortlist
+// to resolve kernels (resolve.cuh) that evaluate only those candidates with the reference's exact f32 arithmetic in
+// ascending index order.  The final choice is therefore the reference's; the tensor cores only prune.
+//
+// Bound.  TF32 keeps 10 mantissa bits of each operand (the low 13 bits of the f32 container are ignored), so
+//   |dot_tc - x.c| <= (2^-10 + 2^-10 + 2^-20 + 2 K 2^-24) sum|x_i c_ji| <= 2.1e-3 |x| |c_j|        (K <= 128)
+// and with the reference's own chain error (<= (dim + 2) 2^-24 relative on the distance) the winner w satisfies
+//   S_w <= S_min + 2 E + 1.05 (dim + 6) 2^-24 (|x|^2 + 2 S_min + 2 E),   E = 2.1e-3 |x| max_j |c_j|.
+// Everything not finite falls out of the comparisons and marks the row for a full exact scan.
+//
+// Kernel layout (one CTA per SM, persistent over 128-row tiles):
+//   warp 0      TMA producer: the codebook once (k x dim, resident in shared memory), then row tiles in 128-byte
+//               column chunks through a 3-stage ring (cp.async.bulk.tensor, 128B swizzle, no multicast)
+//   warp 1      allocates tensor memory and issues tcgen05.mma M128 x N256 x K8 (kind::tf32); two 256-column
+//               accumulators so the next tile's MMAs overlap this tile's epilogue
+//   warps 2..5  epilogue: tcgen05.ld the 128 x 256 dots, one row per lane; pass 1 finds the two smallest S, pass 2
+//               collects the shortlist
+// Every wait is bounded; on expiry the kernel records an error code, stops issuing work and frees its tensor memory.
+#include <cuda.h>
+
+#include <algorithm>
+#include <mutex>
+
+#include "cuda_device.hpp"
+#include "dense_tc.hpp"
+
+namespace vqb {
+
+namespace {
+
+constexpr int BM = 128;          // rows per tile (= TMEM lanes)
+constexpr int BN = 256;          // centroids per tile (= accumulator columns)
+constexpr int CHUNK = 32;        // f32 per 128-byte swizzle row
+constexpr int NSTAGE = 5;        // row-tile ring depth (stages of 128 rows x 128 bytes)
+constexpr int MAX_KCHUNKS = 4;   // dim <= 128
+constexpr uint32_t X_STAGE_BYTES = BM * 128;
+constexpr uint32_t C_CHUNK_BYTES = BN * 128;
+constexpr uint32_t SPIN_LIMIT = 4000000u;
+
+struct alignas(8) Barriers {
+    unsigned long long full[NSTAGE], empty[NSTAGE], cfull, tfull[2], tempty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(void *bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(void *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(void *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+// Bounded wait: returns false (and raises the CTA's abort flag) if the phase does not complete in time.
+__device__ __forceinline__ bool mbar_wait(void *bar, uint32_t parity, volatile int *abort_flag, int *err, int code)
+{
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done)
+                     : "r"(addr), "r"(parity)
+                     : "memory");
+        if (done) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicCAS(err, 0, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1, void *bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+                 "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+
+// K-major operand tile with 128-byte rows and the 128B swizzle: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);  // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                   // leading byte offset (unused for swizzled K-major): 1
+    d |= (uint64_t)(1024u >> 4) << 32;        // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                   // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;                   // layout type: 128-byte swizzle
+    return d;
+}
+
+// kind::tf32, f32 accumulate, A and B K-major, M = 128, N = 256
+constexpr uint32_t IDESC_TF32_M128_N256 = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
+                 "l"(adesc), "l"(bdesc), "r"(IDESC_TF32_M128_N256), "r"(accumulate), "r"(0u)
+                 : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(void *bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// 32 consecutive accumulator columns of this lane's row; the registers are valid after tmem_wait().
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, "
+                 "%19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+                   "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+                   "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+struct ShortlistParams {
+    unsigned long long n;
+    int dim, k, kchunks;
+    const float *hn;      // [256] |c_j|^2 / 2, +inf beyond k
+    const float *cmax;    // [1]   max_j |c_j|
+    const float *xnorm2;  // [n]   |x|^2 per row
+    uint32_t *cand;       // [n][8] bit j set = centroid j may be the reference's choice (all k bits set: examine all)
+    unsigned long long *stats; // [0] rows, [1] candidates, [2] rows needing a full scan   (may be null)
+    float *debug_dots;    // [n][256] raw tensor-core dot products (may be null)
+    int *error;           // device error word, 0 = ok
+};
+
+__global__ void __launch_bounds__(192, 1) dense_shortlist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_c,
+                                                                const ShortlistParams P)
+{
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *base = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char *c_smem = base;                                            // kchunks x 32 KiB
+    unsigned char *x_smem = base + (size_t)MAX_KCHUNKS * C_CHUNK_BYTES;       // NSTAGE x 16 KiB
+    float *hn_s = reinterpret_cast<float *>(x_smem + (size_t)NSTAGE * X_STAGE_BYTES); // 256 floats
+    Barriers *bars = reinterpret_cast<Barriers *>(hn_s + BN);
+    volatile int *abort_flag = &bars->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned long long n_tiles = (P.n + BM - 1) / BM;
+    const int kchunks = P.kchunks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NSTAGE; ++s) {
+            mbar_init(&bars->full[s], 1);
+            mbar_init(&bars->empty[s], 1);
+        }
+        mbar_init(&bars->cfull, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&bars->tfull[b], 1);
+            mbar_init(&bars->tempty[b], 4);
+        }
+        bars->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    for (int t = threadIdx.x; t < BN; t += blockDim.x) hn_s[t] = P.hn[t];
+    if (warp == 1) { // tensor memory: 512 columns = two 128 x 256 f32 accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = bars->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_expect_tx(&bars->cfull, (uint32_t)kchunks * C_CHUNK_BYTES);
+            for (int kc = 0; kc < kchunks; ++kc) tma_load_2d(c_smem + (size_t)kc * C_CHUNK_BYTES, &map_c, kc * CHUNK, 0, &bars->cfull);
+            uint32_t it = 0;
+            for (unsigned long long tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x) {
+                for (int kc = 0; kc < kchunks; ++kc, ++it) {
+                    const int s = it % NSTAGE;
+                    const uint32_t use = it / NSTAGE;
+                    if (!mbar_wait(&bars->empty[s], (use & 1u) ^ 1u, abort_flag, P.error, 1)) break;
+                    mbar_expect_tx(&bars->full[s], X_STAGE_BYTES);
+                    tma_load_2d(x_smem + (size_t)s * X_STAGE_BYTES, &map_x, kc * CHUNK, (int)(tile * BM), &bars->full[s]);
+                }
+            }
+            if (*abort_flag) {
+                // gave up: let the copies already in flight land before the CTA retires (bounded; a phase the MMA warp
+                // already consumed simply runs this short wait out)
+                for (uint32_t back = 0; back < NSTAGE && back < it; ++back) {
+                    const uint32_t j = it - 1 - back;
+                    const uint32_t addr = smem_u32(&bars->full[j % NSTAGE]);
+                    for (uint32_t spin = 0; spin < 20000u; ++spin) {
+                        uint32_t done;
+                        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                                     : "=r"(done)
+                                     : "r"(addr), "r"((j / NSTAGE) & 1u)
+                                     : "memory");
+                        if (done) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            bool ok = mbar_wait(&bars->cfull, 0, abort_flag, P.error, 2);
+            uint32_t it = 0, local = 0;
+            for (unsigned long long tile = blockIdx.x; ok && tile < n_tiles && !*abort_flag; tile += gridDim.x, ++local) {
+                const uint32_t b = local & 1u, buse = local >> 1;
+                if (!mbar_wait(&bars->tempty[b], (buse & 1u) ^ 1u, abort_flag, P.error, 3)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d_tmem = tmem_base + b * BN;
+                for (int kc = 0; kc < kchunks; ++kc, ++it) {
+                    const int s = it % NSTAGE;
+                    const uint32_t use = it / NSTAGE;
+                    if (!mbar_wait(&bars->full[s], use & 1u, abort_flag, P.error, 4)) {
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t adesc = smem_desc_sw128(smem_u32(x_smem + (size_t)s * X_STAGE_BYTES));
+                    const uint64_t bdesc = smem_desc_sw128(smem_u32(c_smem + (size_t)kc * C_CHUNK_BYTES));
+#pragma unroll
+                    for (int k8 = 0; k8 < CHUNK / 8; ++k8) // 8 f32 = 32 bytes = 2 descriptor units per MMA step
+                        umma_tf32(d_tmem, adesc + (uint64_t)(2 * k8), bdesc + (uint64_t)(2 * k8), (kc | k8) ? 1u : 0u);
+                    umma_commit(&bars->empty[s]); // the stage is free once these MMAs have read it
+                }
+                if (ok) umma_commit(&bars->tfull[b]);
+            }
+        }
+    } else {
+        // ------------------------------------------------ epilogue: one row per lane
+        const int q = warp & 3; // TMEM lane quadrant this warp may read
+        const float cmax = *P.cmax;
+        unsigned long long cand_total = 0, full_scans = 0, rows_done = 0;
+        uint32_t local = 0;
+        for (unsigned long long tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x, ++local) {
+            const uint32_t b = local & 1u, buse = local >> 1;
+            if (!mbar_wait(&bars->tfull[b], buse & 1u, abort_flag, P.error, 5)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const unsigned long long row = tile * BM + 32ull * q + lane;
+            const bool valid = row < P.n;
+            const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + b * BN;
+            const float xn2 = valid ? P.xnorm2[row] : 0.0f;
+
+            // pass 1: the two smallest scores; the next 32 columns are in flight while these are processed
+            float best = VQB_DENSE_INF, second = VQB_DENSE_INF;
+            bool col0_nan = false;
+            uint32_t ra[32], rb[32];
+            tmem_ld32_issue(taddr, ra);
+            tmem_wait();
+#pragma unroll 1
+            for (int cb = 0; cb < BN / 32; cb += 2) {
+                tmem_ld32_issue(taddr + (cb + 1) * 32, rb);
+                if (P.debug_dots && valid) {
+#pragma unroll
+                    for (int t = 0; t < 32; ++t) P.debug_dots[row * BN + cb * 32 + t] = __uint_as_float(ra[t]);
+                }
+                if (cb == 0) {
+                    const float s0 = hn_s[0] - __uint_as_float(ra[0]);
+                    col0_nan = !(s0 == s0);
+                }
+#pragma unroll
+                for (int t = 0; t < 32; ++t) {
+                    const float sc = hn_s[cb * 32 + t] - __uint_as_float(ra[t]);
+                    second = fmaxf(best, fminf(second, sc));
+                    best = fminf(best, sc);
+                }
+                tmem_wait();
+                if (cb + 2 < BN / 32) tmem_ld32_issue(taddr + (cb + 2) * 32, ra);
+                if (P.debug_dots && valid) {
+#pragma unroll
+                    for (int t = 0; t < 32; ++t) P.debug_dots[row * BN + (cb + 1) * 32 + t] = __uint_as_float(rb[t]);
+                }
+#pragma unroll
+                for (int t = 0; t < 32; ++t) {
+                    const float sc = hn_s[(cb + 1) * 32 + t] - __uint_as_float(rb[t]);
+                    second = fmaxf(best, fminf(second, sc));
+                    best = fminf(best, sc);
+                }
+                tmem_wait();
+            }
+            // E = 2.1e-3 |x| cmax (+ the rounding of the stored half norms);
+            // limit = best + 2E + 1.05 (dim + 6) u (|x|^2 + 2 best + 2E) + rounding slack of the comparison itself
+            const float e2 = 2.0f * 2.1e-3f * sqrtf(xn2) * cmax + 8e-6f * cmax * cmax;
+            const float d_a = fmaxf(xn2 + 2.0f * best + e2, 0.0f);
+            const float limit = best + e2 + 1.05f * (float)(P.dim + 6) * 5.9604645e-8f * d_a + 2.4e-7f * (fabsf(best) + e2) + 1e-36f;
+            // a row the comparisons cannot rank (NaN / infinity somewhere, or centroid 0 not comparable, on which the
+            // reference's scan depends) is handed over with every centroid marked
+            const bool scan_all = col0_nan || !(second >= best) || !(limit == limit) || !(fabsf(limit) < VQB_DENSE_INF);
+
+            // pass 2: one bit per centroid, set when S_j <= limit.  The sign of (limit - S_j) is shifted into the word,
+            // so the bits arrive in reverse order and inverted.
+            uint32_t words[BN / 32];
+            tmem_ld32_issue(taddr, ra);
+            tmem_wait();
+#pragma unroll
+            for (int cb = 0; cb < BN / 32; cb += 2) {
+                tmem_ld32_issue(taddr + (cb + 1) * 32, rb);
+                uint32_t m = 0;
+#pragma unroll
+                for (int t = 0; t < 32; ++t) {
+                    const float sc = hn_s[cb * 32 + t] - __uint_as_float(ra[t]);
+                    m = __funnelshift_l(__float_as_uint(limit - sc), m, 1);
+                }
+                words[cb] = ~__brev(m);
+                tmem_wait();
+                if (cb + 2 < BN / 32) tmem_ld32_issue(taddr + (cb + 2) * 32, ra);
+                m = 0;
+#pragma unroll
+                for (int t = 0; t < 32; ++t) {
+                    const float sc = hn_s[(cb + 1) * 32 + t] - __uint_as_float(rb[t]);
+                    m = __funnelshift_l(__float_as_uint(limit - sc), m, 1);
+                }
+                words[cb + 1] = ~__brev(m);
+                tmem_wait();
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->tempty[b]); // this accumulator may be overwritten
+            if (valid) {
+                int cnt = 0;
+#pragma unroll
+                for (int wd = 0; wd < BN / 32; ++wd) {
+                    const int lo = wd * 32;
+                    const uint32_t in_range = (P.k >= lo + 32) ? 0xFFFFFFFFu : ((P.k > lo) ? ((1u << (P.k - lo)) - 1u) : 0u);
+                    words[wd] = scan_all ? in_range : (words[wd] & in_range);
+                    cnt += __popc(words[wd]);
+                }
+                if (scan_all) ++full_scans;
+                else cand_total += cnt;
+                ++rows_done;
+                uint4 *o = reinterpret_cast<uint4 *>(P.cand + row * 8);
+                o[0] = make_uint4(words[0], words[1], words[2], words[3]);
+                o[1] = make_uint4(words[4], words[5], words[6], words[7]);
+            }
+        }
+        if (P.stats) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                cand_total += __shfl_xor_sync(0xffffffffu, cand_total, o);
+                full_scans += __shfl_xor_sync(0xffffffffu, full_scans, o);
+                rows_done += __shfl_xor_sync(0xffffffffu, rows_done, o);
+            }
+            if (lane == 0) {
+                atomicAdd(P.stats + 0, rows_done);
+                atomicAdd(P.stats + 1, cand_total);
+                atomicAdd(P.stats + 2, full_scans);
+            }
+        }
+    }
+
+    // ---------------------------------------------------- teardown
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// |c_j|^2 / 2 for j < k (+inf beyond) and max_j |c_j|
+__global__ void codebook_norms_kernel(const float *c, int k, int dim, float *hn, float *cmax)
+{
+    __shared__ float smax[256];
+    const int j = threadIdx.x;
+    float a = 0.0f;
+    if (j < k)
+        for (int i = 0; i < dim; ++i) a = fmaf(c[(size_t)j * dim + i], c[(size_t)j * dim + i], a);
+    hn[j] = (j < k) ? 0.5f * a : VQB_DENSE_INF;
+    smax[j] = (j < k) ? sqrtf(a) : 0.0f;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if (j < o) smax[j] = fmaxf(smax[j], smax[j + o]);
+        __syncthreads();
+    }
+    if (j == 0) *cmax = smax[0] * 1.000001f;
+}
+
+__global__ void row_norms_kernel(const float *x, unsigned long long n, int dim, float *out)
+{
+    const int lane = threadIdx.x & 31;
+    const unsigned long long warps = (unsigned long long)gridDim.x * (blockDim.x >> 5);
+    for (unsigned long long row = blockIdx.x * (unsigned long long)(blockDim.x >> 5) + (threadIdx.x >> 5); row < n; row += warps) {
+        float a = 0.0f;
+        for (int i = lane; i < dim; i += 32) {
+            const float v = x[row * dim + i];
+            a = fmaf(v, v, a);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (lane == 0) out[row] = a * 1.00001f; // an upper bound is what the filter needs
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    if (!fn) throw Error(100, "cuTensorMapEncodeTiled is not available from this driver");
+    return fn;
+}
+
+CUtensorMap make_map(const float *ptr, unsigned long long rows, int dim, int box_rows)
+{
+    CUtensorMap m;
+    cuuint64_t dims[2] = {(cuuint64_t)dim, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)dim * sizeof(float)};
+    cuuint32_t box[2] = {(cuuint32_t)CHUNK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(ptr), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw Error(100, "cuTensorMapEncodeTiled failed (" + std::to_string((int)r) + ")");
+    return m;
+}
+
+} // namespace
+
+bool dense_tc_applicable(size_t n, size_t dim, size_t k, int metric, const float *x)
+{
+    (void)n;
+    return (metric == 0 || metric == 1) && dim >= 32 && dim <= 128 && dim % 32 == 0 && k >= 2 && k <= 256 &&
+           (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+}
+
+size_t dense_tc_smem_bytes()
+{
+    return 1024 + (size_t)MAX_KCHUNKS * C_CHUNK_BYTES + (size_t)NSTAGE * X_STAGE_BYTES + BN * sizeof(float) + sizeof(Barriers) + 64;
+}
+
+void dense_row_norms(CudaDevice &dev, const float *x, size_t n, size_t dim, float *out)
+{
+    if (n == 0) return;
+    KernelScope ks(dev, "row_norms");
+    const unsigned grid = (unsigned)std::max<size_t>(1, std::min<size_t>((n + 7) / 8, (size_t)dev.sm_count() * 8));
+    row_norms_kernel<<<grid, 256, 0, dev.stream()>>>(x, n, (int)dim, out);
+    VQB_CUDA_CHECK(cudaGetLastError());
+    dev.count_launch();
+}
+
+void dense_shortlist(CudaDevice &dev, const float *x, size_t n, size_t dim, const float *codebook, size_t k, const float *xnorm2,
+                     float *hn_scratch /* 257 floats */, uint32_t *cand, unsigned long long *stats, int *error_word, float *debug_dots)
+{
+    if (n == 0) return;
+    {
+        KernelScope ks(dev, "codebook_norms");
+        codebook_norms_kernel<<<1, 256, 0, dev.stream()>>>(codebook, (int)k, (int)dim, hn_scratch, hn_scratch + 256);
+        VQB_CUDA_CHECK(cudaGetLastError());
+        dev.count_launch();
+    }
+    const CUtensorMap mx = make_map(x, n, (int)dim, BM);
+    const CUtensorMap mc = make_map(codebook, k, (int)dim, BN);
+    ShortlistParams p;
+    p.n = n;
+    p.dim = (int)dim;
+    p.k = (int)k;
+    p.kchunks = (int)(dim / CHUNK);
+    p.hn = hn_scratch;
+    p.cmax = hn_scratch + 256;
+    p.xnorm2 = xnorm2;
+    p.cand = cand;
+    p.stats = stats;
+    p.debug_dots = debug_dots;
+    p.error = error_word;
+    const size_t smem = dense_tc_smem_bytes();
+    VQB_CUDA_CHECK(cudaFuncSetAttribute(dense_shortlist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const unsigned long long tiles = (n + BM - 1) / BM;
+    const unsigned grid = (unsigned)std::min<unsigned long long>(tiles, (unsigned long long)dev.sm_count());
+    KernelScope ks(dev, "dense_shortlist");
+    dense_shortlist_kernel<<<grid, 192, smem, dev.stream()>>>(mx, mc, p);
+    VQB_CUDA_CHECK(cudaGetLastError());
+    dev.count_launch();
+}
+
+} // namespace vqb

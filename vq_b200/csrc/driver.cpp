@@ -86,6 +86,7 @@ void lbg_fit(Device &dev, Comm *comm, const Shape &sh, const float *x, size_t ma
         for (size_t s = 0; s < m; ++s) iterations[s] = 0;
     if (max_iters == 0) return; // src/utils.rs:57 never runs
 
+    dev.prepare_rows(sh, x);
     const size_t cb = dev.code_bytes(k);
     DevBuf codes(dev, sh.n_local * m * cb);
     dev.zero(codes.p, sh.n_local * m * cb); // src/utils.rs:55: previous assignments start at 0
@@ -211,37 +212,47 @@ bool opq_fit(Device &dev, Comm *comm, const float *x, size_t n_local, size_t dim
 // completion so that U stays orthogonal (V * U^T must be a rotation even for rank-deficient input).
 void jacobi_svd(const double *a, size_t n, double *u, double *s, double *v)
 {
-    std::vector<double> g(a, a + n * n); // g = a * v, columns converge to u * sigma
+    // gt / vt hold the working matrices TRANSPOSED (row p = column p of g = a * v), so that each plane rotation
+    // streams two contiguous rows.
+    std::vector<double> gt(n * n), vt(n * n, 0.0);
     for (size_t i = 0; i < n; ++i)
-        for (size_t j = 0; j < n; ++j) v[i * n + j] = (i == j) ? 1.0 : 0.0;
+        for (size_t j = 0; j < n; ++j) gt[j * n + i] = a[i * n + j];
+    for (size_t i = 0; i < n; ++i) vt[i * n + i] = 1.0;
     const double eps = 1e-15;
     for (int sweep = 0; sweep < 60; ++sweep) {
         bool rotated = false;
         for (size_t p = 0; p + 1 < n; ++p)
             for (size_t q = p + 1; q < n; ++q) {
+                double *gp = &gt[p * n], *gq = &gt[q * n];
                 double alpha = 0, beta = 0, gamma = 0;
                 for (size_t i = 0; i < n; ++i) {
-                    double gp = g[i * n + p], gq = g[i * n + q];
-                    alpha += gp * gp;
-                    beta += gq * gq;
-                    gamma += gp * gq;
+                    alpha += gp[i] * gp[i];
+                    beta += gq[i] * gq[i];
+                    gamma += gp[i] * gq[i];
                 }
                 if (std::fabs(gamma) <= eps * std::sqrt(alpha * beta) || gamma == 0.0) continue;
                 rotated = true;
                 double zeta = (beta - alpha) / (2.0 * gamma);
                 double t = (zeta >= 0 ? 1.0 : -1.0) / (std::fabs(zeta) + std::sqrt(1.0 + zeta * zeta));
                 double c = 1.0 / std::sqrt(1.0 + t * t), sn = c * t;
+                double *vp = &vt[p * n], *vq = &vt[q * n];
                 for (size_t i = 0; i < n; ++i) {
-                    double gp = g[i * n + p], gq = g[i * n + q];
-                    g[i * n + p] = c * gp - sn * gq;
-                    g[i * n + q] = sn * gp + c * gq;
-                    double vp = v[i * n + p], vq = v[i * n + q];
-                    v[i * n + p] = c * vp - sn * vq;
-                    v[i * n + q] = sn * vp + c * vq;
+                    double a0 = gp[i], b0 = gq[i];
+                    gp[i] = c * a0 - sn * b0;
+                    gq[i] = sn * a0 + c * b0;
+                    double a1 = vp[i], b1 = vq[i];
+                    vp[i] = c * a1 - sn * b1;
+                    vq[i] = sn * a1 + c * b1;
                 }
             }
         if (!rotated) break;
     }
+    std::vector<double> g(n * n);
+    for (size_t i = 0; i < n; ++i)
+        for (size_t j = 0; j < n; ++j) {
+            g[i * n + j] = gt[j * n + i];
+            v[i * n + j] = vt[j * n + i];
+        }
     double smax = 0.0;
     for (size_t j = 0; j < n; ++j) {
         double nn = 0;

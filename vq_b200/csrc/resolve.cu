@@ -1,0 +1,234 @@
+// resolve.cu -- exact decision among shortlisted centroids (the second half of the tensor-core path, dense_tc.cu).
+//
+// For every row the shortlist holds, in ascending order, every centroid that can be the reference's choice.  Here each
+// candidate's distance is evaluated with the reference's own f32 arithmetic (src/vector.rs:198-220, src/distances.rs:
+// 130-140) and compared with strict '<', so the outcome equals the reference's full scan; rows marked "scan all" get that
+// full scan.  The epilogue is the caller's: new assignment (training), residual update (src/rvq.rs:127,133-138), or one
+// stage of the residual encoder (src/rvq.rs:186-207).
+#include <algorithm>
+
+#include "cuda_device.hpp"
+#include "dense_tc.hpp"
+#include "kernels_common.cuh"
+
+namespace vqb {
+
+namespace {
+
+#define XS_STRIDE 33
+
+// Reference distance of this lane's row (xcol, stride 33) to up to four centroids at once: four independent serial
+// chains, each in the reference's order over dimensions.
+__device__ __forceinline__ void exact_dist4(const float *xcol, const float *c0, const float *c1, const float *c2, const float *c3,
+                                            int dim, bool euclid, float (&out)[4])
+{
+    float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+    for (int i = 0; i < dim; ++i) {
+        const float xv = xcol[i * XS_STRIDE];
+        const float d0 = __fsub_rn(xv, c0[i]), d1 = __fsub_rn(xv, c1[i]), d2 = __fsub_rn(xv, c2[i]), d3 = __fsub_rn(xv, c3[i]);
+        a0 = __fadd_rn(a0, __fmul_rn(d0, d0));
+        a1 = __fadd_rn(a1, __fmul_rn(d1, d1));
+        a2 = __fadd_rn(a2, __fmul_rn(d2, d2));
+        a3 = __fadd_rn(a3, __fmul_rn(d3, d3));
+    }
+    out[0] = euclid ? __fsqrt_rn(a0) : a0;
+    out[1] = euclid ? __fsqrt_rn(a1) : a1;
+    out[2] = euclid ? __fsqrt_rn(a2) : a2;
+    out[3] = euclid ? __fsqrt_rn(a3) : a3;
+}
+
+// Index of the lowest set bit at or above `from` in a 256-bit mask, or 256.
+__device__ __forceinline__ int next_bit(const uint32_t (&w)[8], int from)
+{
+    for (int wd = from >> 5; wd < 8; ++wd) {
+        uint32_t m = w[wd];
+        if (wd == (from >> 5)) m &= 0xFFFFFFFFu << (from & 31);
+        if (m) return wd * 32 + __ffs(m) - 1;
+    }
+    return 256;
+}
+
+template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) resolve_kernel(const ResolveParams P)
+{
+    extern __shared__ __align__(16) float smem[];
+    const int dim = P.dim, k = P.k, cstride = dim + 1; // odd stride: lanes reading different centroids hit different banks
+    const int W = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float *cpad = smem;                                   // [k][dim + 1]
+    float *xs = smem + (size_t)k * cstride + (size_t)warp * dim * XS_STRIDE; // [dim][33] per warp
+    for (int t = threadIdx.x; t < k * dim; t += blockDim.x) cpad[(t / dim) * cstride + (t % dim)] = P.codebook[t];
+    __syncthreads();
+    const bool euclid = P.euclid != 0;
+    const unsigned long long tiles = (P.n + 31) / 32;
+    bool moved = false;
+    double warp_norm = 0.0;
+
+    for (unsigned long long tile = (unsigned long long)blockIdx.x * W + warp; tile < tiles; tile += (unsigned long long)gridDim.x * W) {
+        const unsigned long long row0 = tile * 32, row = row0 + lane;
+        const bool valid = row < P.n;
+        bool skip = false;
+        if (MODE == R_RVQ_STAGE && valid) skip = P.done[row] != 0;
+        // stage the 32 rows: lanes walk along a row (coalesced), stored dimension-major
+        for (int r = 0; r < 32; ++r) {
+            const unsigned long long rr = row0 + r;
+            for (int i = lane; i < dim; i += 32) xs[i * XS_STRIDE + r] = (rr < P.n) ? P.x[rr * dim + i] : 0.0f;
+        }
+        __syncwarp();
+        const float *xcol = xs + lane;
+        int best = 0;
+        uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        int ncand = 0;
+        if (valid && !skip) {
+            const uint4 lo = reinterpret_cast<const uint4 *>(P.cand + row * 8)[0], hi = reinterpret_cast<const uint4 *>(P.cand + row * 8)[1];
+            w[0] = lo.x, w[1] = lo.y, w[2] = lo.z, w[3] = lo.w, w[4] = hi.x, w[5] = hi.y, w[6] = hi.z, w[7] = hi.w;
+#pragma unroll
+            for (int t = 0; t < 8; ++t) ncand += __popc(w[t]);
+        }
+        // Rows with many candidates (or marked "examine all") are scanned by the whole warp: lane L takes centroids
+        // L, L+32, ... in ascending order, then the warp keeps the smallest distance, lowest index on ties.  A NaN never
+        // wins in the reference unless it sits at centroid 0, where the scan starts.
+        const bool wide = ncand > 12;
+        unsigned wide_rows = __ballot_sync(0xffffffffu, wide);
+        while (wide_rows) {
+            const int r = __ffs(wide_rows) - 1;
+            wide_rows &= wide_rows - 1;
+            const float *xr = xs + r;
+            float bd = VQB_DENSE_INF;
+            int bi = 0x7fffffff;
+            float d0 = 0.0f;
+            for (int j = lane; j < k; j += 32) {
+                const float *c = cpad + (size_t)j * cstride;
+                float acc = 0.0f;
+                for (int i = 0; i < dim; ++i) {
+                    const float d = __fsub_rn(xr[i * XS_STRIDE], c[i]);
+                    acc = __fadd_rn(acc, __fmul_rn(d, d));
+                }
+                const float d = euclid ? __fsqrt_rn(acc) : acc;
+                if (j == 0) d0 = d;
+                if (d < bd) {
+                    bd = d;
+                    bi = j;
+                }
+            }
+            d0 = __shfl_sync(0xffffffffu, d0, 0);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float od = __shfl_xor_sync(0xffffffffu, bd, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (od < bd || (od == bd && oi < bi)) {
+                    bd = od;
+                    bi = oi;
+                }
+            }
+            int res = (bi == 0x7fffffff) ? 0 : bi; // nothing finite below +inf: the reference keeps centroid 0
+            if (!(d0 == d0)) res = 0;               // NaN at centroid 0: nothing ever replaces it (src/utils.rs:62-66)
+            if (bd == VQB_DENSE_INF) res = 0;       // all distances +inf (or NaN): strict '<' never fires
+            if (lane == r) best = res;
+        }
+        if (valid && !skip) {
+            if (!wide) {
+                float bd = VQB_DENSE_INF;
+                int bi = -1;
+                int j = next_bit(w, 0);
+                while (j < k) {
+                    int js[4];
+                    js[0] = j;
+#pragma unroll
+                    for (int t = 1; t < 4; ++t) js[t] = (js[t - 1] < 256) ? next_bit(w, js[t - 1] + 1) : 256;
+                    float d[4];
+                    exact_dist4(xcol, cpad + (size_t)min(js[0], k - 1) * cstride, cpad + (size_t)min(js[1], k - 1) * cstride,
+                                cpad + (size_t)min(js[2], k - 1) * cstride, cpad + (size_t)min(js[3], k - 1) * cstride, dim, euclid, d);
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        if (js[t] >= k) break;
+                        if (js[t] == 0) { // the reference's scan starts at centroid 0 whatever its value
+                            bd = d[t];
+                            bi = 0;
+                        } else {
+                            argmin_update(d[t], js[t], bd, bi); // a skipped centroid 0 is provably farther than the winner
+                        }
+                    }
+                    j = (js[3] < 256) ? next_bit(w, js[3] + 1) : 256;
+                }
+                best = bi < 0 ? 0 : bi;
+            }
+
+            if (MODE == R_TRAIN) {
+                CodeT *cp = reinterpret_cast<CodeT *>(P.codes) + row;
+                const CodeT nc = (CodeT)best;
+                if (*cp != nc) moved = true;
+                *cp = nc;
+            } else {
+                const float *cw = cpad + (size_t)best * cstride;
+                float nsq = 0.0f;
+                for (int i = 0; i < dim; ++i) {
+                    const float r = __fsub_rn(xs[i * XS_STRIDE + lane], cw[i]);
+                    xs[i * XS_STRIDE + lane] = r;
+                    nsq = __fadd_rn(nsq, __fmul_rn(r, r));
+                }
+                const float nrm = __fsqrt_rn(nsq);
+                if (MODE == R_RVQ_UPDATE) warp_norm += (double)nrm;
+                if (MODE == R_RVQ_STAGE) {
+                    if (P.out_codes) P.out_codes[row * (unsigned long long)P.stages + P.stage] = (uint32_t)best;
+                    if (nrm < P.epsilon) P.done[row] = 1;
+                }
+            }
+        }
+        if (MODE != R_TRAIN) {
+            // write the residual tile back; R_RVQ_STAGE also adds the chosen centroid to the running sum
+            const int mybest = (valid && !skip) ? best : -1;
+            __syncwarp();
+            for (int r = 0; r < 32; ++r) {
+                const unsigned long long rr = row0 + r;
+                if (rr >= P.n) break;
+                const int b = __shfl_sync(0xffffffffu, mybest, r);
+                if (b < 0) continue;
+                const float *cw = cpad + (size_t)b * cstride;
+                for (int i = lane; i < dim; i += 32) {
+                    P.res[rr * dim + i] = xs[i * XS_STRIDE + r];
+                    if (MODE == R_RVQ_STAGE) P.qsum[rr * dim + i] = __fadd_rn(P.qsum[rr * dim + i], cw[i]);
+                }
+            }
+        }
+        __syncwarp();
+    }
+    if (MODE == R_TRAIN) {
+        if (__any_sync(0xffffffffu, moved) && lane == 0) atomicOr(P.changed, 1u);
+    }
+    if (MODE == R_RVQ_UPDATE) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) warp_norm += __shfl_xor_sync(0xffffffffu, warp_norm, o);
+        if (lane == 0 && warp_norm != 0.0) atomicAdd(P.norm_sum, warp_norm);
+    }
+}
+
+template <int MODE, typename CodeT> void launch_t(CudaDevice &dev, const ResolveParams &p, const char *name)
+{
+    const int threads = 128;
+    const size_t smem = ((size_t)p.k * (p.dim + 1) + (size_t)(threads / 32) * p.dim * XS_STRIDE) * sizeof(float);
+    auto kernel = resolve_kernel<MODE, CodeT>;
+    VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const unsigned long long tiles = (p.n + 31) / 32;
+    const unsigned grid = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((tiles + 3) / 4, (unsigned long long)dev.sm_count()));
+    KernelScope ks(dev, name);
+    kernel<<<grid, threads, smem, dev.stream()>>>(p);
+    VQB_CUDA_CHECK(cudaGetLastError());
+    dev.count_launch();
+}
+
+} // namespace
+
+void launch_resolve(CudaDevice &dev, const ResolveParams &p, int mode, size_t cb)
+{
+    if (p.n == 0) return;
+    if (mode == R_TRAIN) {
+        if (cb == 1) launch_t<R_TRAIN, uint8_t>(dev, p, "resolve_train");
+        else if (cb == 2) launch_t<R_TRAIN, uint16_t>(dev, p, "resolve_train");
+        else launch_t<R_TRAIN, uint32_t>(dev, p, "resolve_train");
+    } else if (mode == R_RVQ_UPDATE) {
+        launch_t<R_RVQ_UPDATE, uint32_t>(dev, p, "resolve_rvq_update");
+    } else {
+        launch_t<R_RVQ_STAGE, uint32_t>(dev, p, "resolve_rvq_stage");
+    }
+}
+
+} // namespace vqb
