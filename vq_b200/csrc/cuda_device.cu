@@ -546,12 +546,35 @@ __global__ void accum_wide_kernel(const float *x, unsigned long long n, unsigned
     }
     const int lane = threadIdx.x & 31;
     const unsigned long long warps = (unsigned long long)gridDim.x * (blockDim.x >> 5);
-    for (unsigned long long row = blockIdx.x * (unsigned long long)(blockDim.x >> 5) + (threadIdx.x >> 5); row < n; row += warps) {
-        const int code = (int)codes[row * m + s];
-        const float *xp = x + row * ld + (size_t)s * sd;
-        float *dst = (SHARED ? ssum : gsum) + (size_t)code * sd;
-        for (int d = lane; d < sd; d += 32) atomicAdd(dst + d, xp[d]);
-        if (lane == 0) atomicAdd((SHARED ? scnt : gcnt) + code, 1u);
+    // four rows per step so that enough loads are in flight to cover the memory latency
+    constexpr int RB = 4;
+    for (unsigned long long row0 = (blockIdx.x * (unsigned long long)(blockDim.x >> 5) + (threadIdx.x >> 5)) * RB; row0 < n; row0 += warps * RB) {
+        int code[RB];
+#pragma unroll
+        for (int r = 0; r < RB; ++r) code[r] = (row0 + r < n) ? (int)codes[(row0 + r) * m + s] : -1;
+        for (int d0 = 0; d0 < sd; d0 += 128) {
+            float v[RB][4];
+#pragma unroll
+            for (int r = 0; r < RB; ++r)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int d = d0 + e * 32 + lane;
+                    v[r][e] = (code[r] >= 0 && d < sd) ? x[(row0 + r) * ld + (size_t)s * sd + d] : 0.0f;
+                }
+#pragma unroll
+            for (int r = 0; r < RB; ++r) {
+                if (code[r] < 0) continue;
+                float *dst = (SHARED ? ssum : gsum) + (size_t)code[r] * sd;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int d = d0 + e * 32 + lane;
+                    if (d < sd) atomicAdd(dst + d, v[r][e]);
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < RB; ++r)
+            if (lane == 0 && code[r] >= 0) atomicAdd((SHARED ? scnt : gcnt) + code[r], 1u);
     }
     if (SHARED) {
         __syncthreads();

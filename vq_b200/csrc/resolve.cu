@@ -55,7 +55,27 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
     const int W = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float *cpad = smem;                                   // [k][dim + 1]
     float *xs = smem + (size_t)k * cstride + (size_t)warp * dim * XS_STRIDE; // [dim][33] per warp
-    for (int t = threadIdx.x; t < k * dim; t += blockDim.x) cpad[(t / dim) * cstride + (t % dim)] = P.codebook[t];
+    {
+        // codebook -> shared memory, eight 128-bit loads in flight per thread (dim is a multiple of 4 on this path)
+        const int total4 = k * dim / 4, dim4 = dim / 4;
+        const float4 *src = reinterpret_cast<const float4 *>(P.codebook);
+        for (int base = 0; base < total4; base += 8 * (int)blockDim.x) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int t = base + u * (int)blockDim.x + (int)threadIdx.x;
+                v[u] = (t < total4) ? __ldg(src + t) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int t = base + u * (int)blockDim.x + (int)threadIdx.x;
+                if (t < total4) {
+                    float *d = cpad + (size_t)(t / dim4) * cstride + (size_t)(t % dim4) * 4;
+                    d[0] = v[u].x, d[1] = v[u].y, d[2] = v[u].z, d[3] = v[u].w;
+                }
+            }
+        }
+    }
     __syncthreads();
     const bool euclid = P.euclid != 0;
     const unsigned long long tiles = (P.n + 31) / 32;
@@ -68,9 +88,27 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
         bool skip = false;
         if (MODE == R_RVQ_STAGE && valid) skip = P.done[row] != 0;
         // stage the 32 rows: lanes walk along a row (coalesced), stored dimension-major
-        for (int r = 0; r < 32; ++r) {
-            const unsigned long long rr = row0 + r;
-            for (int i = lane; i < dim; i += 32) xs[i * XS_STRIDE + r] = (rr < P.n) ? P.x[rr * dim + i] : 0.0f;
+        // (eight independent 128-bit loads per lane are issued before any is stored, to cover the memory latency)
+        {
+            const int dim4 = dim / 4, total4 = 32 * dim4;
+            for (int base = 0; base < total4; base += 8 * 32) {
+                float4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int idx = base + u * 32 + lane;
+                    const unsigned long long rr = row0 + idx / dim4;
+                    v[u] = (idx < total4 && rr < P.n) ? __ldg(reinterpret_cast<const float4 *>(P.x + rr * dim) + idx % dim4)
+                                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int idx = base + u * 32 + lane;
+                    if (idx < total4) {
+                        float *d = xs + (size_t)(idx % dim4) * 4 * XS_STRIDE + idx / dim4;
+                        d[0] = v[u].x, d[XS_STRIDE] = v[u].y, d[2 * XS_STRIDE] = v[u].z, d[3 * XS_STRIDE] = v[u].w;
+                    }
+                }
+            }
         }
         __syncwarp();
         const float *xcol = xs + lane;
@@ -177,15 +215,38 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
             // write the residual tile back; R_RVQ_STAGE also adds the chosen centroid to the running sum
             const int mybest = (valid && !skip) ? best : -1;
             __syncwarp();
-            for (int r = 0; r < 32; ++r) {
-                const unsigned long long rr = row0 + r;
-                if (rr >= P.n) break;
-                const int b = __shfl_sync(0xffffffffu, mybest, r);
-                if (b < 0) continue;
-                const float *cw = cpad + (size_t)b * cstride;
-                for (int i = lane; i < dim; i += 32) {
-                    P.res[rr * dim + i] = xs[i * XS_STRIDE + r];
-                    if (MODE == R_RVQ_STAGE) P.qsum[rr * dim + i] = __fadd_rn(P.qsum[rr * dim + i], cw[i]);
+            // four rows per step; the running-sum reads of a step are all issued before any is used
+            for (int r0 = 0; r0 < 32; r0 += 4) {
+                int b[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    b[u] = __shfl_sync(0xffffffffu, mybest, r0 + u);
+                    if (row0 + r0 + u >= P.n) b[u] = -1;
+                }
+                for (int i0 = 0; i0 < dim; i0 += 128) {
+                    float q[4][4];
+                    if (MODE == R_RVQ_STAGE) {
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int i = i0 + e * 32 + lane;
+                                q[u][e] = (b[u] >= 0 && i < dim) ? P.qsum[(row0 + r0 + u) * dim + i] : 0.0f;
+                            }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (b[u] < 0) continue;
+                        const unsigned long long rr = row0 + r0 + u;
+                        const float *cw = cpad + (size_t)b[u] * cstride;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int i = i0 + e * 32 + lane;
+                            if (i >= dim) continue;
+                            P.res[rr * dim + i] = xs[i * XS_STRIDE + r0 + u];
+                            if (MODE == R_RVQ_STAGE) P.qsum[rr * dim + i] = __fadd_rn(q[u][e], cw[i]);
+                        }
+                    }
                 }
             }
         }
