@@ -68,3 +68,40 @@ def test_lbg_full_width_with_duplicates_and_specials(oracle):
     cent, it = vq.lbg_quantize(x, 32, 4, 8, init_idx=init, draw=sg.draw, accumulate=vq.ACCUM_ORDERED)
     assert it == it_o
     assert np.array_equal(cent, cent_o, equal_nan=True)
+
+
+def test_pq_tensor_core_kernel_matches_the_default_path(oracle):
+    """The tcgen05 product-quantizer kernel (opt-in with VQB_PQ_TENSOR=1) in a child process: codebooks and codes must be
+    bit-identical to the oracle's, like the default CUDA-core path."""
+    import os
+    import subprocess
+    import sys
+    import tempfile
+    code = r"""
+import sys, numpy as np
+sys.path.insert(0, %r)
+import vq_b200 as vq
+from vq_b200 import synth
+from vq_b200.seeding import LbgSeeder
+x = synth.uniform01(20000, 128, 42)
+s = LbgSeeder(42)
+init = np.stack([s.init_indices(i, 20000, 256) for i in range(16)])
+pq = vq.ProductQuantizer.fit(x, 16, 256, 4, vq.Distance.Euclidean, 42, init_idx=init, draw=s.draw, accumulate=vq.ACCUM_ORDERED)
+out, codes = pq.quantize(x, return_codes=True)
+np.savez(sys.argv[1], cb=pq.codebooks, codes=codes, out=out.view(np.uint16))
+""" % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    from vq_b200 import synth
+    from vq_b200.seeding import LbgSeeder
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "r.npz")
+        res = subprocess.run([sys.executable, "-c", code, path], env=dict(os.environ, VQB_PQ_TENSOR="1"), stdout=subprocess.PIPE,
+                             stderr=subprocess.STDOUT, timeout=600)
+        assert res.returncode == 0, res.stdout.decode()[-2000:]
+        got = np.load(path)
+        x = synth.uniform01(20000, 128, 42)
+        s = LbgSeeder(42)
+        init = np.stack([s.init_indices(i, 20000, 256) for i in range(16)])
+        cb_o, _ = oracle.pq_fit(x, 16, 256, 4, init, s.draw)
+        out_o, codes_o = oracle.pq_quantize(cb_o, x, ka.EUCLID)
+        assert np.array_equal(got["cb"], cb_o)
+        assert np.array_equal(got["codes"], codes_o) and np.array_equal(got["out"], out_o)

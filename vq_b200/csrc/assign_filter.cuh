@@ -50,13 +50,6 @@ __device__ __forceinline__ float hsum2(f32x2 v)
     return lo + hi;
 }
 
-__device__ __forceinline__ float min3f(float a, float b, float c)
-{
-    float r;
-    asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-    return r;
-}
-
 // S = hn - x.c with the dimensions split into (even, odd) lanes of packed FMAs; nx holds (-x[2t], -x[2t+1]),
 // c the centroid's packed pairs, h0 = (hn, 0).  The same instruction sequence is used by the scan and by the
 // re-check, so a given (row, centroid) always yields the same bits.

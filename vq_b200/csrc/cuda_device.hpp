@@ -88,7 +88,8 @@ class CudaDevice : public Device {
     bool tensor_enabled_ = true;
     const float *prepared_x_ = nullptr;
     size_t prepared_n_ = 0, prepared_dim_ = 0;
-    float *rownorm_ = nullptr, *hn_scratch_ = nullptr;
+    float *rownorm_ = nullptr, *hn_scratch_ = nullptr, *pq_scratch_ = nullptr;
+    bool pq_tensor_enabled_ = false;
     uint32_t *cand_ = nullptr;
     size_t rows_cap_ = 0;
     unsigned long long *tc_stats_ = nullptr;

@@ -29,6 +29,8 @@
 
 #include "cuda_device.hpp"
 #include "dense_tc.hpp"
+#include "tma_host.hpp"
+#include "umma.cuh"
 
 namespace vqb {
 
@@ -41,98 +43,12 @@ constexpr int NSTAGE = 5;        // row-tile ring depth (stages of 128 rows x 12
 constexpr int MAX_KCHUNKS = 4;   // dim <= 128
 constexpr uint32_t X_STAGE_BYTES = BM * 128;
 constexpr uint32_t C_CHUNK_BYTES = BN * 128;
-constexpr uint32_t SPIN_LIMIT = 4000000u;
 
 struct alignas(8) Barriers {
     unsigned long long full[NSTAGE], empty[NSTAGE], cfull, tfull[2], tempty[2];
     uint32_t tmem_base;
     int abort_flag;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(void *bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(void *bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ void mbar_expect_tx(void *bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-
-// Bounded wait: returns false (and raises the CTA's abort flag) if the phase does not complete in time.
-__device__ __forceinline__ bool mbar_wait(void *bar, uint32_t parity, volatile int *abort_flag, int *err, int code)
-{
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-                     : "=r"(done)
-                     : "r"(addr), "r"(parity)
-                     : "memory");
-        if (done) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    atomicCAS(err, 0, code);
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1, void *bar)
-{
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
-                 "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-                 : "memory");
-}
-
-// K-major operand tile with 128-byte rows and the 128B swizzle: 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
-{
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);  // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                   // leading byte offset (unused for swizzled K-major): 1
-    d |= (uint64_t)(1024u >> 4) << 32;        // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                   // descriptor version for sm_100
-    d |= (uint64_t)2 << 61;                   // layout type: 128-byte swizzle
-    return d;
-}
-
-// kind::tf32, f32 accumulate, A and B K-major, M = 128, N = 256
-constexpr uint32_t IDESC_TF32_M128_N256 = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate)
-{
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
-                 "l"(adesc), "l"(bdesc), "r"(IDESC_TF32_M128_N256), "r"(accumulate), "r"(0u)
-                 : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(void *bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-// 32 consecutive accumulator columns of this lane's row; the registers are valid after tmem_wait().
-__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32])
-{
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, "
-                 "%19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-                   "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-                   "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr)
-                 : "memory");
-}
-
-__device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 struct ShortlistParams {
     unsigned long long n;
@@ -410,36 +326,9 @@ __global__ void row_norms_kernel(const float *x, unsigned long long n, int dim, 
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn()
-{
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    if (!fn) throw Error(100, "cuTensorMapEncodeTiled is not available from this driver");
-    return fn;
-}
-
 CUtensorMap make_map(const float *ptr, unsigned long long rows, int dim, int box_rows)
 {
-    CUtensorMap m;
-    cuuint64_t dims[2] = {(cuuint64_t)dim, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)dim * sizeof(float)};
-    cuuint32_t box[2] = {(cuuint32_t)CHUNK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(ptr), dims, strides, box, estr,
-                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) throw Error(100, "cuTensorMapEncodeTiled failed (" + std::to_string((int)r) + ")");
-    return m;
+    return make_tensor_map_2d(ptr, (unsigned long long)dim, rows, CHUNK, (unsigned)box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 } // namespace

@@ -81,6 +81,14 @@ __device__ __forceinline__ unsigned short f32_to_f16_bits(float v)
     return __half_as_ushort(__float2half_rn(v)); // IEEE round-to-nearest-even == half::f16::from_f32
 }
 
+// Three-input minimum (one instruction on sm_100); NaN operands are ignored like fminf.
+__device__ __forceinline__ float min3f(float a, float b, float c)
+{
+    float r;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 template <typename CodeT> __device__ __forceinline__ CodeT to_code(int j) { return (CodeT)j; }
 
 } // namespace vqb
