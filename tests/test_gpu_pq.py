@@ -262,3 +262,18 @@ def test_full_size_properties_1m(oracle):
     #     test_fast_accumulation_within_reference_tolerance; here: reconstruction error in the published range
     mse = float(((xt - out.float()) ** 2).mean())
     assert 0.015 < mse < 0.03
+
+
+def test_large_host_batch_goes_through_the_chunked_pipeline(oracle):
+    """Host arrays of >= 131072 rows are encoded in 65536-row chunks with copies and kernels overlapped; the result
+    must not depend on the chunking (row count deliberately not a multiple of the chunk)."""
+    n = 200_003
+    x = synth.uniform01(n, 16, 77)
+    rng = np.random.default_rng(2)
+    cb = rng.uniform(0, 1, (2, 32, 8)).astype(np.float32)
+    pq = vq.ProductQuantizer.from_codebooks(cb, vq.Distance.Euclidean)
+    out, codes = pq.quantize(x, return_codes=True)
+    out_o, codes_o = oracle.pq_quantize(cb, x, ka.EUCLID)
+    assert np.array_equal(codes, codes_o) and np.array_equal(out.view(np.uint16), out_o)
+    only_f16 = pq.quantize(x)
+    assert np.array_equal(only_f16.view(np.uint16), out_o)

@@ -76,3 +76,12 @@ def test_full_size_10m_x_128(oracle):
         sl = x[start:start + (1 << 20)].cpu().numpy()
         assert np.array_equal(sq[start:start + (1 << 20)].cpu().numpy(), oracle.sq_quantize(0.0, 1.0, 256, q.step, sl))
         assert np.array_equal(bq[start:start + (1 << 20)].cpu().numpy(), oracle.bq_quantize(0.0, 0, 1, sl))
+
+
+def test_large_host_arrays_go_through_the_chunked_pipeline(oracle):
+    n = (1 << 24) + 12345  # just over two 8 Mi-value chunks
+    x = synth.uniform(n, 1, 5, -1.5, 1.5).reshape(-1)
+    q = vq.ScalarQuantizer.fit(0.0, 1.0, 256)
+    assert np.array_equal(q.quantize(x), oracle.sq_quantize(0.0, 1.0, 256, q.step, x))
+    b = vq.BinaryQuantizer.fit(0.1, 2, 7)
+    assert np.array_equal(b.quantize(x), oracle.bq_quantize(0.1, 2, 7, x))

@@ -3,6 +3,7 @@
 // Validation follows the reference's order and wording (src/pq.rs:87-102,147-156; src/opq.rs:99-114;
 // src/rvq.rs:96-98; src/sq.rs:51-68; src/bq.rs:47-54; src/exceptions.rs).  Host pointers are staged
 // through device buffers; device pointers are used in place.
+#include <algorithm>
 #include <cstring>
 #include <memory>
 #include <mutex>
@@ -136,6 +137,68 @@ struct Out {
         if (host) dev.release(d);
     }
     template <typename T> T *as() const { return static_cast<T *>(d); }
+};
+
+// Host buffers in, host buffers out: the items are cut into chunks and walked through a two-slot pipeline so that the
+// upload of chunk i+1, the kernels of chunk i and the download of chunk i-1 overlap (PCIe is full duplex).
+//   in_bytes / out_bytes[k]: bytes per item;  run(dev_in, items, dev_out[]) launches the kernels of one chunk on dev.stream().
+struct HostPipeline {
+    static constexpr int MAX_OUT = 2;
+    CudaDevice &dev;
+    size_t chunk_items;
+    HostPipeline(CudaDevice &d, size_t items_per_chunk) : dev(d), chunk_items(items_per_chunk) {}
+
+    template <typename Run>
+    void go(const void *host_in, size_t n_items, size_t in_bytes, void *const host_out[MAX_OUT], const size_t out_bytes[MAX_OUT], Run &&run)
+    {
+        cudaStream_t s_in = dev.aux_stream(0), s_out = dev.aux_stream(1), s_run = dev.stream();
+        void *din[2] = {nullptr, nullptr}, *dout[2][MAX_OUT] = {{nullptr, nullptr}, {nullptr, nullptr}};
+        cudaEvent_t in_done[2], run_done[2], out_done[2], start;
+        for (int b = 0; b < 2; ++b) {
+            din[b] = dev.alloc(chunk_items * in_bytes);
+            for (int k = 0; k < MAX_OUT; ++k)
+                if (host_out[k]) dout[b][k] = dev.alloc(chunk_items * out_bytes[k]);
+            VQB_CUDA_CHECK(cudaEventCreateWithFlags(&in_done[b], cudaEventDisableTiming));
+            VQB_CUDA_CHECK(cudaEventCreateWithFlags(&run_done[b], cudaEventDisableTiming));
+            VQB_CUDA_CHECK(cudaEventCreateWithFlags(&out_done[b], cudaEventDisableTiming));
+        }
+        VQB_CUDA_CHECK(cudaEventCreateWithFlags(&start, cudaEventDisableTiming));
+        VQB_CUDA_CHECK(cudaEventRecord(start, s_run)); // the buffers were allocated in s_run's order
+        VQB_CUDA_CHECK(cudaStreamWaitEvent(s_in, start, 0));
+        VQB_CUDA_CHECK(cudaStreamWaitEvent(s_out, start, 0));
+        size_t c = 0;
+        for (size_t off = 0; off < n_items; off += chunk_items, ++c) {
+            const int b = (int)(c & 1);
+            const size_t items = std::min(chunk_items, n_items - off);
+            if (c >= 2) VQB_CUDA_CHECK(cudaStreamWaitEvent(s_in, run_done[b], 0)); // slot b's input was consumed
+            VQB_CUDA_CHECK(cudaMemcpyAsync(din[b], (const char *)host_in + off * in_bytes, items * in_bytes, cudaMemcpyHostToDevice, s_in));
+            VQB_CUDA_CHECK(cudaEventRecord(in_done[b], s_in));
+            VQB_CUDA_CHECK(cudaStreamWaitEvent(s_run, in_done[b], 0));
+            if (c >= 2) VQB_CUDA_CHECK(cudaStreamWaitEvent(s_run, out_done[b], 0)); // slot b's outputs were downloaded
+            void *outs[MAX_OUT] = {dout[b][0], dout[b][1]};
+            run(din[b], items, outs);
+            VQB_CUDA_CHECK(cudaEventRecord(run_done[b], s_run));
+            VQB_CUDA_CHECK(cudaStreamWaitEvent(s_out, run_done[b], 0));
+            for (int k = 0; k < MAX_OUT; ++k)
+                if (host_out[k])
+                    VQB_CUDA_CHECK(cudaMemcpyAsync((char *)host_out[k] + off * out_bytes[k], dout[b][k], items * out_bytes[k],
+                                                   cudaMemcpyDeviceToHost, s_out));
+            VQB_CUDA_CHECK(cudaEventRecord(out_done[b], s_out));
+        }
+        // everything the caller waits for goes through s_run: it joins the copy streams, then the host waits once
+        for (int b = 0; b < 2; ++b) {
+            if (c > (size_t)b) VQB_CUDA_CHECK(cudaStreamWaitEvent(s_run, out_done[b], 0));
+        }
+        VQB_CUDA_CHECK(cudaStreamSynchronize(s_run));
+        for (int b = 0; b < 2; ++b) {
+            dev.release(din[b]);
+            for (int k = 0; k < MAX_OUT; ++k) dev.release(dout[b][k]);
+            cudaEventDestroy(in_done[b]);
+            cudaEventDestroy(run_done[b]);
+            cudaEventDestroy(out_done[b]);
+        }
+        cudaEventDestroy(start);
+    }
 };
 
 void check_minkowski(int metric, double p)
@@ -432,14 +495,29 @@ int vqb_pq_quantize(vqb_pq *pq, const float *x, size_t n, size_t dim, uint16_t *
         if (n == 0) return;
         if (!x) throw Error(VQB_ERR_BAD_ARGUMENT, "x is NULL");
         CudaDevice &dev = *ctx->dev;
-        In ix(dev, x, sizeof(float) * n * dim);
-        Out of(dev, out_f16, sizeof(uint16_t) * n * dim), oc(dev, codes, sizeof(uint32_t) * n * pq->m);
         Shape sh;
         sh.n_local = n;
         sh.ld = dim;
         sh.m = pq->m;
         sh.sd = pq->sd;
         sh.k = pq->k;
+        const size_t chunk_rows = 1u << 16;
+        const bool all_host = !dev.is_device_pointer(x) && (!out_f16 || !dev.is_device_pointer(out_f16)) &&
+                              (!codes || !dev.is_device_pointer(codes)) && (out_f16 || codes);
+        if (all_host && n >= 2 * chunk_rows) {
+            // large host batch (the loop of src/bin/eval_pq.rs:51-59 in one call): chunked copy / encode / copy pipeline
+            HostPipeline pipe(dev, chunk_rows);
+            void *const outs[2] = {out_f16, codes};
+            const size_t ob[2] = {sizeof(uint16_t) * dim, sizeof(uint32_t) * pq->m};
+            pipe.go(x, n, sizeof(float) * dim, outs, ob, [&](void *din, size_t rows, void *const *dout) {
+                Shape c = sh;
+                c.n_local = rows;
+                dev.pq_encode(c, (const float *)din, pq->codebooks, pq->metric, pq->p, (uint16_t *)dout[0], (uint32_t *)dout[1], nullptr);
+            });
+            return;
+        }
+        In ix(dev, x, sizeof(float) * n * dim);
+        Out of(dev, out_f16, sizeof(uint16_t) * n * dim), oc(dev, codes, sizeof(uint32_t) * n * pq->m);
         dev.pq_encode(sh, ix.as<float>(), pq->codebooks, pq->metric, pq->p, of.as<uint16_t>(), oc.as<uint32_t>(), nullptr);
         of.finish();
         oc.finish();
@@ -797,6 +875,16 @@ int vqb_sq_quantize(vqb_ctx *ctx, float min, float max, size_t levels, float ste
         if (n_elems == 0) return;
         if (!x || !out) throw Error(VQB_ERR_BAD_ARGUMENT, "NULL data pointer");
         CudaDevice &dev = *ctx->dev;
+        const size_t chunk = 1u << 23; // 8 Mi values = 32 MiB in, 8 MiB out
+        if (!dev.is_device_pointer(x) && !dev.is_device_pointer(out) && n_elems >= 2 * chunk) {
+            HostPipeline pipe(dev, chunk);
+            void *const outs[2] = {out, nullptr};
+            const size_t ob[2] = {1, 0};
+            pipe.go(x, n_elems, sizeof(float), outs, ob, [&](void *din, size_t items, void *const *dout) {
+                dev.sq_quantize(min, max, levels, step, (const float *)din, items, (uint8_t *)dout[0]);
+            });
+            return;
+        }
         In ix(dev, x, sizeof(float) * n_elems);
         Out o(dev, out, n_elems);
         dev.sq_quantize(min, max, levels, step, ix.as<float>(), n_elems, o.as<uint8_t>());
@@ -821,6 +909,16 @@ int vqb_bq_quantize(vqb_ctx *ctx, float threshold, uint8_t low, uint8_t high, co
         if (n_elems == 0) return;
         if (!x || !out) throw Error(VQB_ERR_BAD_ARGUMENT, "NULL data pointer");
         CudaDevice &dev = *ctx->dev;
+        const size_t chunk = 1u << 23;
+        if (!dev.is_device_pointer(x) && !dev.is_device_pointer(out) && n_elems >= 2 * chunk) {
+            HostPipeline pipe(dev, chunk);
+            void *const outs[2] = {out, nullptr};
+            const size_t ob[2] = {1, 0};
+            pipe.go(x, n_elems, sizeof(float), outs, ob, [&](void *din, size_t items, void *const *dout) {
+                dev.bq_quantize(threshold, low, high, (const float *)din, items, (uint8_t *)dout[0]);
+            });
+            return;
+        }
         In ix(dev, x, sizeof(float) * n_elems);
         Out o(dev, out, n_elems);
         dev.bq_quantize(threshold, low, high, ix.as<float>(), n_elems, o.as<uint8_t>());

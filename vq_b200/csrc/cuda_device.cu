@@ -55,6 +55,8 @@ CudaDevice::~CudaDevice()
     if (own_stream_) {
         cudaSetDevice(device_);
         cudaStreamSynchronize(own_stream_);
+        for (int i = 0; i < 2; ++i)
+            if (aux_[i]) cudaStreamDestroy(aux_[i]);
         cudaFree(rownorm_);
         cudaFree(hn_scratch_);
         cudaFree(pq_scratch_);
@@ -115,6 +117,12 @@ std::string CudaDevice::timing_report()
         out += "\"" + kv.first + "\": {\"launches\": " + std::to_string(kv.second.first) + ", \"ms\": " + std::to_string(kv.second.second) + "}";
     }
     return out + "}";
+}
+
+cudaStream_t CudaDevice::aux_stream(int i)
+{
+    if (!aux_[i]) VQB_CUDA_CHECK(cudaStreamCreateWithFlags(&aux_[i], cudaStreamNonBlocking));
+    return aux_[i];
 }
 
 void CudaDevice::make_current() const { VQB_CUDA_CHECK(cudaSetDevice(device_)); }

@@ -56,6 +56,8 @@ class CudaDevice : public Device {
     void sq_quantize(float mn, float mx, size_t levels, float step, const float *x, size_t n, uint8_t *out);
     void bq_quantize(float threshold, uint8_t low, uint8_t high, const float *x, size_t n, uint8_t *out);
 
+    // Two helper streams for overlapping host<->device copies with kernels (created on first use).
+    cudaStream_t aux_stream(int i);
     void set_stream(cudaStream_t s) { stream_ = s; } // nullptr = the CUDA default stream
     void reset_stream() { stream_ = own_stream_; }
     cudaStream_t stream() const { return stream_; }
@@ -82,7 +84,7 @@ class CudaDevice : public Device {
     int device_;
     int sm_count_ = 148;
     size_t smem_limit_ = 0;
-    cudaStream_t own_stream_ = nullptr, stream_ = nullptr;
+    cudaStream_t own_stream_ = nullptr, stream_ = nullptr, aux_[2] = {nullptr, nullptr};
     std::atomic<uint64_t> launches_{0};
     // tensor-core path state (dense_tc.cu): row norms of the rows announced by prepare_rows, shortlist scratch
     bool tensor_enabled_ = true;
