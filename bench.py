@@ -38,7 +38,7 @@ METRIC_NAME, UNIT = "pq_fit_plus_encode_throughput", "Mvec/s"
 TRAIN_BYTES_PER_VEC, ENCODE_BYTES_PER_VEC = 544, 768
 # DRAM traffic per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the 1M-row workload,
 # from the captures summarised under profiles/ (valid for the 1M-row, 1-GPU workload).
-NCU_TRAFFIC_BYTES = {"assign_train": 557.9e6, "pq_encode": 735.8e6}  # profiles/assign_reg_kernel_pq_1m_full.md
+NCU_TRAFFIC_BYTES = {"assign_train": 545.1e6, "pq_encode": 906.4e6}  # profiles/assign_filter_kernel_pq_1m_full.md
 
 
 def measured_peaks():
