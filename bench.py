@@ -270,7 +270,9 @@ def run_ours(args):
         avg_s = k["ms"] / k["launches"] / 1e3
         achieved = bytes_per_vec * n_local / avg_s / 1e9
         return {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(name), "launches": k["launches"],
+                "frac": achieved / peak,
+                "traffic": (NCU_TRAFFIC_BYTES[name] * n_local / N_ROWS) if NCU_TRAFFIC_BYTES.get(name) else None,  # scales with the rows of this rank
+                "launches": k["launches"],
                 "avg_ms": avg_s * 1e3, "algorithmic_bytes_per_launch": bytes_per_vec * n_local,
                 "fp32_ops_per_launch": n_local * M * K * (DIM // M) * 3}
 

@@ -2,6 +2,7 @@
 #include <algorithm>
 
 #include <cstdlib>
+#include <mutex>
 
 #include "assign_filter.cuh"
 #include "assign_generic.cuh"
@@ -12,9 +13,54 @@ namespace vqb {
 
 namespace {
 
-template <typename K> void set_smem(K kernel, size_t bytes)
+// The opt-in to large dynamic shared memory is one attribute per kernel: it is only ever raised, and the resident
+// CTAs per SM are looked up once per (kernel, device, size, threads) instead of on every launch (both are host round
+// trips that show in short per-iteration launches).  The caches are shared by all kernels with the same signature,
+// so the kernel's address is part of every key.
+template <typename K> int configure(K kernel, int threads, size_t smem)
 {
-    VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    struct Slot {
+        const void *fn = nullptr;
+        int device = -1, threads = 0, occ = 1;
+        size_t smem = 0;
+    };
+    struct MaxSlot {
+        const void *fn = nullptr;
+        int device = -1;
+        size_t smem = 0;
+    };
+    static std::mutex mu;
+    static Slot slots[64];
+    static MaxSlot maxes[64];
+    static int next = 0, next_max = 0;
+    int device = 0;
+    cudaGetDevice(&device);
+    const void *fn = reinterpret_cast<const void *>(kernel);
+    std::lock_guard<std::mutex> lk(mu);
+    MaxSlot *mx = nullptr;
+    for (auto &m : maxes)
+        if (m.fn == fn && m.device == device) mx = &m;
+    if (!mx) {
+        mx = &maxes[next_max++ % 64];
+        mx->fn = fn;
+        mx->device = device;
+        mx->smem = 0;
+    }
+    if (smem > mx->smem) {
+        VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        mx->smem = smem;
+    }
+    for (auto &s : slots)
+        if (s.fn == fn && s.device == device && s.smem == smem && s.threads == threads) return s.occ;
+    int occ = 1;
+    VQB_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, threads, smem));
+    Slot &s = slots[next++ % 64];
+    s.fn = fn;
+    s.device = device;
+    s.threads = threads;
+    s.smem = smem;
+    s.occ = std::max(1, occ);
+    return s.occ;
 }
 
 // VQB_EXACT_SCAN=1 forces the plain exact scan (for A/B comparisons); results are identical either way.
@@ -53,11 +99,8 @@ template <int SD, int V, int METRIC, typename CodeT, bool TRAIN, bool FILTER>
 void launch_reg_t(CudaDevice &dev, const AssignParams &p, size_t smem)
 {
     auto kernel = KernelPick<SD, V, METRIC, CodeT, TRAIN, FILTER>::get();
-    set_smem(kernel, smem);
     const int threads = 512;
-    int occ = 1;
-    VQB_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, threads, smem));
-    occ = std::max(1, occ);
+    const int occ = configure(kernel, threads, smem);
     const unsigned long long rbw = (threads / 32) / p.group;
     const unsigned long long n_blocks = (p.n + 32ull * V - 1) / (32ull * V);
     const unsigned long long chunks = (n_blocks + rbw - 1) / rbw;
@@ -136,10 +179,7 @@ template <int METRIC, int MODE, typename CodeT> void launch_gen_t(CudaDevice &de
     const int threads = 32 * w;
     const unsigned long long n_tiles = (p.n + 32ull * w - 1) / (32ull * w);
     auto go = [&](auto kernel) {
-        set_smem(kernel, smem);
-        int occ = 1;
-        VQB_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, threads, smem));
-        occ = std::max(1, occ);
+        const int occ = configure(kernel, threads, smem);
         const unsigned gx = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>(n_tiles, (unsigned long long)dev.sm_count() * occ));
         KernelScope ks(dev, MODE == G_TRAIN ? "assign_train" : (MODE == G_ENCODE ? "pq_encode" : (MODE == G_RVQ_UPDATE ? "rvq_update" : "rvq_quantize")));
         kernel<<<dim3(gx, (unsigned)p.m), threads, smem, dev.stream()>>>(p);

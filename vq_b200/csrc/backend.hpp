@@ -42,6 +42,9 @@ class Comm {
     virtual void allreduce_sum_u32(uint32_t *buf, size_t n) = 0;
     virtual void allreduce_max_u32(uint32_t *buf, size_t n) = 0;
     virtual void allreduce_sum_u64(uint64_t *buf, size_t n) = 0;
+    // Collectives issued between group_begin() and group_end() may be fused into one launch.
+    virtual void group_begin() {}
+    virtual void group_end() {}
 };
 
 class Device {

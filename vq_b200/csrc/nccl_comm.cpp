@@ -22,6 +22,8 @@ struct NcclApi {
     ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
 };
 
@@ -42,6 +44,8 @@ NcclApi &api()
         a.CommDestroy = (decltype(a.CommDestroy))dlsym(a.handle, "ncclCommDestroy");
         a.AllReduce = (decltype(a.AllReduce))dlsym(a.handle, "ncclAllReduce");
         a.GetErrorString = (decltype(a.GetErrorString))dlsym(a.handle, "ncclGetErrorString");
+        a.GroupStart = (decltype(a.GroupStart))dlsym(a.handle, "ncclGroupStart");
+        a.GroupEnd = (decltype(a.GroupEnd))dlsym(a.handle, "ncclGroupEnd");
     });
     if (!a.handle || !a.GetUniqueId || !a.CommInitRank || !a.CommDestroy || !a.AllReduce)
         throw Error(101, "NCCL library (libnccl.so.2) could not be loaded");
@@ -77,6 +81,14 @@ class NcclComm : public Comm {
     void allreduce_sum_u32(uint32_t *b, size_t n) override { run(b, n, ncclUint32, ncclSum); }
     void allreduce_max_u32(uint32_t *b, size_t n) override { run(b, n, ncclUint32, ncclMax); }
     void allreduce_sum_u64(uint64_t *b, size_t n) override { run(b, n, ncclUint64, ncclSum); }
+    void group_begin() override
+    {
+        if (api().GroupStart) check(api().GroupStart(), "ncclGroupStart");
+    }
+    void group_end() override
+    {
+        if (api().GroupEnd) check(api().GroupEnd(), "ncclGroupEnd");
+    }
 
   private:
     void run(void *b, size_t n, ncclDataType_t t, ncclRedOp_t op)

@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(320, 1) pq_tc_kernel(const __grid_constant__ C
     unsigned char *c_smem = base;                                     // m x 8 KiB
     unsigned char *x_smem = base + (size_t)MAXM * CB_BYTES;           // NSTAGE x 16 KiB
     float *hn_s = reinterpret_cast<float *>(x_smem + (size_t)NSTAGE * X_STAGE_BYTES); // [m][256]
-    PqBarriers *bars = reinterpret_cast<PqBarriers *>(hn_s + (size_t)MAXM * BN);
+    PqBarriers *bars = reinterpret_cast<PqBarriers *>(hn_s + (size_t)MAXM * BN + MAXM);
     volatile int *abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -76,6 +76,8 @@ __global__ void __launch_bounds__(320, 1) pq_tc_kernel(const __grid_constant__ C
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     for (int t = threadIdx.x; t < m * BN; t += blockDim.x) hn_s[t] = Q.hn[t];
+    float *cmax_s = hn_s + (size_t)MAXM * BN; // [m]
+    if ((int)threadIdx.x < m) cmax_s[threadIdx.x] = Q.cmax[threadIdx.x];
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -160,6 +162,17 @@ __global__ void __launch_bounds__(320, 1) pq_tc_kernel(const __grid_constant__ C
 #pragma unroll
             for (int i = 0; i < SDW; ++i) xnext[i] = 0.0f;
             if (valid && team < m) load_slice<SDW>(xnext, P.x + row * P.ld + (size_t)team * SDW, P.x_vec4 != 0);
+            // previous assignments of this row (training): one byte per sub-space, fetched once per tile
+            uint32_t oldc[4] = {0, 0, 0, 0};
+            if (TRAIN && valid) {
+                const uint8_t *oc = reinterpret_cast<const uint8_t *>(P.codes) + row * (unsigned long long)m;
+                if (m == 16) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(oc);
+                    oldc[0] = v.x, oldc[1] = v.y, oldc[2] = v.z, oldc[3] = v.w;
+                } else {
+                    for (int t = 0; t < m; ++t) oldc[t >> 2] |= (uint32_t)oc[t] << ((t & 3) * 8);
+                }
+            }
             for (int s = team; s < m && !*abort_flag; s += 2, ++uu) {
                 const uint32_t b = (uint32_t)team;
                 float x[SDW];
@@ -209,7 +222,7 @@ __global__ void __launch_bounds__(320, 1) pq_tc_kernel(const __grid_constant__ C
 #pragma unroll
                 for (int i = 0; i < SDW; ++i) xn2 = fmaf(x[i], x[i], xn2);
                 xn2 *= 1.00001f;
-                const float cmax = Q.cmax[s];
+                const float cmax = cmax_s[s];
                 const float e2 = 2.0f * 2.0e-3f * sqrtf(xn2) * cmax + 1e-6f * cmax * cmax;
                 const float d_a = fmaxf(xn2 + 2.0f * best + e2, 0.0f);
                 const float limit = best + e2 + 1.05f * 14.0f * 5.9604645e-8f * d_a + 2.4e-7f * (fabsf(best) + e2) + 1e-36f;
@@ -250,7 +263,6 @@ __global__ void __launch_bounds__(320, 1) pq_tc_kernel(const __grid_constant__ C
                     int idx = 0, cnt = 0;
                     float bd = PQ_INF;
                     int bi = -1;
-                    const float *cbs = P.centroids + (size_t)s * k * SDW;
                     const unsigned char *cs = c_smem + (size_t)s * CB_BYTES; // 32B-swizzled: row j at (j/8)*256 + (j%8)*32, halves swapped when (j & 4)
                     auto exact = [&](int j) {
                         const unsigned char *rowp = cs + (size_t)(j >> 3) * 256 + (size_t)(j & 7) * 32;
@@ -297,9 +309,31 @@ __global__ void __launch_bounds__(320, 1) pq_tc_kernel(const __grid_constant__ C
                     }
                     if (cnt >= 2) idx = bi < 0 ? 0 : bi;
                     if (cnt == 0) idx = 0;
-                    bool mv = false;
-                    store_result<SDW, CodeT, TRAIN>(P, row, s, idx, cbs, mv);
-                    if (mv) moved_mask |= 1u << s;
+                    if (TRAIN) {
+                        const uint32_t old = (oldc[s >> 2] >> ((s & 3) * 8)) & 0xFFu;
+                        if (old != (uint32_t)idx) moved_mask |= 1u << s;
+                        reinterpret_cast<uint8_t *>(P.codes)[row * (unsigned long long)m + s] = (uint8_t)idx;
+                    } else {
+                        // the chosen centroid's values come from the shared-memory copy (src/pq.rs:176-180)
+                        const unsigned char *rowp = cs + (size_t)(idx >> 3) * 256 + (size_t)(idx & 7) * 32;
+                        const int sw = ((idx >> 2) & 1) * 16;
+                        const float4 lo4 = *reinterpret_cast<const float4 *>(rowp + sw), hi4 = *reinterpret_cast<const float4 *>(rowp + (16 - sw));
+                        const int dim = m * SDW;
+                        if (P.out_codes) P.out_codes[row * m + s] = (uint32_t)idx;
+                        if (P.out_f16) {
+                            uint4 pk;
+                            pk.x = f32_to_f16_bits(lo4.x) | ((uint32_t)f32_to_f16_bits(lo4.y) << 16);
+                            pk.y = f32_to_f16_bits(lo4.z) | ((uint32_t)f32_to_f16_bits(lo4.w) << 16);
+                            pk.z = f32_to_f16_bits(hi4.x) | ((uint32_t)f32_to_f16_bits(hi4.y) << 16);
+                            pk.w = f32_to_f16_bits(hi4.z) | ((uint32_t)f32_to_f16_bits(hi4.w) << 16);
+                            *reinterpret_cast<uint4 *>(P.out_f16 + row * dim + (size_t)s * SDW) = pk; // 16-byte aligned: dim % 8 == 0
+                        }
+                        if (P.out_f32) {
+                            float4 *o = reinterpret_cast<float4 *>(P.out_f32 + row * dim + (size_t)s * SDW);
+                            o[0] = lo4;
+                            o[1] = hi4;
+                        }
+                    }
                 }
             }
         }
@@ -346,7 +380,9 @@ __global__ void pq_codebook_norms_kernel(const float *cb, int m, int k, float *h
 bool pq_tc_applicable(const AssignParams &p, int metric)
 {
     return (metric == M_SQ || metric == M_EUCLID) && p.sd == SDW && p.m >= 4 && p.m <= MAXM && p.m % 4 == 0 && p.k >= 2 && p.k <= BN &&
-           p.ld == (unsigned long long)p.m * SDW && (reinterpret_cast<uintptr_t>(p.x) & 15u) == 0 && p.n >= 1;
+           p.ld == (unsigned long long)p.m * SDW && (reinterpret_cast<uintptr_t>(p.x) & 15u) == 0 && p.n >= 1 &&
+           (reinterpret_cast<uintptr_t>(p.codes) & 15u) == 0 && (reinterpret_cast<uintptr_t>(p.out_f16) & 15u) == 0 &&
+           (reinterpret_cast<uintptr_t>(p.out_f32) & 15u) == 0;
 }
 
 size_t pq_tc_scratch_floats() { return (size_t)MAXM * BN + MAXM; }
@@ -377,7 +413,7 @@ void launch_pq_tc(CudaDevice &dev, const AssignParams &p, int metric, bool train
     q.hn = scratch;
     q.cmax = scratch + (size_t)MAXM * BN;
     q.error = error_word;
-    const size_t smem = 1024 + (size_t)MAXM * CB_BYTES + (size_t)NSTAGE * X_STAGE_BYTES + (size_t)MAXM * BN * sizeof(float) + sizeof(PqBarriers) + 64;
+    const size_t smem = 1024 + (size_t)MAXM * CB_BYTES + (size_t)NSTAGE * X_STAGE_BYTES + ((size_t)MAXM * BN + MAXM) * sizeof(float) + sizeof(PqBarriers) + 64;
     const unsigned long long tiles = (p.n + BM - 1) / BM;
     const unsigned grid = (unsigned)std::min<unsigned long long>(tiles, (unsigned long long)dev.sm_count());
     const bool eu = metric == M_EUCLID;

@@ -32,9 +32,10 @@ __device__ __forceinline__ bool mbar_wait(void *bar, uint32_t parity, volatile i
     const uint32_t addr = smem_u32(bar);
     for (uint32_t i = 0; i < UMMA_SPIN_LIMIT; ++i) {
         uint32_t done;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+        // the hint lets the hardware park the thread (up to ~1 us) instead of spinning through issue slots
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, p;\n\t}"
                      : "=r"(done)
-                     : "r"(addr), "r"(parity)
+                     : "r"(addr), "r"(parity), "r"(1000u)
                      : "memory");
         if (done) return true;
         if ((i & 1023u) == 1023u && *abort_flag) return false;
