@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the quantizer hot path: product-quantizer training + encode at README scale.
 
-Workload (BASELINE.json configs[2]): 1,000,000 x 128 f32 rows, i.i.d. uniform [0,1) from seed 7 (synthetic
+Workload (the reference README's scale): 1,000,000 x 128 f32 rows, i.i.d. uniform [0,1) from seed 7 (synthetic
 stand-in for the reference's StdRng-generated evaluation data, src/bin/utils.rs:31-41), m=16, k=256,
 10 LBG iterations on all rows, then encode all rows to f16 (src/bin/eval_pq.rs:40-60 is what is timed).
 One step = one fit + one encode.  With N > 1 the same 1M rows are sharded over the ranks (strong scaling),
@@ -304,7 +304,7 @@ def run_ours(args):
 
 
 def run_secondary(args):
-    """Other BASELINE.json configurations on one GPU (measurement aid; the headline line is the default workload).
+    """The other benchmark configurations on one GPU (measurement aid; the headline line is the default workload).
     sq / bq: 10,000,000 x 128 values in [-1,1), SQ [0,1] x 256 levels, BQ threshold 0.
     rvq: 1,000,000 x 128 Gaussian mixture (64 components, sigma 0.05), 8 stages, k=256, 10 iterations, Euclidean.
     opq: 1,000,000 x 128 correlated rows, m=16, k=256, 10 outer x 5 LBG iterations."""

@@ -38,7 +38,7 @@ def test_two_gpu_fit_matches_the_oracle(oracle, tmp_path):
     init = so.init_pq(n, m, k)
     cb_int, it_int = oracle.pq_fit(x_int, m, k, 6, init, so.draw)
     so2 = RecordingSeeder(9)
-    # float rows: partial sums meet in a different order, so the bar is north_star's <= 1e-3 after the first iteration
+    # float rows: partial sums meet in a different order, so the bar is <= 1e-3 relative per centroid after the first iteration
     cb_flt, it_flt = oracle.pq_fit(x_flt, m, k, 1, so2.init_pq(n, m, k), so2.draw)
     for r in res:
         assert np.array_equal(r["cb_int"], cb_int) and np.array_equal(r["it_int"], it_int)

@@ -20,7 +20,7 @@ def _fit_both(oracle, x, m, k, iters, seed, accumulate=vq.ACCUM_ORDERED, metric=
     return cb_o, it_o, so, pq, sg
 
 
-def test_config1_shape_bit_exact_training_and_encode(oracle):
+def test_10k_shape_bit_exact_training_and_encode(oracle):
     """10,000 x 128 uniform [0,1), m=16, k=256, 10 iterations, Euclidean: every cluster stays under 1025 members,
     so the reference is deterministic and the whole trajectory must match bit for bit."""
     x = synth.uniform01(10000, 128, 42)

@@ -97,7 +97,7 @@ def test_errors():
 
 
 def test_mixture_config_scaled_down(oracle):
-    """BASELINE configuration 4 scaled to 20,000 rows: 64-component mixture in 128-d, 8 stages, k=256, Euclidean.
+    """The mixture benchmark configuration scaled to 20,000 rows: 64-component mixture in 128-d, 8 stages, k=256, Euclidean.
     Fast (unordered) accumulation: codebooks within tolerance after the first stage, final error within 1 %."""
     x = synth.gaussian_mixture(20000, 128, 11)
     so, sg = RecordingSeeder(5), RecordingSeeder(5)

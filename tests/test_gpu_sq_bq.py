@@ -49,7 +49,7 @@ def test_unaligned_device_pointers(oracle):
 
 
 def test_full_size_10m_x_128(oracle):
-    """BASELINE configuration 2: 10,000,000 x 128 values in [-1, 1); SQ [0,1] with 256 levels, BQ threshold 0.
+    """The element-wise benchmark configuration: 10,000,000 x 128 values in [-1, 1); SQ [0,1] with 256 levels, BQ threshold 0.
     Device-generated (seeded torch generator) to avoid a 5 GB host array; whole-array properties plus oracle
     comparison on sampled slabs."""
     import torch

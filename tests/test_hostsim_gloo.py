@@ -92,7 +92,7 @@ def test_single_rank_host_loop_equals_oracle_on_float_rows(hostsim, oracle, tmp_
 
 def test_pq_fit_sharded_float_rows_within_tolerance(hostsim, oracle, tmp_path):
     """Float rows: per-rank partial sums are added in a different order than the single-process sum, so the codebooks
-    agree to rounding (<= 1e-3 relative per centroid after the first iteration, north_star's tolerance)."""
+    agree to rounding (<= 1e-3 relative per centroid after the first iteration, the accepted tolerance)."""
     from vq_b200 import synth
     x = synth.uniform01(4001, 8, 21)
     so = RecordingSeeder(2)

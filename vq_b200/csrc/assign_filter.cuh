@@ -83,7 +83,7 @@ template <int SD> __device__ __forceinline__ void unpack_centroid(float (&c)[SD]
 }
 
 template <int SD, int V, int METRIC, typename CodeT, bool TRAIN>
-__global__ void __launch_bounds__(512, 1) assign_filter_kernel(const AssignParams P)
+__global__ void __launch_bounds__((SD == 8 && V == 2) ? 1024 : 512, 1) assign_filter_kernel(const AssignParams P)
 {
     static_assert(METRIC == M_SQ || METRIC == M_EUCLID, "the FMA filter is defined for the Euclidean metrics");
     static_assert(SD % 2 == 0, "even sub-space width");

@@ -99,7 +99,7 @@ template <int SD, int V, int METRIC, typename CodeT, bool TRAIN, bool FILTER>
 void launch_reg_t(CudaDevice &dev, const AssignParams &p, size_t smem)
 {
     auto kernel = KernelPick<SD, V, METRIC, CodeT, TRAIN, FILTER>::get();
-    const int threads = 512;
+    const int threads = (FILTER && SD == 8 && V == 2) ? 1024 : 512; // the two-rows-per-lane filter variant runs 32 warps per CTA
     const int occ = configure(kernel, threads, smem);
     const unsigned long long rbw = (threads / 32) / p.group;
     const unsigned long long n_blocks = (p.n + 32ull * V - 1) / (32ull * V);
@@ -153,7 +153,13 @@ bool launch_assign_reg(CudaDevice &dev, const AssignParams &p_in, int metric, bo
     p.group = g;
     const size_t smem = (size_t)g * per_sub;
     if (p.sd == 4) return launch_reg_sd<4, 4>(dev, p, met, train, cb, smem);
-    if (p.sd == 8) return launch_reg_sd<8, 4>(dev, p, met, train, cb, smem);
+    if (p.sd == 8) {
+        static const bool v2 = [] {
+            const char *e = std::getenv("VQB_FILTER_V2"); // experiment: 2 rows per lane, 1024 threads per CTA
+            return e && *e == '1';
+        }();
+        return v2 ? launch_reg_sd<8, 2>(dev, p, met, train, cb, smem) : launch_reg_sd<8, 4>(dev, p, met, train, cb, smem);
+    }
     return launch_reg_sd<16, 2>(dev, p, met, train, cb, smem);
 }
 
