@@ -116,6 +116,13 @@ int vqb_comm_destroy(vqb_ctx *ctx);
 int vqb_distance_rows(vqb_ctx *ctx, int metric, double p, const float *a, size_t da, const float *b,
                       size_t db, size_t n, float *out);
 
+/* ---- evaluation metrics of the reference's harness, computed on the device --------------------------------
+ * mse_out: mean squared reconstruction error, calculate_reconstruction_error (src/bin/utils.rs:50-67);
+ * recall_out: recall@k over at most 1000 evenly spaced queries, each searched in a 5000-row window when n > 10000,
+ * calculate_recall (src/bin/utils.rs:70-127).  q_f16: the n x dim binary16 output of a quantize call.  1 <= k <= 32. */
+int vqb_evaluate_f16(vqb_ctx *ctx, const float *x, const uint16_t *q_f16, size_t n, size_t dim, size_t k,
+                     float *mse_out, float *recall_out);
+
 /* Diagnostic for the tensor-core path used by full-width k-means (residual quantizer): the raw tcgen05 TF32 dot
  * products x_r . c_j (dots_out: n x 256, columns >= k are 0; may be NULL) and shortlist statistics
  * stats_out[3] = {rows, shortlisted candidates, rows that needed a full exact scan}.  Requires 32 <= dim <= 128,

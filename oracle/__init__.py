@@ -325,6 +325,34 @@ def bq_quantize(threshold: float, low: int, high: int, x) -> np.ndarray:
     return out
 
 
+def recall_at_k(original, approx, k: int = 10) -> float:
+    """calculate_recall, src/bin/utils.rs:70-127 (approx = the f16 reconstruction converted back to f32)."""
+    original, approx = _f32(original), _f32(approx)
+    n = original.shape[0]
+    eval_samples = min(n, 1000)
+    step = n // eval_samples if n // eval_samples > 0 else 1
+    total = np.float32(0.0)
+
+    def knn(data, i, start, end):
+        rows, q = data[start:end], data[i]
+        acc = np.zeros(end - start, np.float32)
+        for t in range(data.shape[1]):  # serial f32 fold over the dimensions, as Vector::distance2 does
+            diff = q[t] - rows[:, t]
+            acc = acc + diff * diff
+        d = np.sqrt(acc)
+        order = [start + t for t in np.argsort(d, kind="stable") if start + t != i]
+        return order[:k]
+
+    for i in range(0, n, step):
+        window = 5000 if n > 10_000 else n
+        start = i - window // 2 if i > window // 2 else 0
+        end = min(i + window // 2, n)
+        true_nn = knn(original, i, start, end)
+        approx_nn = set(knn(approx, i, start, end))
+        total = np.float32(total + np.float32(sum(1 for j in true_nn if j in approx_nn)) / np.float32(k))
+    return float(total / np.float32(n // step))
+
+
 def mse_f16(x, q_bits) -> float:
     """src/bin/utils.rs:50-67 (f64 accumulation)."""
     x = _f32(x)

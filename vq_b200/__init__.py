@@ -599,6 +599,25 @@ class BinaryQuantizer:
         return out
 
 
+def evaluate(original, quantized_f16, k: int = 10, *, ctx: Context | None = None):
+    """The reference harness's quality metrics on the device: (reconstruction error, recall@k), i.e.
+    calculate_reconstruction_error and calculate_recall of src/bin/utils.rs:50-127 applied to the f16 output of a
+    ``quantize`` call (numpy float16 array or CUDA float16 tensor, one row per vector)."""
+    ctx = ctx or default_context()
+    x = _Arr(original, ctx)
+    if _is_torch(quantized_f16) and quantized_f16.is_cuda:
+        qk = quantized_f16.contiguous()
+        qptr = qk.data_ptr()
+    else:
+        qk = np.ascontiguousarray(quantized_f16, dtype=np.float16)
+        qptr = qk.ctypes.data
+    mse, rec = C.c_float(), C.c_float()
+    rc = _lib.load().vqb_evaluate_f16(ctx.handle, x.ptr, qptr, x.n, x.dim, int(k), C.byref(mse), C.byref(rec))
+    if rc:
+        _raise(rc, ctx.handle)
+    return float(mse.value), float(rec.value)
+
+
 def lbg_quantize(data, k: int, max_iters: int, seed: int, *, ctx: Context | None = None, accumulate: int = ACCUM_AUTO,
                  init_idx=None, draw=None):
     """lbg_quantize (src/utils.rs:32-109) on n x d rows.  Returns (centroids k x d, iterations)."""

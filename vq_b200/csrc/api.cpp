@@ -361,6 +361,19 @@ int vqb_distance_rows(vqb_ctx *ctx, int metric, double p, const float *a, size_t
     });
 }
 
+int vqb_evaluate_f16(vqb_ctx *ctx, const float *x, const uint16_t *q_f16, size_t n, size_t dim, size_t k, float *mse_out,
+                     float *recall_out)
+{
+    if (!ctx) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "ctx is NULL");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (!x || !q_f16 || !mse_out || !recall_out) throw Error(VQB_ERR_BAD_ARGUMENT, "NULL argument");
+        CudaDevice &dev = *ctx->dev;
+        In ix(dev, x, sizeof(float) * n * dim), iq(dev, q_f16, sizeof(uint16_t) * n * dim);
+        dev.evaluate_f16(ix.as<float>(), iq.as<uint16_t>(), n, dim, k, mse_out, recall_out);
+    });
+}
+
 int vqb_dense_dots(vqb_ctx *ctx, const float *x, size_t n, size_t dim, const float *codebook, size_t k, float *dots_out,
                    unsigned long long *stats_out)
 {
