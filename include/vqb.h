@@ -130,6 +130,13 @@ int vqb_evaluate_f16(vqb_ctx *ctx, const float *x, const uint16_t *q_f16, size_t
 int vqb_dense_dots(vqb_ctx *ctx, const float *x, size_t n, size_t dim, const float *codebook, size_t k,
                    float *dots_out, unsigned long long *stats_out);
 
+/* Diagnostic for the tensor-core path of the product quantizer (sub-space width 8): the raw split-TF32 scores
+ * |c_j|^2/2 - x.c_j (scores_out: n x m x 256, may be NULL), the codes the path produces (codes_out: n x m) and the number
+ * of (row, sub-space) pairs it left to the exact scan.  Requires m % 4 == 0, 4 <= m <= 64, 2 <= k <= 256.
+ * No counterpart in the reference. */
+int vqb_pq_tensor_scores(vqb_ctx *ctx, const float *x, size_t n, size_t m, const float *codebooks, size_t k,
+                         float *scores_out, uint32_t *codes_out, unsigned long long *marked_out);
+
 /* ---- lbg_quantize (src/utils.rs:32-109) on `n` rows of width d:
  * init_idx = k row indices, centroids_out = k x d (host or device). ------- */
 int vqb_lbg_fit(vqb_ctx *ctx, const float *x, size_t n, size_t d, size_t k, size_t max_iters,

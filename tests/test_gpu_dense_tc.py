@@ -70,9 +70,9 @@ def test_lbg_full_width_with_duplicates_and_specials(oracle):
     assert np.array_equal(cent, cent_o, equal_nan=True)
 
 
-def test_pq_tensor_core_kernel_matches_the_default_path(oracle):
-    """The tcgen05 product-quantizer kernel (opt-in with VQB_PQ_TENSOR=1) in a child process: codebooks and codes must be
-    bit-identical to the oracle's, like the default CUDA-core path."""
+def test_pq_filter_kernel_matches_the_default_path(oracle):
+    """The CUDA-core filter kernel of the product quantizer (VQB_PQ_TENSOR=0) in a child process: codebooks and codes must
+    be bit-identical to the oracle's, like the default tcgen05 path."""
     import os
     import subprocess
     import sys
@@ -94,7 +94,7 @@ np.savez(sys.argv[1], cb=pq.codebooks, codes=codes, out=out.view(np.uint16))
     from vq_b200.seeding import LbgSeeder
     with tempfile.TemporaryDirectory() as d:
         path = os.path.join(d, "r.npz")
-        res = subprocess.run([sys.executable, "-c", code, path], env=dict(os.environ, VQB_PQ_TENSOR="1"), stdout=subprocess.PIPE,
+        res = subprocess.run([sys.executable, "-c", code, path], env=dict(os.environ, VQB_PQ_TENSOR="0"), stdout=subprocess.PIPE,
                              stderr=subprocess.STDOUT, timeout=600)
         assert res.returncode == 0, res.stdout.decode()[-2000:]
         got = np.load(path)

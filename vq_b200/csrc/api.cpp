@@ -389,6 +389,22 @@ int vqb_dense_dots(vqb_ctx *ctx, const float *x, size_t n, size_t dim, const flo
     });
 }
 
+int vqb_pq_tensor_scores(vqb_ctx *ctx, const float *x, size_t n, size_t m, const float *codebooks, size_t k, float *scores_out,
+                         uint32_t *codes_out, unsigned long long *marked_out)
+{
+    if (!ctx) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "ctx is NULL");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (!x || !codebooks || !codes_out || !marked_out || n == 0) throw Error(VQB_ERR_BAD_ARGUMENT, "NULL or empty argument");
+        CudaDevice &dev = *ctx->dev;
+        In ix(dev, x, sizeof(float) * n * m * 8), ic(dev, codebooks, sizeof(float) * m * k * 8);
+        Out os(dev, scores_out, scores_out ? sizeof(float) * n * m * 256 : 0), oc(dev, codes_out, sizeof(uint32_t) * n * m);
+        dev.pq_tensor_debug(ix.as<float>(), n, m, ic.as<float>(), k, scores_out ? os.as<float>() : nullptr, oc.as<uint32_t>(), marked_out);
+        os.finish();
+        oc.finish();
+    });
+}
+
 int vqb_lbg_fit(vqb_ctx *ctx, const float *x, size_t n, size_t d, size_t k, size_t max_iters, const uint64_t *init_idx,
                 vqb_draw_fn draw, void *user, int flags, float *centroids_out, size_t *iterations_out)
 {

@@ -38,10 +38,10 @@ CudaDevice::CudaDevice(int device) : device_(device)
     {
         const char *e = std::getenv("VQB_NO_TENSOR"); // VQB_NO_TENSOR=1: CUDA-core kernels only (A/B comparisons)
         tensor_enabled_ = !(e && *e && *e != '0');
-        // The product quantizer's 8-wide sub-spaces run on the CUDA-core filter kernel by default (it is the faster of the
-        // two today: 2.3 ms against 3.0 ms per 1M-row pass); VQB_PQ_TENSOR=1 selects the tcgen05 kernel of pq_tc.cu.
+        // The product quantizer's 8-wide sub-spaces run on the tcgen05 kernel of pq_tc.cu (about twice as fast as the
+        // CUDA-core filter kernel); VQB_PQ_TENSOR=0 selects the filter kernel (A/B comparisons).
         const char *f = std::getenv("VQB_PQ_TENSOR");
-        pq_tensor_enabled_ = tensor_enabled_ && f && *f == '1';
+        pq_tensor_enabled_ = tensor_enabled_ && !(f && *f == '0');
     }
     cudaMemPool_t pool;
     if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
@@ -176,6 +176,7 @@ void CudaDevice::ensure_tc_buffers(size_t n)
     if (!hn_scratch_) {
         VQB_CUDA_CHECK(cudaMalloc(&hn_scratch_, 260 * sizeof(float)));
         VQB_CUDA_CHECK(cudaMalloc(&pq_scratch_, pq_tc_scratch_floats() * sizeof(float)));
+        VQB_CUDA_CHECK(cudaMemsetAsync(pq_scratch_, 0, pq_tc_scratch_floats() * sizeof(float), stream_));
         VQB_CUDA_CHECK(cudaMalloc(&tc_stats_, 3 * sizeof(unsigned long long)));
         VQB_CUDA_CHECK(cudaMalloc(&tc_error_, sizeof(int)));
         VQB_CUDA_CHECK(cudaMemsetAsync(tc_stats_, 0, 3 * sizeof(unsigned long long), stream_));
@@ -229,6 +230,28 @@ void CudaDevice::dense_debug(const float *x, size_t n, size_t dim, const float *
     dense_shortlist(*this, x, n, dim, codebook, k, rownorm_, hn_scratch_, cand_, tc_stats_, tc_error_, dots);
     download(stats3, tc_stats_, 3 * sizeof(unsigned long long));
     prepared_x_ = nullptr;
+}
+
+void CudaDevice::pq_tensor_debug(const float *x, size_t n, size_t m, const float *codebooks, size_t k, float *scores, uint32_t *codes,
+                                 unsigned long long *marked)
+{
+    AssignParams p = {};
+    p.x = x;
+    p.n = n;
+    p.ld = m * 8;
+    p.m = (int)m;
+    p.k = (int)k;
+    p.sd = 8;
+    p.centroids = codebooks;
+    p.out_codes = codes;
+    p.x_vec4 = 1;
+    if (!pq_tc_applicable(p, M_SQ)) throw Error(103, "shape not covered by the product-quantizer tensor-core path");
+    ensure_tc_buffers(0);
+    unsigned long long before = 0, after = 0;
+    download(&before, pq_scratch_ + pq_tc_stats_offset_floats(), sizeof before);
+    launch_pq_tc(*this, p, M_SQ, false, 4, pq_scratch_, tc_error_, scores);
+    download(&after, pq_scratch_ + pq_tc_stats_offset_floats(), sizeof after);
+    *marked = after - before;
 }
 
 void CudaDevice::copy(void *dst, const void *src, size_t bytes)

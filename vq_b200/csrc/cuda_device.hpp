@@ -52,6 +52,9 @@ class CudaDevice : public Device {
     void rvq_quantize(const float *x, size_t n, size_t dim, const float *codebooks, size_t stages, size_t k,
                       float epsilon, int metric, double p, uint16_t *out_f16, uint32_t *out_codes);
     void f32_to_f16_rows(const float *in, size_t n, uint16_t *out);
+    // Raw scores, codes and the number of pairs left to the exact scan of the product-quantizer tensor-core kernel.
+    void pq_tensor_debug(const float *x, size_t n, size_t m, const float *codebooks, size_t k, float *scores, uint32_t *codes,
+                         unsigned long long *marked);
     // Reconstruction error and windowed recall@k of an f16 reconstruction (the reference's evaluation metrics).
     void evaluate_f16(const float *x, const uint16_t *q, size_t n, size_t dim, size_t k, float *mse_out, float *recall_out);
     void distance_rows(int metric, double p, const float *a, const float *b, size_t d, size_t n, float *out);

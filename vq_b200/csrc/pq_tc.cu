@@ -1,18 +1,41 @@
-// pq_tc.cu -- product-quantizer nearest-centroid search (sub-space width 8) with the dot products on the tensor cores.
+// pq_tc.cu -- product-quantizer nearest-centroid search (sub-space width 8) with the scores on the tensor cores.
 //
 // Replaces the per-point scan of src/utils.rs:59-73 (training) and src/pq.rs:159-182 (encode) for the Euclidean metrics.
-// For every 128-row tile and every sub-space one tcgen05.mma (M128 x N256 x K8, kind::tf32) writes the 128 x 256 dot
-// products x.c_j into tensor memory; the epilogue turns them into scores S_j = |c_j|^2/2 - x.c_j, finds the smallest and
-// marks every centroid whose score lies within a proven bound of it (the reasoning of dense_tc.cu with K = 8):
-//     |dot_tc - x.c| <= 2.0e-3 |x| |c_j|,   limit = S_min + 2E + 1.05 (8 + 6) 2^-24 d + slack,   E = 2.0e-3 |x| max|c_j| (+ half-norm rounding)
-// A single marked centroid is the answer; several are decided by the reference's exact f32 arithmetic in ascending index
-// order with strict '<' (the row slice is re-read from L2, the centroids from the L1-cached codebook).  The result is the
-// exact scan's, bit for bit; rows that cannot be ranked (NaN / infinity) are scanned exactly in full.
 //
-// CTA (1 per SM, persistent): warp 0 TMA producer (row tiles in 128-byte column chunks = 4 sub-spaces each, 5-stage ring;
-// all codebooks once, 8 KiB per sub-space in the 32B-swizzled K-major layout), warp 1 MMA issuer + tensor-memory owner
-// (two 256-column accumulators, one per sub-space parity), warps 2..9 epilogue in two teams of four (one row per lane;
-// team t takes the sub-spaces of parity t).  All waits are bounded.
+// Scores.  S_j = |c_j|^2/2 - x.c_j ranks the centroids like the squared distance (|x - c_j|^2 = |x|^2 + 2 S_j).  Both
+// operands are split into two TF32 numbers (x = xh + xl, c = ch + cl, each part exactly representable, so the hardware's
+// treatment of the low mantissa bits does not matter) and one K = 32 tcgen05.mma chain per (128-row tile, sub-space)
+// accumulates, in f32,
+//     xh.(-ch) + xh.(-cl) + xl.(-ch) + 1*hn_h + 1*hn_l            (hn = |c|^2/2 split the same way)
+// into tensor memory: 128 x 256 scores with about 2^-21 relative accuracy instead of TF32's 2^-11.
+//
+// Decision.  Per row the epilogue finds the smallest score, then counts the scores below
+//     limit = best + 7e-6 (|x|^2/2 + 2 max_j hn_j + |best|)
+// If exactly one score lies below the limit its centroid is the reference's answer; otherwise (two or more within the
+// limit, NaN / infinity, values too small to rank) the (row, sub-space) pair is marked and a second kernel decides it with
+// the reference's own f32 arithmetic over all centroids (ascending index, strict '<', sqrt inside the comparison for the
+// Euclidean metric, scan started at centroid 0).  The result equals the exact scan's bit for bit.
+//
+// Bound behind 7e-6.  u = 2^-24, xh2 = |x|^2/2, HN = max_j hn_j.
+//   operand split:   dropped xl.cl and the rounding of xl, cl to TF32: <= 3 * 2^-22 sum|x_i c_ji| <= 3 * 2^-22 (xh2 + hn_j)
+//   half norm:       f32 chain 9u hn_j, split 2^-22 hn_j
+//   accumulation:    26 exact products summed by the tensor core in f32; assumed error <= 2^-20 (hn_j + sum|x_i c_ji|),
+//                    sixteen times what is measured (tests/test_gpu_pq_tensor.py measures it against f64)
+//   => |S_j - true| <= E = 1.25 * 2^-19 (xh2 + 2 HN) = 2.4e-6 (xh2 + 2 HN)
+//   the reference prefers w over a = argmin S only if D_w <= D_a (1 + 4u) in its own arithmetic (10u relative each), i.e.
+//   S_w <= S_a + 2E + 25u (xh2 + |S_a| + E)  <=  S_a + 4.8e-6 (xh2 + 2HN) + 1.5e-6 (xh2 + |S_a|) + ...  <  limit.
+// The count uses t = sat((limit - S) * 2^p) with p chosen per row so that limit * 2^p ~ 2^60: a score differs from the
+// limit by nothing or by at least one unit in its last place (>= 2^-24 |limit|), so t is exactly 0 or 1, and
+// sum t * (1 + j / 512) yields count and index at once on the FMA pipe.
+//
+// CTA (1 per SM, persistent, 448 threads), owning 4 consecutive sub-spaces (m / 4 groups share the row tiles):
+//   warp 0       loads the group's four operand-B tiles once (TMA, 128B swizzle, no multicast; 32 KiB each)
+//   warp 1       owns tensor memory (two 128 x 256 f32 accumulators) and issues the MMAs
+//   warps 2-5    read row slices from global memory, split them and write operand-A tiles (128 rows x 128 bytes, 128B
+//                swizzle) into a 4-stage ring, plus |x|^2/2 per row
+//   warps 6-13   epilogue: two teams of four warps (one row per lane, one TMEM lane quadrant per warp); team t serves
+//                sub-spaces 2t, 2t+1 of the group through accumulator t
+// Every wait is bounded; on expiry the CTA records a code, stops issuing, frees tensor memory and the host raises an error.
 #include <algorithm>
 
 #include "assign_reg.cuh"
@@ -25,48 +48,89 @@ namespace vqb {
 
 namespace {
 
-constexpr int BM = 128, BN = 256, SDW = 8, CHUNK = 32, NSTAGE = 5, MAXM = 16;
-constexpr uint32_t X_STAGE_BYTES = BM * 128;
-constexpr uint32_t CB_BYTES = BN * SDW * 4; // 8 KiB per sub-space
+constexpr int BM = 128, BN = 256, SDW = 8, KOP = 32, NSTAGE = 4, MAXM = 64, XH_RING = 8, NTHREADS = 448;
+constexpr uint32_t A_STAGE_BYTES = BM * 128; // 16 KiB
+constexpr uint32_t B_BYTES = BN * 128;       // 32 KiB per sub-space
+constexpr float PAD_SCORE = 1e30f;           // score of the columns beyond k
+constexpr float MARGIN_COEF = 7e-6f;
+
+// scratch layout (floats)
+constexpr size_t OFF_BOP = 0;                                   // [MAXM][256][32] operand B
+constexpr size_t OFF_C16 = OFF_BOP + (size_t)MAXM * BN * KOP;   // [MAXM][256] 8 halves (uint4)
+constexpr size_t OFF_HMAX = OFF_C16 + (size_t)MAXM * BN * 4;    // [MAXM]
+constexpr size_t OFF_STATS = OFF_HMAX + MAXM;                   // 2 x u64: marked pairs, launches
+constexpr size_t SCRATCH_FLOATS = OFF_STATS + 4;
 
 struct alignas(8) PqBarriers {
-    unsigned long long full[NSTAGE], empty[NSTAGE], cfull, tfull[2], tempty[2];
+    unsigned long long afull[NSTAGE], aempty[NSTAGE], bfull, tfull[2], tempty[2];
     uint32_t tmem_base;
     int abort_flag;
 };
 
 struct PqTcParams {
     AssignParams a;
-    const float *hn;   // [m][256] |c|^2/2, +inf beyond k
-    const float *cmax; // [m]      max |c|
+    const uint4 *c16;   // [m][256] centroid values as 8 binary16
+    const float *hnmax; // [m]
+    uint8_t *marks;     // [n][m/2]: bit h of byte (g, team) = pair (row, 4g + 2 team + h) needs the exact scan
+    unsigned long long *stats;
     int *error;
+    float *dbg_scores; // optional [n][m][256]
 };
 
-#define PQ_INF __int_as_float(0x7f800000)
+__device__ __forceinline__ float to_tf32(float v)
+{
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return __uint_as_float(r);
+}
 
-template <typename CodeT, bool TRAIN, bool EUCLID>
-__global__ void __launch_bounds__(320, 1) pq_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_c, const PqTcParams Q)
+__device__ __forceinline__ float fma_sat(float a, float b, float c)
+{
+    float d;
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// order in which the four sub-spaces of a group are issued: accumulator / team = ss >> 1 alternates
+__device__ __forceinline__ int issue_order(int p) { return ((p & 1) << 1) | (p >> 1); } // 0, 2, 1, 3
+
+template <bool TRAIN, bool EUCLID>
+__global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constant__ CUtensorMap map_b, const PqTcParams Q)
 {
     extern __shared__ unsigned char smem_raw[];
     const AssignParams &P = Q.a;
     unsigned char *base = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned char *c_smem = base;                                     // m x 8 KiB
-    unsigned char *x_smem = base + (size_t)MAXM * CB_BYTES;           // NSTAGE x 16 KiB
-    float *hn_s = reinterpret_cast<float *>(x_smem + (size_t)NSTAGE * X_STAGE_BYTES); // [m][256]
-    PqBarriers *bars = reinterpret_cast<PqBarriers *>(hn_s + (size_t)MAXM * BN + MAXM);
+    unsigned char *b_smem = base;                                           // 4 x 32 KiB
+    unsigned char *a_smem = base + 4 * (size_t)B_BYTES;                     // NSTAGE x 16 KiB
+    float *xh_ring = reinterpret_cast<float *>(a_smem + (size_t)NSTAGE * A_STAGE_BYTES); // [XH_RING][128]
+    PqBarriers *bars = reinterpret_cast<PqBarriers *>(xh_ring + XH_RING * BM);
     volatile int *abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m = P.m, k = P.k;
-    const int nchunks = m / 4; // 4 sub-spaces per 128-byte chunk
+    const int ngroups = m >> 2;
+    const int g = blockIdx.x % ngroups;
+    const unsigned long long tile0 = blockIdx.x / ngroups, tstep = gridDim.x / ngroups;
     const unsigned long long n_tiles = (P.n + BM - 1) / BM;
+
+    // the active sub-spaces of this group in issue order (identical in every thread)
+    int list[4], pos[4] = {-1, -1, -1, -1}, nact = 0;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        const int ss = issue_order(p);
+        const bool act = !(TRAIN && P.active && P.active[g * 4 + ss] == 0);
+        if (act) {
+            pos[ss] = nact;
+            list[nact++] = ss;
+        }
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
-            mbar_init(&bars->full[s], 1);
-            mbar_init(&bars->empty[s], 1);
+            mbar_init(&bars->afull[s], 4);
+            mbar_init(&bars->aempty[s], 1);
         }
-        mbar_init(&bars->cfull, 1);
+        mbar_init(&bars->bfull, 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(&bars->tfull[b], 1);
             mbar_init(&bars->tempty[b], 4);
@@ -75,9 +139,6 @@ __global__ void __launch_bounds__(320, 1) pq_tc_kernel(const __grid_constant__ C
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    for (int t = threadIdx.x; t < m * BN; t += blockDim.x) hn_s[t] = Q.hn[t];
-    float *cmax_s = hn_s + (size_t)MAXM * BN; // [m]
-    if ((int)threadIdx.x < m) cmax_s[threadIdx.x] = Q.cmax[threadIdx.x];
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -88,260 +149,259 @@ __global__ void __launch_bounds__(320, 1) pq_tc_kernel(const __grid_constant__ C
     const uint32_t tmem_base = bars->tmem_base;
 
     if (warp == 0) {
-        // ------------------------------------------------ TMA producer
-        if (lane == 0) {
-            mbar_expect_tx(&bars->cfull, (uint32_t)m * CB_BYTES);
-            for (int s = 0; s < m; ++s) tma_load_2d(c_smem + (size_t)s * CB_BYTES, &map_c, 0, s * k, &bars->cfull);
-            uint32_t it = 0;
-            for (unsigned long long tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x) {
-                for (int c = 0; c < nchunks; ++c, ++it) {
-                    const int st = it % NSTAGE;
-                    if (!mbar_wait(&bars->empty[st], ((it / NSTAGE) & 1u) ^ 1u, abort_flag, Q.error, 11)) break;
-                    mbar_expect_tx(&bars->full[st], X_STAGE_BYTES);
-                    tma_load_2d(x_smem + (size_t)st * X_STAGE_BYTES, &map_x, c * CHUNK, (int)(tile * BM), &bars->full[st]);
-                }
-            }
-            if (*abort_flag) { // let copies in flight land before the CTA retires (bounded)
-                for (uint32_t back = 0; back < NSTAGE && back < it; ++back) {
-                    const uint32_t j = it - 1 - back;
-                    const uint32_t addr = smem_u32(&bars->full[j % NSTAGE]);
-                    for (uint32_t spin = 0; spin < 20000u; ++spin) {
-                        uint32_t done;
-                        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-                                     : "=r"(done)
-                                     : "r"(addr), "r"((j / NSTAGE) & 1u)
-                                     : "memory");
-                        if (done) break;
-                    }
-                }
-            }
+        // ------------------------------------------------ operand B: the group's four sub-spaces, once
+        if (lane == 0 && nact > 0) {
+            mbar_expect_tx(&bars->bfull, 4 * B_BYTES);
+            for (int ss = 0; ss < 4; ++ss) tma_load_2d(b_smem + (size_t)ss * B_BYTES, &map_b, 0, (g * 4 + ss) * BN, &bars->bfull);
         }
     } else if (warp == 1) {
-        // ------------------------------------------------ MMA issuer: one K=8 MMA per (tile, sub-space)
-        if (lane == 0) {
-            bool ok = mbar_wait(&bars->cfull, 0, abort_flag, Q.error, 12);
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0 && nact > 0) {
+            bool ok = mbar_wait(&bars->bfull, 0, abort_flag, Q.error, 12);
             uint32_t it = 0, uses[2] = {0, 0};
-            for (unsigned long long tile = blockIdx.x; ok && tile < n_tiles && !*abort_flag; tile += gridDim.x) {
-                for (int c = 0; ok && c < nchunks; ++c, ++it) {
+            for (unsigned long long tile = tile0; ok && tile < n_tiles && !*abort_flag; tile += tstep) {
+                for (int p = 0; ok && p < nact; ++p, ++it) {
+                    const int ss = list[p];
+                    const uint32_t b = (uint32_t)ss >> 1;
                     const int st = it % NSTAGE;
-                    if (!mbar_wait(&bars->full[st], (it / NSTAGE) & 1u, abort_flag, Q.error, 14)) {
+                    if (!mbar_wait(&bars->afull[st], (it / NSTAGE) & 1u, abort_flag, Q.error, 14) ||
+                        !mbar_wait(&bars->tempty[b], (uses[b] & 1u) ^ 1u, abort_flag, Q.error, 13)) {
                         ok = false;
                         break;
                     }
+                    ++uses[b];
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t adesc = smem_desc_sw128(smem_u32(x_smem + (size_t)st * X_STAGE_BYTES));
-                    for (int ss = 0; ss < 4; ++ss) {
-                        const uint32_t b = (uint32_t)ss & 1u; // sub-space parity = epilogue team = accumulator
-                        if (!mbar_wait(&bars->tempty[b], (uses[b] & 1u) ^ 1u, abort_flag, Q.error, 13)) {
-                            ok = false;
-                            break;
-                        }
-                        ++uses[b];
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        const uint64_t bdesc = smem_desc_sw32(smem_u32(c_smem + (size_t)(c * 4 + ss) * CB_BYTES));
-                        umma_tf32(tmem_base + b * BN, adesc + (uint64_t)(2 * ss), bdesc, 0u); // sub-space ss = bytes [32 ss, 32 ss + 32) of the chunk rows
-                        umma_commit(&bars->tfull[b]);
-                    }
-                    if (ok) umma_commit(&bars->empty[st]);
+                    const uint64_t adesc = smem_desc_sw128(smem_u32(a_smem + (size_t)st * A_STAGE_BYTES));
+                    const uint64_t bdesc = smem_desc_sw128(smem_u32(b_smem + (size_t)ss * B_BYTES));
+#pragma unroll
+                    for (int k8 = 0; k8 < KOP / 8; ++k8) // 8 f32 = 32 bytes = 2 descriptor units per step
+                        umma_tf32(tmem_base + b * BN, adesc + (uint64_t)(2 * k8), bdesc + (uint64_t)(2 * k8), k8 ? 1u : 0u);
+                    umma_commit(&bars->aempty[st]);
+                    umma_commit(&bars->tfull[b]);
                 }
             }
         }
-    } else {
-        // ------------------------------------------------ epilogue: two teams of four warps; team t owns accumulator t
-        // and the sub-spaces s = t, t + 2, ...; within a team warp w reads the TMEM lane quadrant w & 3
-        const int q = warp & 3;
-        const int team = (warp - 2) >> 2;
-        uint32_t moved_mask = 0; // bit s: some row of sub-space s changed its assignment (src/utils.rs:76-80)
-        uint32_t uu = 0;         // uses of this team's accumulator so far
-        mbar_wait(&bars->cfull, 0, abort_flag, Q.error, 16); // the codebooks are read from shared memory below
-        for (unsigned long long tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x) {
-            const unsigned long long row = tile * BM + 32ull * q + lane;
-            const bool valid = row < P.n;
-            // row slices are fetched one sub-space ahead (L2 hits: the tile was just streamed through it)
-            float xnext[SDW];
+    } else if (warp < 6) {
+        // ------------------------------------------------ operand A: split row slices into the ring
+        const int r = (warp - 2) * 32 + lane; // row of the tile
+        uint32_t it = 0;
+        float4 cur[8], nxt[8];
+        auto fetch = [&](float4(&dst)[8], unsigned long long tile) {
+            const unsigned long long row = tile * BM + r;
+            if (tile < n_tiles && row < P.n) {
+                const float4 *src = reinterpret_cast<const float4 *>(P.x + row * P.ld + (size_t)g * 32);
 #pragma unroll
-            for (int i = 0; i < SDW; ++i) xnext[i] = 0.0f;
-            if (valid && team < m) load_slice<SDW>(xnext, P.x + row * P.ld + (size_t)team * SDW, P.x_vec4 != 0);
-            // previous assignments of this row (training): one byte per sub-space, fetched once per tile
-            uint32_t oldc[4] = {0, 0, 0, 0};
-            if (TRAIN && valid) {
-                const uint8_t *oc = reinterpret_cast<const uint8_t *>(P.codes) + row * (unsigned long long)m;
-                if (m == 16) {
-                    const uint4 v = *reinterpret_cast<const uint4 *>(oc);
-                    oldc[0] = v.x, oldc[1] = v.y, oldc[2] = v.z, oldc[3] = v.w;
-                } else {
-                    for (int t = 0; t < m; ++t) oldc[t >> 2] |= (uint32_t)oc[t] << ((t & 3) * 8);
-                }
+                for (int i = 0; i < 8; ++i) dst[i] = __ldg(src + i);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            for (int s = team; s < m && !*abort_flag; s += 2, ++uu) {
-                const uint32_t b = (uint32_t)team;
-                float x[SDW];
+        };
+        if (nact > 0) fetch(nxt, tile0);
+        for (unsigned long long tile = tile0; nact > 0 && tile < n_tiles && !*abort_flag; tile += tstep) {
 #pragma unroll
-                for (int i = 0; i < SDW; ++i) x[i] = xnext[i];
-                if (valid && s + 2 < m) load_slice<SDW>(xnext, P.x + row * P.ld + (size_t)(s + 2) * SDW, P.x_vec4 != 0);
-                const float *hns = hn_s + (size_t)s * BN;
-                if (!mbar_wait(&bars->tfull[b], uu & 1u, abort_flag, Q.error, 15)) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + b * BN;
-                if (TRAIN && P.active && P.active[s] == 0) { // retired sub-space: hand the accumulator back untouched
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&bars->tempty[b]);
+            for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
+            fetch(nxt, tile + tstep);
+            bool ok = true;
+#pragma unroll
+            for (int ss4 = 0; ss4 < 4; ++ss4) { // static indexing of cur[]; issue order 0, 2, 1, 3
+                const int ss = issue_order(ss4);
+                if (pos[ss] < 0 || !ok) continue;
+                const int st = it % NSTAGE;
+                if (!mbar_wait(&bars->aempty[st], ((it / NSTAGE) & 1u) ^ 1u, abort_flag, Q.error, 11)) {
+                    ok = false;
                     continue;
                 }
+                const float4 v0 = cur[2 * ss], v1 = cur[2 * ss + 1];
+                const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                float hi[8], lo[8], sq = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    hi[i] = to_tf32(v[i]);
+                    lo[i] = to_tf32(v[i] - hi[i]);
+                    sq = fmaf(v[i], v[i], sq);
+                }
+                unsigned char *rowp = a_smem + (size_t)st * A_STAGE_BYTES + (size_t)r * 128;
+                const int sw = r & 7;
+                const float4 h0 = make_float4(hi[0], hi[1], hi[2], hi[3]), h1 = make_float4(hi[4], hi[5], hi[6], hi[7]);
+                *reinterpret_cast<float4 *>(rowp + ((0 ^ sw) << 4)) = h0;
+                *reinterpret_cast<float4 *>(rowp + ((1 ^ sw) << 4)) = h1;
+                *reinterpret_cast<float4 *>(rowp + ((2 ^ sw) << 4)) = h0;
+                *reinterpret_cast<float4 *>(rowp + ((3 ^ sw) << 4)) = h1;
+                *reinterpret_cast<float4 *>(rowp + ((4 ^ sw) << 4)) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<float4 *>(rowp + ((5 ^ sw) << 4)) = make_float4(lo[4], lo[5], lo[6], lo[7]);
+                *reinterpret_cast<float4 *>(rowp + ((6 ^ sw) << 4)) = make_float4(1.0f, 1.0f, 0.0f, 0.0f);
+                *reinterpret_cast<float4 *>(rowp + ((7 ^ sw) << 4)) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                xh_ring[(it & (XH_RING - 1)) * BM + r] = 0.5f * sq;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic writes -> visible to the MMA's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->afull[st]);
+                ++it;
+            }
+            if (!ok) break;
+        }
+    } else {
+        // ------------------------------------------------ epilogue
+        const int q = warp & 3;           // TMEM lane quadrant
+        const int team = (warp - 6) >> 2; // accumulator and sub-space pair
+        const int nch = (k + 31) >> 5;    // 32-column chunks that hold centroids
+        uint32_t uu = 0, moved_mask = 0, tile_iter = 0;
+        for (unsigned long long tile = tile0; nact > 0 && tile < n_tiles && !*abort_flag; tile += tstep, ++tile_iter) {
+            const unsigned long long row = tile * BM + 32ull * q + lane;
+            const bool valid = row < P.n;
+            uint32_t old2 = 0;
+            if (TRAIN && valid) old2 = *reinterpret_cast<const uint16_t *>(reinterpret_cast<const uint8_t *>(P.codes) + row * (unsigned long long)m + g * 4 + team * 2);
+            int idxs[2] = {0, 0};
+            uint32_t marked = 0, done = 0;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int ss = team * 2 + h;
+                if (pos[ss] < 0) continue;
+                const int s = g * 4 + ss;
+                const uint32_t it = tile_iter * (uint32_t)nact + (uint32_t)pos[ss];
+                if (!mbar_wait(&bars->tfull[team], uu & 1u, abort_flag, Q.error, 15)) break;
+                ++uu;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)team * BN;
+                const float xh2 = xh_ring[(it & (XH_RING - 1)) * BM + 32 * q + lane];
+                const float hmax2 = 2.0f * Q.hnmax[s];
 
                 // pass 1: the smallest score (two independent 3-input min chains)
-                float b0 = PQ_INF, b1 = PQ_INF;
+                float b0 = VQB_INF, b1 = VQB_INF;
                 bool col0_nan = false;
                 uint32_t ra[32], rb[32];
                 tmem_ld32_issue(taddr, ra);
                 tmem_wait();
-#pragma unroll 1
+#pragma unroll
                 for (int cb = 0; cb < BN / 32; cb += 2) {
-                    tmem_ld32_issue(taddr + (cb + 1) * 32, rb);
-                    if (cb == 0) {
-                        const float sc0 = hns[0] - __uint_as_float(ra[0]);
-                        col0_nan = !(sc0 == sc0);
-                    }
+                    if (cb < nch) {
+                        if (cb + 1 < nch) tmem_ld32_issue(taddr + (cb + 1) * 32, rb);
+                        if (cb == 0) {
+                            const float s0 = __uint_as_float(ra[0]);
+                            col0_nan = !(s0 == s0);
+                        }
 #pragma unroll
-                    for (int t = 0; t < 32; t += 4) {
-                        b0 = min3f(b0, hns[cb * 32 + t] - __uint_as_float(ra[t]), hns[cb * 32 + t + 1] - __uint_as_float(ra[t + 1]));
-                        b1 = min3f(b1, hns[cb * 32 + t + 2] - __uint_as_float(ra[t + 2]), hns[cb * 32 + t + 3] - __uint_as_float(ra[t + 3]));
+                        for (int t = 0; t < 32; t += 4) {
+                            b0 = min3f(b0, __uint_as_float(ra[t]), __uint_as_float(ra[t + 1]));
+                            b1 = min3f(b1, __uint_as_float(ra[t + 2]), __uint_as_float(ra[t + 3]));
+                        }
+                        tmem_wait();
                     }
-                    tmem_wait();
-                    if (cb + 2 < BN / 32) tmem_ld32_issue(taddr + (cb + 2) * 32, ra);
+                    if (cb + 1 < nch) {
+                        if (cb + 2 < nch) tmem_ld32_issue(taddr + (cb + 2) * 32, ra);
 #pragma unroll
-                    for (int t = 0; t < 32; t += 4) {
-                        b0 = min3f(b0, hns[(cb + 1) * 32 + t] - __uint_as_float(rb[t]), hns[(cb + 1) * 32 + t + 1] - __uint_as_float(rb[t + 1]));
-                        b1 = min3f(b1, hns[(cb + 1) * 32 + t + 2] - __uint_as_float(rb[t + 2]), hns[(cb + 1) * 32 + t + 3] - __uint_as_float(rb[t + 3]));
+                        for (int t = 0; t < 32; t += 4) {
+                            b0 = min3f(b0, __uint_as_float(rb[t]), __uint_as_float(rb[t + 1]));
+                            b1 = min3f(b1, __uint_as_float(rb[t + 2]), __uint_as_float(rb[t + 3]));
+                        }
+                        tmem_wait();
                     }
-                    tmem_wait();
                 }
                 const float best = fminf(b0, b1);
-                float xn2 = 0.0f;
-#pragma unroll
-                for (int i = 0; i < SDW; ++i) xn2 = fmaf(x[i], x[i], xn2);
-                xn2 *= 1.00001f;
-                const float cmax = cmax_s[s];
-                const float e2 = 2.0f * 2.0e-3f * sqrtf(xn2) * cmax + 1e-6f * cmax * cmax;
-                const float d_a = fmaxf(xn2 + 2.0f * best + e2, 0.0f);
-                const float limit = best + e2 + 1.05f * 14.0f * 5.9604645e-8f * d_a + 2.4e-7f * (fabsf(best) + e2) + 1e-36f;
-                // rows the comparisons cannot rank (NaN / infinity, or centroid 0 not comparable) are scanned in full
-                const bool scan_all = col0_nan || !(best < PQ_INF) || !(limit == limit) || !(fabsf(limit) < PQ_INF);
+                const float limit = best + (MARGIN_COEF * (xh2 + hmax2 + fabsf(best)) + 1e-36f);
+                // rows the test below cannot rank: NaN / infinity anywhere that matters, or values too small to scale
+                const bool rankable = !col0_nan && (fabsf(limit) >= 8.6736174e-19f /* 2^-60 */) && (fabsf(limit) < VQB_INF);
+                const uint32_t eb = (__float_as_uint(limit) >> 23) & 0xFFu;
+                const float nbig = __uint_as_float(0x80000000u | ((314u - eb) << 23)); // -2^(60 - exponent(limit))
+                const float lb = -limit * nbig;                                       // exact scaling
 
-                // pass 2: candidate bits (sign of limit - S shifted in; reversed and inverted afterwards)
-                uint32_t words[BN / 32];
+                // pass 2: sum over the scores below the limit of (1 + j / 512)
+                float acc0 = 0.0f, acc1 = 0.0f;
                 tmem_ld32_issue(taddr, ra);
                 tmem_wait();
 #pragma unroll
                 for (int cb = 0; cb < BN / 32; cb += 2) {
-                    tmem_ld32_issue(taddr + (cb + 1) * 32, rb);
-                    uint32_t me = 0, mo = 0;
+                    if (cb < nch) {
+                        if (cb + 1 < nch) tmem_ld32_issue(taddr + (cb + 1) * 32, rb);
 #pragma unroll
-                    for (int t = 0; t < 32; t += 2) {
-                        me = __funnelshift_l(__float_as_uint(limit - (hns[cb * 32 + t] - __uint_as_float(ra[t]))), me, 1);
-                        mo = __funnelshift_l(__float_as_uint(limit - (hns[cb * 32 + t + 1] - __uint_as_float(ra[t + 1]))), mo, 1);
+                        for (int t = 0; t < 32; t += 2) {
+                            acc0 = fmaf(fma_sat(__uint_as_float(ra[t]), nbig, lb), 1.0f + (float)(cb * 32 + t) * 0.001953125f, acc0);
+                            acc1 = fmaf(fma_sat(__uint_as_float(ra[t + 1]), nbig, lb), 1.0f + (float)(cb * 32 + t + 1) * 0.001953125f, acc1);
+                        }
+                        tmem_wait();
                     }
-                    words[cb] = me | (mo << 16);
-                    tmem_wait();
-                    if (cb + 2 < BN / 32) tmem_ld32_issue(taddr + (cb + 2) * 32, ra);
-                    me = 0, mo = 0;
+                    if (cb + 1 < nch) {
+                        if (cb + 2 < nch) tmem_ld32_issue(taddr + (cb + 2) * 32, ra);
 #pragma unroll
-                    for (int t = 0; t < 32; t += 2) {
-                        me = __funnelshift_l(__float_as_uint(limit - (hns[(cb + 1) * 32 + t] - __uint_as_float(rb[t]))), me, 1);
-                        mo = __funnelshift_l(__float_as_uint(limit - (hns[(cb + 1) * 32 + t + 1] - __uint_as_float(rb[t + 1]))), mo, 1);
+                        for (int t = 0; t < 32; t += 2) {
+                            acc0 = fmaf(fma_sat(__uint_as_float(rb[t]), nbig, lb), 1.0f + (float)((cb + 1) * 32 + t) * 0.001953125f, acc0);
+                            acc1 = fmaf(fma_sat(__uint_as_float(rb[t + 1]), nbig, lb), 1.0f + (float)((cb + 1) * 32 + t + 1) * 0.001953125f, acc1);
+                        }
+                        tmem_wait();
                     }
-                    words[cb + 1] = me | (mo << 16);
-                    tmem_wait();
+                }
+                if (Q.dbg_scores) { // diagnostic dump of the raw scores
+                    for (int cb = 0; cb < nch; ++cb) {
+                        tmem_ld32_issue(taddr + cb * 32, ra);
+                        tmem_wait();
+                        if (valid) {
+                            float *o = Q.dbg_scores + ((size_t)row * m + s) * BN + cb * 32;
+#pragma unroll
+                            for (int t = 0; t < 32; ++t) o[t] = __uint_as_float(ra[t]);
+                        }
+                    }
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&bars->tempty[b]);
+                if (lane == 0) mbar_arrive(&bars->tempty[team]);
 
-                if (valid) {
-                    // decode: low half holds even columns, high half odd columns, each most-recent-first and inverted
-                    int idx = 0, cnt = 0;
-                    float bd = PQ_INF;
-                    int bi = -1;
-                    const unsigned char *cs = c_smem + (size_t)s * CB_BYTES; // 32B-swizzled: row j at (j/8)*256 + (j%8)*32, halves swapped when (j & 4)
-                    auto exact = [&](int j) {
-                        const unsigned char *rowp = cs + (size_t)(j >> 3) * 256 + (size_t)(j & 7) * 32;
-                        const int sw = ((j >> 2) & 1) * 16;
-                        const float4 lo = *reinterpret_cast<const float4 *>(rowp + sw), hi = *reinterpret_cast<const float4 *>(rowp + (16 - sw));
-                        const float c[SDW] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-                        float d = reg_dist<SDW, M_SQ>(x, c, 0.0f, 0.0f, 0.0f);
-                        if (EUCLID) d = __fsqrt_rn(d);
-                        if (j == 0) { // the reference's scan starts at centroid 0 whatever its value
-                            bd = d;
-                            bi = 0;
-                        } else {
-                            argmin_update(d, j, bd, bi);
+                const float acc = acc0 + acc1;
+                const bool single = rankable && acc >= 1.0f && acc < 1.5f;
+                idxs[h] = single ? (int)((acc - 1.0f) * 512.0f + 0.5f) : 0;
+                if (!single || idxs[h] >= k) marked |= 1u << h;
+                done |= 1u << h;
+            }
+
+            if (valid && done) {
+                if (marked) {
+                    Q.marks[row * (unsigned long long)(m >> 1) + g * 2 + team] = (uint8_t)marked;
+                    atomicAdd(Q.stats, (unsigned long long)__popc(marked));
+                }
+                if (TRAIN) {
+                    uint8_t *cp = reinterpret_cast<uint8_t *>(P.codes) + row * (unsigned long long)m + g * 4 + team * 2;
+                    if (done == 3u && marked == 0u) {
+                        const uint32_t nw = (uint32_t)idxs[0] | ((uint32_t)idxs[1] << 8);
+                        if (nw != old2) {
+                            if ((nw ^ old2) & 0xFFu) moved_mask |= 1u << (team * 2);
+                            if ((nw ^ old2) & 0xFF00u) moved_mask |= 1u << (team * 2 + 1);
+                            *reinterpret_cast<uint16_t *>(cp) = (uint16_t)nw;
                         }
-                    };
-#pragma unroll 1
-                    for (int wd = 0; wd < BN / 32; ++wd) {
-                        uint32_t cand = 0;
-                        if (scan_all) {
-                            cand = 0xFFFFFFFFu;
-                        } else {
-                            const uint32_t inv = ~words[wd];
-                            uint32_t xe = __brev(inv << 16) & 0xFFFFu, xo = __brev(inv & 0xFFFF0000u) & 0xFFFFu; // bit i = column 2i (+1)
-                            xe = (xe | (xe << 8)) & 0x00FF00FFu;
-                            xe = (xe | (xe << 4)) & 0x0F0F0F0Fu;
-                            xe = (xe | (xe << 2)) & 0x33333333u;
-                            xe = (xe | (xe << 1)) & 0x55555555u;
-                            xo = (xo | (xo << 8)) & 0x00FF00FFu;
-                            xo = (xo | (xo << 4)) & 0x0F0F0F0Fu;
-                            xo = (xo | (xo << 2)) & 0x33333333u;
-                            xo = (xo | (xo << 1)) & 0x55555555u;
-                            cand = xe | (xo << 1);
-                        }
-                        const int lo = wd * 32;
-                        cand &= (k >= lo + 32) ? 0xFFFFFFFFu : ((k > lo) ? ((1u << (k - lo)) - 1u) : 0u);
-                        while (cand) {
-                            const int j = lo + __ffs(cand) - 1;
-                            cand &= cand - 1;
-                            ++cnt;
-                            if (cnt == 1) idx = j;              // a lone candidate needs no arithmetic
-                            if (cnt == 2) exact(idx);           // a second one: now the first needs its exact distance too
-                            if (cnt >= 2) exact(j);
-                        }
-                    }
-                    if (cnt >= 2) idx = bi < 0 ? 0 : bi;
-                    if (cnt == 0) idx = 0;
-                    if (TRAIN) {
-                        const uint32_t old = (oldc[s >> 2] >> ((s & 3) * 8)) & 0xFFu;
-                        if (old != (uint32_t)idx) moved_mask |= 1u << s;
-                        reinterpret_cast<uint8_t *>(P.codes)[row * (unsigned long long)m + s] = (uint8_t)idx;
                     } else {
-                        // the chosen centroid's values come from the shared-memory copy (src/pq.rs:176-180)
-                        const unsigned char *rowp = cs + (size_t)(idx >> 3) * 256 + (size_t)(idx & 7) * 32;
-                        const int sw = ((idx >> 2) & 1) * 16;
-                        const float4 lo4 = *reinterpret_cast<const float4 *>(rowp + sw), hi4 = *reinterpret_cast<const float4 *>(rowp + (16 - sw));
-                        const int dim = m * SDW;
-                        if (P.out_codes) P.out_codes[row * m + s] = (uint32_t)idx;
-                        if (P.out_f16) {
-                            uint4 pk;
-                            pk.x = f32_to_f16_bits(lo4.x) | ((uint32_t)f32_to_f16_bits(lo4.y) << 16);
-                            pk.y = f32_to_f16_bits(lo4.z) | ((uint32_t)f32_to_f16_bits(lo4.w) << 16);
-                            pk.z = f32_to_f16_bits(hi4.x) | ((uint32_t)f32_to_f16_bits(hi4.y) << 16);
-                            pk.w = f32_to_f16_bits(hi4.z) | ((uint32_t)f32_to_f16_bits(hi4.w) << 16);
-                            *reinterpret_cast<uint4 *>(P.out_f16 + row * dim + (size_t)s * SDW) = pk; // 16-byte aligned: dim % 8 == 0
-                        }
-                        if (P.out_f32) {
-                            float4 *o = reinterpret_cast<float4 *>(P.out_f32 + row * dim + (size_t)s * SDW);
-                            o[0] = lo4;
-                            o[1] = hi4;
-                        }
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+                            if ((done >> h & 1u) && !(marked >> h & 1u)) {
+                                const uint32_t ob = (old2 >> (8 * h)) & 0xFFu;
+                                if (ob != (uint32_t)idxs[h]) {
+                                    moved_mask |= 1u << (team * 2 + h);
+                                    cp[h] = (uint8_t)idxs[h];
+                                }
+                            }
                     }
+                } else {
+                    const int dim = m * SDW;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+                        if ((done >> h & 1u) && !(marked >> h & 1u)) {
+                            const int s = g * 4 + team * 2 + h;
+                            const int idx = idxs[h];
+                            if (P.out_codes) P.out_codes[row * m + s] = (uint32_t)idx;
+                            if (P.out_f16) // 16-byte aligned: dim % 8 == 0
+                                *reinterpret_cast<uint4 *>(P.out_f16 + row * dim + (size_t)s * SDW) = __ldg(Q.c16 + (size_t)s * BN + idx);
+                            if (P.out_f32) {
+                                const float4 *c = reinterpret_cast<const float4 *>(P.centroids + ((size_t)s * k + idx) * SDW);
+                                float4 *o = reinterpret_cast<float4 *>(P.out_f32 + row * dim + (size_t)s * SDW);
+                                o[0] = __ldg(c);
+                                o[1] = __ldg(c + 1);
+                            }
+                        }
                 }
             }
         }
         if (TRAIN) {
             moved_mask = __reduce_or_sync(0xffffffffu, moved_mask);
             if (lane == 0)
-                for (int s = 0; s < m; ++s)
-                    if (moved_mask & (1u << s)) atomicOr(P.changed + s, 1u);
+                for (int ss = 0; ss < 4; ++ss)
+                    if (moved_mask & (1u << ss)) atomicOr(P.changed + g * 4 + ss, 1u);
         }
     }
 
@@ -353,26 +413,123 @@ __global__ void __launch_bounds__(320, 1) pq_tc_kernel(const __grid_constant__ C
     }
 }
 
-// per sub-space: |c_j|^2/2 (+inf beyond k) and max_j |c_j|
-__global__ void pq_codebook_norms_kernel(const float *cb, int m, int k, float *hn, float *cmax)
+// Operand B of one sub-space per block (thread j = centroid j): 32 TF32 numbers per centroid
+//   [-ch(8) | -cl(8) | -ch(8) | hn_h, hn_l, 0 ...]   (columns beyond k: zeros and a huge score),
+// the binary16 image of the centroid (what an encode writes, src/pq.rs:176-180) and max_j hn_j.
+__global__ void pq_operand_b_kernel(const float *cb, int k, float *bop, uint4 *c16, float *hnmax)
 {
-    __shared__ float smax[256];
+    __shared__ float smax[BN];
     const int s = blockIdx.x, j = threadIdx.x;
-    float a = 0.0f;
-    if (j < k) {
-        const float *c = cb + ((size_t)s * k + j) * SDW;
+    float4 out[8];
 #pragma unroll
-        for (int i = 0; i < SDW; ++i) a = fmaf(c[i], c[i], a);
+    for (int i = 0; i < 8; ++i) out[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float hn = 0.0f;
+    uint4 img = make_uint4(0, 0, 0, 0);
+    if (j < k) {
+        const float4 *c = reinterpret_cast<const float4 *>(cb + ((size_t)s * k + j) * SDW);
+        const float4 c0 = c[0], c1 = c[1];
+        const float v[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        float hi[8], lo[8], a = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            hi[i] = to_tf32(v[i]);
+            lo[i] = to_tf32(v[i] - hi[i]);
+            a = fmaf(v[i], v[i], a);
+        }
+        hn = 0.5f * a;
+        const float hh = to_tf32(hn), hl = to_tf32(hn - hh);
+        out[0] = out[4] = make_float4(-hi[0], -hi[1], -hi[2], -hi[3]);
+        out[1] = out[5] = make_float4(-hi[4], -hi[5], -hi[6], -hi[7]);
+        out[2] = make_float4(-lo[0], -lo[1], -lo[2], -lo[3]);
+        out[3] = make_float4(-lo[4], -lo[5], -lo[6], -lo[7]);
+        out[6] = make_float4(hh, hl, 0.f, 0.f);
+        img.x = f32_to_f16_bits(v[0]) | ((uint32_t)f32_to_f16_bits(v[1]) << 16);
+        img.y = f32_to_f16_bits(v[2]) | ((uint32_t)f32_to_f16_bits(v[3]) << 16);
+        img.z = f32_to_f16_bits(v[4]) | ((uint32_t)f32_to_f16_bits(v[5]) << 16);
+        img.w = f32_to_f16_bits(v[6]) | ((uint32_t)f32_to_f16_bits(v[7]) << 16);
+    } else {
+        out[6] = make_float4(to_tf32(PAD_SCORE), 0.f, 0.f, 0.f);
     }
-    hn[(size_t)s * BN + j] = (j < k) ? 0.5f * a : PQ_INF;
-    smax[j] = (j < k) ? sqrtf(a) : 0.0f;
+    float4 *o = reinterpret_cast<float4 *>(bop + ((size_t)s * BN + j) * KOP);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = out[i];
+    c16[(size_t)s * BN + j] = img;
+    smax[j] = (j < k) ? fabsf(hn) : 0.0f;
     __syncthreads();
-    for (int o = 128; o > 0; o >>= 1) {
-        if (j < o) smax[j] = fmaxf(smax[j], smax[j + o]);
+    for (int o2 = BN / 2; o2 > 0; o2 >>= 1) {
+        if (j < o2) smax[j] = fmaxf(smax[j], smax[j + o2]); // a NaN half norm is dropped here; its column scores NaN and is never counted
         __syncthreads();
     }
-    if (j == 0) cmax[s] = smax[0] * 1.000001f;
-    (void)m;
+    if (j == 0) hnmax[s] = smax[0];
+}
+
+// The marked (row, sub-space) pairs: one warp per pair scans all centroids with the reference's arithmetic
+// (src/utils.rs:59-73, src/pq.rs:159-182): strict '<' in ascending index from centroid 0, so a NaN distance never wins
+// unless it is centroid 0's, and equal distances keep the lowest index.
+template <bool TRAIN, bool EUCLID> __global__ void __launch_bounds__(256) pq_marked_kernel(const PqTcParams Q)
+{
+    const AssignParams &P = Q.a;
+    const int lane = threadIdx.x & 31;
+    const int m = P.m, k = P.k, half = m >> 1;
+    const unsigned long long total = P.n * (unsigned long long)half;
+    const unsigned long long nwarps = (unsigned long long)gridDim.x * (blockDim.x >> 5);
+    uint32_t moved_lo = 0, moved_hi = 0;
+    for (unsigned long long base = ((unsigned long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 32ull; base < total; base += nwarps * 32ull) {
+        const unsigned long long mine = base + lane;
+        const uint32_t f = mine < total ? Q.marks[mine] : 0u;
+        uint32_t pending = __ballot_sync(0xffffffffu, f != 0u);
+        while (pending) {
+            const int src = __ffs(pending) - 1;
+            pending &= pending - 1;
+            const uint32_t bits = __shfl_sync(0xffffffffu, f, src);
+            const unsigned long long e = base + src;
+            const unsigned long long row = e / half;
+            const int rem = (int)(e % half);
+            for (int h = 0; h < 2; ++h) {
+                if (!(bits >> h & 1u)) continue;
+                const int s = (rem >> 1) * 4 + (rem & 1) * 2 + h;
+                float x[SDW];
+                load_slice<SDW>(x, P.x + row * P.ld + (size_t)s * SDW, P.x_vec4 != 0);
+                const float *cbs = P.centroids + (size_t)s * k * SDW;
+                float bd = VQB_INF, d0 = 0.0f;
+                int bi = 0x7fffffff;
+                for (int j = lane; j < k; j += 32) {
+                    float c[SDW];
+                    load_centroid<SDW>(c, cbs + (size_t)j * SDW);
+                    float d = reg_dist<SDW, M_SQ>(x, c, 0.0f, 0.0f, 0.0f);
+                    if (EUCLID) d = __fsqrt_rn(d);
+                    if (j == 0) d0 = d;
+                    if (d < bd) {
+                        bd = d;
+                        bi = j;
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float od = __shfl_xor_sync(0xffffffffu, bd, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                    if (od < bd || (od == bd && oi < bi)) {
+                        bd = od;
+                        bi = oi;
+                    }
+                }
+                d0 = __shfl_sync(0xffffffffu, d0, 0);
+                int idx = (bi == 0x7fffffff || !(d0 == d0)) ? 0 : bi; // nothing below +inf, or the scan started at a NaN
+                if (lane == 0) {
+                    bool moved = false;
+                    store_result<SDW, uint8_t, TRAIN>(P, row, s, idx, cbs, moved);
+                    if (moved) {
+                        if (s < 32) moved_lo |= 1u << s;
+                        else moved_hi |= 1u << (s - 32);
+                    }
+                }
+            }
+        }
+    }
+    if (TRAIN && lane == 0) {
+        for (int s = 0; s < m; ++s)
+            if ((s < 32 ? moved_lo >> s : moved_hi >> (s - 32)) & 1u) atomicOr(P.changed + s, 1u);
+    }
 }
 
 } // namespace
@@ -380,52 +537,72 @@ __global__ void pq_codebook_norms_kernel(const float *cb, int m, int k, float *h
 bool pq_tc_applicable(const AssignParams &p, int metric)
 {
     return (metric == M_SQ || metric == M_EUCLID) && p.sd == SDW && p.m >= 4 && p.m <= MAXM && p.m % 4 == 0 && p.k >= 2 && p.k <= BN &&
-           p.ld == (unsigned long long)p.m * SDW && (reinterpret_cast<uintptr_t>(p.x) & 15u) == 0 && p.n >= 1 &&
-           (reinterpret_cast<uintptr_t>(p.codes) & 15u) == 0 && (reinterpret_cast<uintptr_t>(p.out_f16) & 15u) == 0 &&
+           p.ld % 4 == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15u) == 0 && p.n >= 1 && (reinterpret_cast<uintptr_t>(p.codes) & 1u) == 0 &&
+           (reinterpret_cast<uintptr_t>(p.centroids) & 15u) == 0 && (reinterpret_cast<uintptr_t>(p.out_f16) & 15u) == 0 &&
            (reinterpret_cast<uintptr_t>(p.out_f32) & 15u) == 0;
 }
 
-size_t pq_tc_scratch_floats() { return (size_t)MAXM * BN + MAXM; }
+size_t pq_tc_scratch_floats() { return SCRATCH_FLOATS; }
+size_t pq_tc_stats_offset_floats() { return OFF_STATS; }
 
-template <typename CodeT, bool TRAIN, bool EUCLID>
-static void launch_t(CudaDevice &dev, const CUtensorMap &mx, const CUtensorMap &mc, const PqTcParams &q, size_t smem, unsigned grid)
+template <bool TRAIN, bool EUCLID>
+static void launch_t(CudaDevice &dev, const CUtensorMap &mb, const PqTcParams &q, size_t smem, unsigned grid)
 {
-    auto kernel = pq_tc_kernel<CodeT, TRAIN, EUCLID>;
-    VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    KernelScope ks(dev, TRAIN ? "assign_train" : "pq_encode");
-    kernel<<<grid, 320, smem, dev.stream()>>>(mx, mc, q);
-    VQB_CUDA_CHECK(cudaGetLastError());
-    dev.count_launch();
-}
-
-void launch_pq_tc(CudaDevice &dev, const AssignParams &p, int metric, bool train, size_t code_bytes, float *scratch, int *error_word)
-{
+    auto kernel = pq_tc_kernel<TRAIN, EUCLID>;
+    static bool configured = false; // one device context per process configuration; the attribute is sticky per function
+    if (!configured) {
+        VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
     {
-        KernelScope ks(dev, "codebook_norms");
-        pq_codebook_norms_kernel<<<p.m, 256, 0, dev.stream()>>>(p.centroids, p.m, p.k, scratch, scratch + (size_t)MAXM * BN);
+        KernelScope ks(dev, TRAIN ? "assign_train" : "pq_encode");
+        kernel<<<grid, NTHREADS, smem, dev.stream()>>>(mb, q);
         VQB_CUDA_CHECK(cudaGetLastError());
         dev.count_launch();
     }
-    const CUtensorMap mx = make_tensor_map_2d(p.x, (unsigned long long)p.ld, p.n, CHUNK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
-    const CUtensorMap mc = make_tensor_map_2d(p.centroids, SDW, (unsigned long long)p.m * p.k, SDW, BN, CU_TENSOR_MAP_SWIZZLE_32B);
+    {
+        KernelScope ks(dev, TRAIN ? "assign_train_marked" : "pq_encode_marked");
+        pq_marked_kernel<TRAIN, EUCLID><<<dev.sm_count() * 4, 256, 0, dev.stream()>>>(q);
+        VQB_CUDA_CHECK(cudaGetLastError());
+        dev.count_launch();
+    }
+}
+
+void launch_pq_tc(CudaDevice &dev, const AssignParams &p, int metric, bool train, size_t code_bytes, float *scratch, int *error_word,
+                  float *dbg_scores)
+{
+    if (train && code_bytes != 1) throw Error(100, "pq tensor path: one-byte codes expected for k <= 256");
+    float *bop = scratch + OFF_BOP;
+    uint4 *c16 = reinterpret_cast<uint4 *>(scratch + OFF_C16);
+    float *hnmax = scratch + OFF_HMAX;
+    unsigned long long *stats = reinterpret_cast<unsigned long long *>(scratch + OFF_STATS);
+    {
+        KernelScope ks(dev, "pq_operand_b");
+        pq_operand_b_kernel<<<p.m, BN, 0, dev.stream()>>>(p.centroids, p.k, bop, c16, hnmax);
+        VQB_CUDA_CHECK(cudaGetLastError());
+        dev.count_launch();
+    }
+    const size_t mark_bytes = (size_t)p.n * (size_t)(p.m / 2);
+    uint8_t *marks = static_cast<uint8_t *>(dev.alloc(mark_bytes));
+    dev.zero(marks, mark_bytes);
+    const CUtensorMap mb = make_tensor_map_2d(bop, KOP, (unsigned long long)p.m * BN, KOP, BN, CU_TENSOR_MAP_SWIZZLE_128B);
     PqTcParams q;
     q.a = p;
-    q.hn = scratch;
-    q.cmax = scratch + (size_t)MAXM * BN;
+    q.c16 = c16;
+    q.hnmax = hnmax;
+    q.marks = marks;
+    q.stats = stats;
     q.error = error_word;
-    const size_t smem = 1024 + (size_t)MAXM * CB_BYTES + (size_t)NSTAGE * X_STAGE_BYTES + ((size_t)MAXM * BN + MAXM) * sizeof(float) + sizeof(PqBarriers) + 64;
+    q.dbg_scores = dbg_scores;
+    const size_t smem = 1024 + 4 * (size_t)B_BYTES + (size_t)NSTAGE * A_STAGE_BYTES + (size_t)XH_RING * BM * sizeof(float) + sizeof(PqBarriers) + 64;
     const unsigned long long tiles = (p.n + BM - 1) / BM;
-    const unsigned grid = (unsigned)std::min<unsigned long long>(tiles, (unsigned long long)dev.sm_count());
-    const bool eu = metric == M_EUCLID;
-    if (train) {
-        if (code_bytes == 1) launch_t<uint8_t, true, false>(dev, mx, mc, q, smem, grid);
-        else if (code_bytes == 2) launch_t<uint16_t, true, false>(dev, mx, mc, q, smem, grid);
-        else launch_t<uint32_t, true, false>(dev, mx, mc, q, smem, grid);
-    } else if (eu) {
-        launch_t<uint32_t, false, true>(dev, mx, mc, q, smem, grid);
-    } else {
-        launch_t<uint32_t, false, false>(dev, mx, mc, q, smem, grid);
-    }
+    const unsigned ngroups = (unsigned)p.m / 4;
+    const unsigned per = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>(tiles, (unsigned long long)dev.sm_count() / ngroups));
+    const unsigned grid = per * ngroups;
+    if (train) launch_t<true, false>(dev, mb, q, smem, grid);
+    else if (metric == M_EUCLID) launch_t<false, true>(dev, mb, q, smem, grid);
+    else launch_t<false, false>(dev, mb, q, smem, grid);
+    dev.release(marks);
 }
 
 } // namespace vqb
