@@ -37,6 +37,7 @@
 //                sub-spaces 2t, 2t+1 of the group through accumulator t
 // Every wait is bounded; on expiry the CTA records a code, stops issuing, frees tensor memory and the host raises an error.
 #include <algorithm>
+#include <cstdio>
 
 #include "assign_reg.cuh"
 #include "cuda_device.hpp"
@@ -77,6 +78,15 @@ struct PqTcParams {
     float *dbg_scores; // optional [n][m][256]
 };
 
+#ifdef VQB_PQ_PROFILE
+__device__ unsigned long long g_prof[16];
+#define PROF_T0 long long _t0 = clock64()
+#define PROF_ADD(i) do { long long _t1 = clock64(); if (blockIdx.x == 0 && lane == 0) atomicAdd(&g_prof[i], (unsigned long long)(_t1 - _t0)); _t0 = _t1; } while (0)
+#else
+#define PROF_T0
+#define PROF_ADD(i)
+#endif
+
 __device__ __forceinline__ float to_tf32(float v)
 {
     uint32_t r;
@@ -87,8 +97,15 @@ __device__ __forceinline__ float to_tf32(float v)
 __device__ __forceinline__ float fma_sat(float a, float b, float c)
 {
     float d;
-    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    asm volatile("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); // volatile: stays between the tensor-memory load and its wait
     return d;
+}
+
+__device__ __forceinline__ float min3v(float a, float b, float c)
+{
+    float r;
+    asm volatile("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
 }
 
 // order in which the four sub-spaces of a group are issued: accumulator / team = ss >> 1 alternates
@@ -103,7 +120,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
     unsigned char *b_smem = base;                                           // 4 x 32 KiB
     unsigned char *a_smem = base + 4 * (size_t)B_BYTES;                     // NSTAGE x 16 KiB
     float *xh_ring = reinterpret_cast<float *>(a_smem + (size_t)NSTAGE * A_STAGE_BYTES); // [XH_RING][128]
-    PqBarriers *bars = reinterpret_cast<PqBarriers *>(xh_ring + XH_RING * BM);
+    const uint4 *c16_s = reinterpret_cast<const uint4 *>(xh_ring + XH_RING * BM);         // [4][256] binary16 images
+    PqBarriers *bars = reinterpret_cast<PqBarriers *>(xh_ring + XH_RING * BM + 4 * BN * 4);
     volatile int *abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -151,8 +169,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
     if (warp == 0) {
         // ------------------------------------------------ operand B: the group's four sub-spaces, once
         if (lane == 0 && nact > 0) {
-            mbar_expect_tx(&bars->bfull, 4 * B_BYTES);
+            mbar_expect_tx(&bars->bfull, 4 * B_BYTES + (TRAIN ? 0u : 4u * BN * 16u));
             for (int ss = 0; ss < 4; ++ss) tma_load_2d(b_smem + (size_t)ss * B_BYTES, &map_b, 0, (g * 4 + ss) * BN, &bars->bfull);
+            if (!TRAIN) bulk_load_1d(const_cast<uint4 *>(c16_s), Q.c16 + (size_t)g * 4 * BN, 4u * BN * 16u, &bars->bfull);
         }
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer
@@ -164,11 +183,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                     const int ss = list[p];
                     const uint32_t b = (uint32_t)ss >> 1;
                     const int st = it % NSTAGE;
-                    if (!mbar_wait(&bars->afull[st], (it / NSTAGE) & 1u, abort_flag, Q.error, 14) ||
-                        !mbar_wait(&bars->tempty[b], (uses[b] & 1u) ^ 1u, abort_flag, Q.error, 13)) {
+                    PROF_T0;
+                    if (!mbar_wait(&bars->afull[st], (it / NSTAGE) & 1u, abort_flag, Q.error, 14)) {
                         ok = false;
                         break;
                     }
+                    PROF_ADD(0);
+                    if (!mbar_wait(&bars->tempty[b], (uses[b] & 1u) ^ 1u, abort_flag, Q.error, 13)) {
+                        ok = false;
+                        break;
+                    }
+                    PROF_ADD(1);
                     ++uses[b];
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t adesc = smem_desc_sw128(smem_u32(a_smem + (size_t)st * A_STAGE_BYTES));
@@ -178,6 +203,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                         umma_tf32(tmem_base + b * BN, adesc + (uint64_t)(2 * k8), bdesc + (uint64_t)(2 * k8), k8 ? 1u : 0u);
                     umma_commit(&bars->aempty[st]);
                     umma_commit(&bars->tfull[b]);
+                    PROF_ADD(2);
                 }
             }
         }
@@ -208,10 +234,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                 const int ss = issue_order(ss4);
                 if (pos[ss] < 0 || !ok) continue;
                 const int st = it % NSTAGE;
+                PROF_T0;
                 if (!mbar_wait(&bars->aempty[st], ((it / NSTAGE) & 1u) ^ 1u, abort_flag, Q.error, 11)) {
                     ok = false;
                     continue;
                 }
+                if (warp == 2) PROF_ADD(3);
                 const float4 v0 = cur[2 * ss], v1 = cur[2 * ss + 1];
                 const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
                 float hi[8], lo[8], sq = 0.0f;
@@ -236,6 +264,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic writes -> visible to the MMA's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars->afull[st]);
+                if (warp == 2) PROF_ADD(4);
                 ++it;
             }
             if (!ok) break;
@@ -246,6 +275,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
         const int team = (warp - 6) >> 2; // accumulator and sub-space pair
         const int nch = (k + 31) >> 5;    // 32-column chunks that hold centroids
         uint32_t uu = 0, moved_mask = 0, tile_iter = 0;
+        const float hmax2_0 = 2.0f * Q.hnmax[g * 4 + team * 2], hmax2_1 = 2.0f * Q.hnmax[g * 4 + team * 2 + 1];
+        if (!TRAIN && nact > 0) mbar_wait(&bars->bfull, 0, abort_flag, Q.error, 16); // the f16 images arrive with operand B
+        PROF_T0;
         for (unsigned long long tile = tile0; nact > 0 && tile < n_tiles && !*abort_flag; tile += tstep, ++tile_iter) {
             const unsigned long long row = tile * BM + 32ull * q + lane;
             const bool valid = row < P.n;
@@ -253,51 +285,56 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
             if (TRAIN && valid) old2 = *reinterpret_cast<const uint16_t *>(reinterpret_cast<const uint8_t *>(P.codes) + row * (unsigned long long)m + g * 4 + team * 2);
             int idxs[2] = {0, 0};
             uint32_t marked = 0, done = 0;
-#pragma unroll
+#pragma unroll 1
             for (int h = 0; h < 2; ++h) {
                 const int ss = team * 2 + h;
                 if (pos[ss] < 0) continue;
-                const int s = g * 4 + ss;
                 const uint32_t it = tile_iter * (uint32_t)nact + (uint32_t)pos[ss];
                 if (!mbar_wait(&bars->tfull[team], uu & 1u, abort_flag, Q.error, 15)) break;
+                if (warp == 6) PROF_ADD(5);
                 ++uu;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)team * BN;
-                const float xh2 = xh_ring[(it & (XH_RING - 1)) * BM + 32 * q + lane];
-                const float hmax2 = 2.0f * Q.hnmax[s];
-
-                // pass 1: the smallest score (two independent 3-input min chains)
-                float b0 = VQB_INF, b1 = VQB_INF;
-                bool col0_nan = false;
                 uint32_t ra[32], rb[32];
                 tmem_ld32_issue(taddr, ra);
+                const float xh2 = xh_ring[(it & (XH_RING - 1)) * BM + 32 * q + lane];
+                const float hmax2 = h ? hmax2_1 : hmax2_0;
+
+                // pass 1: the smallest score (four independent 3-input min chains)
+                float b0 = VQB_INF, b1 = VQB_INF, b2 = VQB_INF, b3 = VQB_INF;
+                bool col0_nan = false;
                 tmem_wait();
-#pragma unroll
-                for (int cb = 0; cb < BN / 32; cb += 2) {
-                    if (cb < nch) {
-                        if (cb + 1 < nch) tmem_ld32_issue(taddr + (cb + 1) * 32, rb);
-                        if (cb == 0) {
-                            const float s0 = __uint_as_float(ra[0]);
-                            col0_nan = !(s0 == s0);
-                        }
-#pragma unroll
-                        for (int t = 0; t < 32; t += 4) {
-                            b0 = min3f(b0, __uint_as_float(ra[t]), __uint_as_float(ra[t + 1]));
-                            b1 = min3f(b1, __uint_as_float(ra[t + 2]), __uint_as_float(ra[t + 3]));
-                        }
-                        tmem_wait();
+#pragma unroll 1
+                for (int cb = 0; cb < nch; cb += 2) {
+                    if (cb + 1 < nch) tmem_ld32_issue(taddr + (cb + 1) * 32, rb);
+                    if (cb == 0) {
+                        const float s0 = __uint_as_float(ra[0]);
+                        col0_nan = !(s0 == s0);
                     }
+#pragma unroll
+                    for (int t = 0; t < 32; t += 8) {
+                        b0 = min3v(b0, __uint_as_float(ra[t]), __uint_as_float(ra[t + 1]));
+                        b1 = min3v(b1, __uint_as_float(ra[t + 2]), __uint_as_float(ra[t + 3]));
+                        b2 = min3v(b2, __uint_as_float(ra[t + 4]), __uint_as_float(ra[t + 5]));
+                        b3 = min3v(b3, __uint_as_float(ra[t + 6]), __uint_as_float(ra[t + 7]));
+                    }
+                    tmem_wait();
                     if (cb + 1 < nch) {
-                        if (cb + 2 < nch) tmem_ld32_issue(taddr + (cb + 2) * 32, ra);
+                        tmem_ld32_issue(taddr + (cb + 2 < nch ? cb + 2 : 0) * 32, ra); // past the end: the first chunk of pass 2
 #pragma unroll
-                        for (int t = 0; t < 32; t += 4) {
-                            b0 = min3f(b0, __uint_as_float(rb[t]), __uint_as_float(rb[t + 1]));
-                            b1 = min3f(b1, __uint_as_float(rb[t + 2]), __uint_as_float(rb[t + 3]));
+                        for (int t = 0; t < 32; t += 8) {
+                            b0 = min3v(b0, __uint_as_float(rb[t]), __uint_as_float(rb[t + 1]));
+                            b1 = min3v(b1, __uint_as_float(rb[t + 2]), __uint_as_float(rb[t + 3]));
+                            b2 = min3v(b2, __uint_as_float(rb[t + 4]), __uint_as_float(rb[t + 5]));
+                            b3 = min3v(b3, __uint_as_float(rb[t + 6]), __uint_as_float(rb[t + 7]));
                         }
-                        tmem_wait();
+                    } else {
+                        tmem_ld32_issue(taddr, ra); // odd chunk count: the first chunk of pass 2
                     }
+                    tmem_wait();
                 }
-                const float best = fminf(b0, b1);
+                if (warp == 6) PROF_ADD(6);
+                const float best = fminf(fminf(b0, b1), fminf(b2, b3));
                 const float limit = best + (MARGIN_COEF * (xh2 + hmax2 + fabsf(best)) + 1e-36f);
                 // rows the test below cannot rank: NaN / infinity anywhere that matters, or values too small to scale
                 const bool rankable = !col0_nan && (fabsf(limit) >= 8.6736174e-19f /* 2^-60 */) && (fabsf(limit) < VQB_INF);
@@ -305,37 +342,49 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                 const float nbig = __uint_as_float(0x80000000u | ((314u - eb) << 23)); // -2^(60 - exponent(limit))
                 const float lb = -limit * nbig;                                       // exact scaling
 
-                // pass 2: sum over the scores below the limit of (1 + j / 512)
-                float acc0 = 0.0f, acc1 = 0.0f;
-                tmem_ld32_issue(taddr, ra);
-                tmem_wait();
+                // pass 2: over the scores below the limit, total = sum (1 + t / 512) and offs = sum chunk * (1 + t / 512),
+                // t = column within its 32-column chunk: exactly one score below the limit <=> 1 <= total < 1.07
+                float total = 0.0f, offs = 0.0f; // chunk 0 was requested (and awaited) at the end of pass 1
+#pragma unroll 1
+                for (int cb = 0; cb < nch; cb += 2) {
+                    if (cb + 1 < nch) tmem_ld32_issue(taddr + (cb + 1) * 32, rb);
+                    {
+                        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
-                for (int cb = 0; cb < BN / 32; cb += 2) {
-                    if (cb < nch) {
-                        if (cb + 1 < nch) tmem_ld32_issue(taddr + (cb + 1) * 32, rb);
-#pragma unroll
-                        for (int t = 0; t < 32; t += 2) {
-                            acc0 = fmaf(fma_sat(__uint_as_float(ra[t]), nbig, lb), 1.0f + (float)(cb * 32 + t) * 0.001953125f, acc0);
-                            acc1 = fmaf(fma_sat(__uint_as_float(ra[t + 1]), nbig, lb), 1.0f + (float)(cb * 32 + t + 1) * 0.001953125f, acc1);
+                        for (int t = 0; t < 32; t += 4) {
+                            a0 = fmaf(fma_sat(__uint_as_float(ra[t]), nbig, lb), 1.0f + (float)t * 0.001953125f, a0);
+                            a1 = fmaf(fma_sat(__uint_as_float(ra[t + 1]), nbig, lb), 1.0f + (float)(t + 1) * 0.001953125f, a1);
+                            a2 = fmaf(fma_sat(__uint_as_float(ra[t + 2]), nbig, lb), 1.0f + (float)(t + 2) * 0.001953125f, a2);
+                            a3 = fmaf(fma_sat(__uint_as_float(ra[t + 3]), nbig, lb), 1.0f + (float)(t + 3) * 0.001953125f, a3);
                         }
-                        tmem_wait();
+                        const float cs = (a0 + a1) + (a2 + a3);
+                        total += cs;
+                        offs = fmaf(cs, (float)cb, offs);
                     }
+                    tmem_wait();
                     if (cb + 1 < nch) {
                         if (cb + 2 < nch) tmem_ld32_issue(taddr + (cb + 2) * 32, ra);
+                        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
-                        for (int t = 0; t < 32; t += 2) {
-                            acc0 = fmaf(fma_sat(__uint_as_float(rb[t]), nbig, lb), 1.0f + (float)((cb + 1) * 32 + t) * 0.001953125f, acc0);
-                            acc1 = fmaf(fma_sat(__uint_as_float(rb[t + 1]), nbig, lb), 1.0f + (float)((cb + 1) * 32 + t + 1) * 0.001953125f, acc1);
+                        for (int t = 0; t < 32; t += 4) {
+                            a0 = fmaf(fma_sat(__uint_as_float(rb[t]), nbig, lb), 1.0f + (float)t * 0.001953125f, a0);
+                            a1 = fmaf(fma_sat(__uint_as_float(rb[t + 1]), nbig, lb), 1.0f + (float)(t + 1) * 0.001953125f, a1);
+                            a2 = fmaf(fma_sat(__uint_as_float(rb[t + 2]), nbig, lb), 1.0f + (float)(t + 2) * 0.001953125f, a2);
+                            a3 = fmaf(fma_sat(__uint_as_float(rb[t + 3]), nbig, lb), 1.0f + (float)(t + 3) * 0.001953125f, a3);
                         }
+                        const float cs = (a0 + a1) + (a2 + a3);
+                        total += cs;
+                        offs = fmaf(cs, (float)(cb + 1), offs);
                         tmem_wait();
                     }
                 }
+                if (warp == 6) PROF_ADD(7);
                 if (Q.dbg_scores) { // diagnostic dump of the raw scores
                     for (int cb = 0; cb < nch; ++cb) {
                         tmem_ld32_issue(taddr + cb * 32, ra);
                         tmem_wait();
                         if (valid) {
-                            float *o = Q.dbg_scores + ((size_t)row * m + s) * BN + cb * 32;
+                            float *o = Q.dbg_scores + ((size_t)row * m + g * 4 + ss) * BN + cb * 32;
 #pragma unroll
                             for (int t = 0; t < 32; ++t) o[t] = __uint_as_float(ra[t]);
                         }
@@ -345,18 +394,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars->tempty[team]);
 
-                const float acc = acc0 + acc1;
-                const bool single = rankable && acc >= 1.0f && acc < 1.5f;
-                idxs[h] = single ? (int)((acc - 1.0f) * 512.0f + 0.5f) : 0;
-                if (!single || idxs[h] >= k) marked |= 1u << h;
+                const bool single = rankable && total >= 1.0f && total < 1.07f;
+                const int idx = single ? ((int)offs) * 32 + (int)((total - 1.0f) * 512.0f + 0.5f) : 0;
+                if (h == 0) idxs[0] = idx;
+                else idxs[1] = idx;
+                if (!single || idx >= k) marked |= 1u << h;
                 done |= 1u << h;
+                if (warp == 6) PROF_ADD(8);
             }
 
             if (valid && done) {
-                if (marked) {
-                    Q.marks[row * (unsigned long long)(m >> 1) + g * 2 + team] = (uint8_t)marked;
-                    atomicAdd(Q.stats, (unsigned long long)__popc(marked));
-                }
+                if (marked) Q.marks[row * (unsigned long long)(m >> 1) + g * 2 + team] = (uint8_t)marked;
                 if (TRAIN) {
                     uint8_t *cp = reinterpret_cast<uint8_t *>(P.codes) + row * (unsigned long long)m + g * 4 + team * 2;
                     if (done == 3u && marked == 0u) {
@@ -382,11 +430,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
 #pragma unroll
                     for (int h = 0; h < 2; ++h)
                         if ((done >> h & 1u) && !(marked >> h & 1u)) {
-                            const int s = g * 4 + team * 2 + h;
+                            const int ss = team * 2 + h, s = g * 4 + ss;
                             const int idx = idxs[h];
                             if (P.out_codes) P.out_codes[row * m + s] = (uint32_t)idx;
                             if (P.out_f16) // 16-byte aligned: dim % 8 == 0
-                                *reinterpret_cast<uint4 *>(P.out_f16 + row * dim + (size_t)s * SDW) = __ldg(Q.c16 + (size_t)s * BN + idx);
+                                *reinterpret_cast<uint4 *>(P.out_f16 + row * dim + (size_t)s * SDW) = c16_s[ss * BN + idx];
                             if (P.out_f32) {
                                 const float4 *c = reinterpret_cast<const float4 *>(P.centroids + ((size_t)s * k + idx) * SDW);
                                 float4 *o = reinterpret_cast<float4 *>(P.out_f32 + row * dim + (size_t)s * SDW);
@@ -396,6 +444,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                         }
                 }
             }
+            {
+                const uint32_t nm = __reduce_add_sync(0xffffffffu, (valid && done) ? (uint32_t)__popc(marked) : 0u);
+                if (nm && lane == 0) atomicAdd(Q.stats, (unsigned long long)nm);
+            }
+            if (warp == 6) PROF_ADD(9);
         }
         if (TRAIN) {
             moved_mask = __reduce_or_sync(0xffffffffu, moved_mask);
@@ -594,7 +647,7 @@ void launch_pq_tc(CudaDevice &dev, const AssignParams &p, int metric, bool train
     q.stats = stats;
     q.error = error_word;
     q.dbg_scores = dbg_scores;
-    const size_t smem = 1024 + 4 * (size_t)B_BYTES + (size_t)NSTAGE * A_STAGE_BYTES + (size_t)XH_RING * BM * sizeof(float) + sizeof(PqBarriers) + 64;
+    const size_t smem = 1024 + 4 * (size_t)B_BYTES + (size_t)NSTAGE * A_STAGE_BYTES + ((size_t)XH_RING * BM + 4 * BN * 4) * sizeof(float) + sizeof(PqBarriers) + 64;
     const unsigned long long tiles = (p.n + BM - 1) / BM;
     const unsigned ngroups = (unsigned)p.m / 4;
     const unsigned per = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>(tiles, (unsigned long long)dev.sm_count() / ngroups));
@@ -603,6 +656,17 @@ void launch_pq_tc(CudaDevice &dev, const AssignParams &p, int metric, bool train
     else if (metric == M_EUCLID) launch_t<false, true>(dev, mb, q, smem, grid);
     else launch_t<false, false>(dev, mb, q, smem, grid);
     dev.release(marks);
+#ifdef VQB_PQ_PROFILE
+    {
+        cudaStreamSynchronize(dev.stream());
+        unsigned long long h[16];
+        cudaMemcpyFromSymbol(h, g_prof, sizeof h);
+        static const char *nm[11] = {"mma wait afull", "mma wait tempty", "mma issue", "conv wait aempty", "conv work", "epi wait tfull", "epi pass1", "epi pass2", "epi tail", "epi outputs", "epi gap"};
+        for (int i = 0; i < 11; ++i) fprintf(stderr, "%-18s %12llu\n", nm[i], h[i]);
+        unsigned long long z[16] = {0};
+        cudaMemcpyToSymbol(g_prof, z, sizeof z);
+    }
+#endif
 }
 
 } // namespace vqb

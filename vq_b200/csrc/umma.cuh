@@ -8,6 +8,9 @@
 namespace vqb {
 
 constexpr uint32_t UMMA_SPIN_LIMIT = 4000000u;
+#ifndef VQB_WAIT_HINT_NS
+#define VQB_WAIT_HINT_NS 1000u
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -35,7 +38,7 @@ __device__ __forceinline__ bool mbar_wait(void *bar, uint32_t parity, volatile i
         // the hint lets the hardware park the thread (up to ~1 us) instead of spinning through issue slots
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, p;\n\t}"
                      : "=r"(done)
-                     : "r"(addr), "r"(parity), "r"(1000u)
+                     : "r"(addr), "r"(parity), "r"(VQB_WAIT_HINT_NS)
                      : "memory");
         if (done) return true;
         if ((i & 1023u) == 1023u && *abort_flag) return false;
@@ -49,6 +52,14 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, i
 {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
                  "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16 bytes), no multicast.
+__device__ __forceinline__ void bulk_load_1d(void *dst, const void *src, uint32_t bytes, void *bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)), "l"(src),
+                 "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
 
