@@ -37,7 +37,6 @@
 //                sub-spaces 2t, 2t+1 of the group through accumulator t
 // Every wait is bounded; on expiry the CTA records a code, stops issuing, frees tensor memory and the host raises an error.
 #include <algorithm>
-#include <cstdio>
 
 #include "assign_reg.cuh"
 #include "cuda_device.hpp"
@@ -78,15 +77,6 @@ struct PqTcParams {
     float *dbg_scores; // optional [n][m][256]
 };
 
-#ifdef VQB_PQ_PROFILE
-__device__ unsigned long long g_prof[16];
-#define PROF_T0 long long _t0 = clock64()
-#define PROF_ADD(i) do { long long _t1 = clock64(); if (blockIdx.x == 0 && lane == 0) atomicAdd(&g_prof[i], (unsigned long long)(_t1 - _t0)); _t0 = _t1; } while (0)
-#else
-#define PROF_T0
-#define PROF_ADD(i)
-#endif
-
 __device__ __forceinline__ float to_tf32(float v)
 {
     uint32_t r;
@@ -97,15 +87,8 @@ __device__ __forceinline__ float to_tf32(float v)
 __device__ __forceinline__ float fma_sat(float a, float b, float c)
 {
     float d;
-    asm volatile("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); // volatile: stays between the tensor-memory load and its wait
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
-}
-
-__device__ __forceinline__ float min3v(float a, float b, float c)
-{
-    float r;
-    asm volatile("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-    return r;
 }
 
 // order in which the four sub-spaces of a group are issued: accumulator / team = ss >> 1 alternates
@@ -183,17 +166,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                     const int ss = list[p];
                     const uint32_t b = (uint32_t)ss >> 1;
                     const int st = it % NSTAGE;
-                    PROF_T0;
                     if (!mbar_wait(&bars->afull[st], (it / NSTAGE) & 1u, abort_flag, Q.error, 14)) {
                         ok = false;
                         break;
                     }
-                    PROF_ADD(0);
                     if (!mbar_wait(&bars->tempty[b], (uses[b] & 1u) ^ 1u, abort_flag, Q.error, 13)) {
                         ok = false;
                         break;
                     }
-                    PROF_ADD(1);
                     ++uses[b];
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t adesc = smem_desc_sw128(smem_u32(a_smem + (size_t)st * A_STAGE_BYTES));
@@ -203,7 +183,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                         umma_tf32(tmem_base + b * BN, adesc + (uint64_t)(2 * k8), bdesc + (uint64_t)(2 * k8), k8 ? 1u : 0u);
                     umma_commit(&bars->aempty[st]);
                     umma_commit(&bars->tfull[b]);
-                    PROF_ADD(2);
                 }
             }
         }
@@ -234,12 +213,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                 const int ss = issue_order(ss4);
                 if (pos[ss] < 0 || !ok) continue;
                 const int st = it % NSTAGE;
-                PROF_T0;
                 if (!mbar_wait(&bars->aempty[st], ((it / NSTAGE) & 1u) ^ 1u, abort_flag, Q.error, 11)) {
                     ok = false;
                     continue;
                 }
-                if (warp == 2) PROF_ADD(3);
                 const float4 v0 = cur[2 * ss], v1 = cur[2 * ss + 1];
                 const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
                 float hi[8], lo[8], sq = 0.0f;
@@ -264,7 +241,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic writes -> visible to the MMA's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars->afull[st]);
-                if (warp == 2) PROF_ADD(4);
                 ++it;
             }
             if (!ok) break;
@@ -277,7 +253,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
         uint32_t uu = 0, moved_mask = 0, tile_iter = 0;
         const float hmax2_0 = 2.0f * Q.hnmax[g * 4 + team * 2], hmax2_1 = 2.0f * Q.hnmax[g * 4 + team * 2 + 1];
         if (!TRAIN && nact > 0) mbar_wait(&bars->bfull, 0, abort_flag, Q.error, 16); // the f16 images arrive with operand B
-        PROF_T0;
         for (unsigned long long tile = tile0; nact > 0 && tile < n_tiles && !*abort_flag; tile += tstep, ++tile_iter) {
             const unsigned long long row = tile * BM + 32ull * q + lane;
             const bool valid = row < P.n;
@@ -291,7 +266,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                 if (pos[ss] < 0) continue;
                 const uint32_t it = tile_iter * (uint32_t)nact + (uint32_t)pos[ss];
                 if (!mbar_wait(&bars->tfull[team], uu & 1u, abort_flag, Q.error, 15)) break;
-                if (warp == 6) PROF_ADD(5);
                 ++uu;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)team * BN;
@@ -313,27 +287,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                     }
 #pragma unroll
                     for (int t = 0; t < 32; t += 8) {
-                        b0 = min3v(b0, __uint_as_float(ra[t]), __uint_as_float(ra[t + 1]));
-                        b1 = min3v(b1, __uint_as_float(ra[t + 2]), __uint_as_float(ra[t + 3]));
-                        b2 = min3v(b2, __uint_as_float(ra[t + 4]), __uint_as_float(ra[t + 5]));
-                        b3 = min3v(b3, __uint_as_float(ra[t + 6]), __uint_as_float(ra[t + 7]));
+                        b0 = min3f(b0, __uint_as_float(ra[t]), __uint_as_float(ra[t + 1]));
+                        b1 = min3f(b1, __uint_as_float(ra[t + 2]), __uint_as_float(ra[t + 3]));
+                        b2 = min3f(b2, __uint_as_float(ra[t + 4]), __uint_as_float(ra[t + 5]));
+                        b3 = min3f(b3, __uint_as_float(ra[t + 6]), __uint_as_float(ra[t + 7]));
                     }
                     tmem_wait();
                     if (cb + 1 < nch) {
                         tmem_ld32_issue(taddr + (cb + 2 < nch ? cb + 2 : 0) * 32, ra); // past the end: the first chunk of pass 2
 #pragma unroll
                         for (int t = 0; t < 32; t += 8) {
-                            b0 = min3v(b0, __uint_as_float(rb[t]), __uint_as_float(rb[t + 1]));
-                            b1 = min3v(b1, __uint_as_float(rb[t + 2]), __uint_as_float(rb[t + 3]));
-                            b2 = min3v(b2, __uint_as_float(rb[t + 4]), __uint_as_float(rb[t + 5]));
-                            b3 = min3v(b3, __uint_as_float(rb[t + 6]), __uint_as_float(rb[t + 7]));
+                            b0 = min3f(b0, __uint_as_float(rb[t]), __uint_as_float(rb[t + 1]));
+                            b1 = min3f(b1, __uint_as_float(rb[t + 2]), __uint_as_float(rb[t + 3]));
+                            b2 = min3f(b2, __uint_as_float(rb[t + 4]), __uint_as_float(rb[t + 5]));
+                            b3 = min3f(b3, __uint_as_float(rb[t + 6]), __uint_as_float(rb[t + 7]));
                         }
                     } else {
                         tmem_ld32_issue(taddr, ra); // odd chunk count: the first chunk of pass 2
                     }
                     tmem_wait();
                 }
-                if (warp == 6) PROF_ADD(6);
                 const float best = fminf(fminf(b0, b1), fminf(b2, b3));
                 const float limit = best + (MARGIN_COEF * (xh2 + hmax2 + fabsf(best)) + 1e-36f);
                 // rows the test below cannot rank: NaN / infinity anywhere that matters, or values too small to scale
@@ -378,7 +351,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                         tmem_wait();
                     }
                 }
-                if (warp == 6) PROF_ADD(7);
                 if (Q.dbg_scores) { // diagnostic dump of the raw scores
                     for (int cb = 0; cb < nch; ++cb) {
                         tmem_ld32_issue(taddr + cb * 32, ra);
@@ -400,7 +372,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                 else idxs[1] = idx;
                 if (!single || idx >= k) marked |= 1u << h;
                 done |= 1u << h;
-                if (warp == 6) PROF_ADD(8);
             }
 
             if (valid && done) {
@@ -448,7 +419,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                 const uint32_t nm = __reduce_add_sync(0xffffffffu, (valid && done) ? (uint32_t)__popc(marked) : 0u);
                 if (nm && lane == 0) atomicAdd(Q.stats, (unsigned long long)nm);
             }
-            if (warp == 6) PROF_ADD(9);
         }
         if (TRAIN) {
             moved_mask = __reduce_or_sync(0xffffffffu, moved_mask);
@@ -656,17 +626,6 @@ void launch_pq_tc(CudaDevice &dev, const AssignParams &p, int metric, bool train
     else if (metric == M_EUCLID) launch_t<false, true>(dev, mb, q, smem, grid);
     else launch_t<false, false>(dev, mb, q, smem, grid);
     dev.release(marks);
-#ifdef VQB_PQ_PROFILE
-    {
-        cudaStreamSynchronize(dev.stream());
-        unsigned long long h[16];
-        cudaMemcpyFromSymbol(h, g_prof, sizeof h);
-        static const char *nm[11] = {"mma wait afull", "mma wait tempty", "mma issue", "conv wait aempty", "conv work", "epi wait tfull", "epi pass1", "epi pass2", "epi tail", "epi outputs", "epi gap"};
-        for (int i = 0; i < 11; ++i) fprintf(stderr, "%-18s %12llu\n", nm[i], h[i]);
-        unsigned long long z[16] = {0};
-        cudaMemcpyToSymbol(g_prof, z, sizeof z);
-    }
-#endif
 }
 
 } // namespace vqb
