@@ -38,7 +38,9 @@ METRIC_NAME, UNIT = "pq_fit_plus_encode_throughput", "Mvec/s"
 TRAIN_BYTES_PER_VEC, ENCODE_BYTES_PER_VEC = 544, 768
 # DRAM traffic per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the 1M-row workload,
 # from the captures summarised under profiles/ (valid for the 1M-row, 1-GPU workload).
-NCU_TRAFFIC_BYTES = {"assign_train": 545.1e6, "pq_encode": 906.4e6}  # profiles/assign_filter_kernel_pq_1m_full.md
+# assign_train: pq_tc_kernel, 530.6 B read + 27 B written per row on a 262144-row capture, scaled to 1M rows (traffic grows
+# with the rows: every row is read once) -- profiles/pq_tc_kernel_pq_1m.md; the encode launch was not captured.
+NCU_TRAFFIC_BYTES = {"assign_train": 558.0e6, "pq_encode": None}
 
 
 def measured_peaks():

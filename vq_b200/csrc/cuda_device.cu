@@ -543,6 +543,7 @@ template <typename CodeT>
 __global__ void accum_small_kernel(const float *x, unsigned long long n, unsigned long long ld, int m, int k, int sd,
                                    int group, const CodeT *codes, const uint32_t *active, float *sums, uint32_t *counts)
 {
+    const bool vec4 = (sd % 4 == 0) && (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
     extern __shared__ __align__(16) float smem[];
     const int g0 = blockIdx.y * group;
     const int gcount = min(group, m - g0);
@@ -561,7 +562,17 @@ __global__ void accum_small_kernel(const float *x, unsigned long long n, unsigne
         const int code = (int)codes[row * m + s];
         const float *xp = x + row * ld + (size_t)s * sd;
         float *dst = ssum + (size_t)sl * sd * k + code;
-        for (int d = 0; d < sd; ++d) atomicAdd(dst + (size_t)d * k, xp[d]);
+        if (vec4) { // 128-bit loads of the row slice
+            for (int d = 0; d < sd; d += 4) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(xp + d));
+                atomicAdd(dst + (size_t)d * k, v.x);
+                atomicAdd(dst + (size_t)(d + 1) * k, v.y);
+                atomicAdd(dst + (size_t)(d + 2) * k, v.z);
+                atomicAdd(dst + (size_t)(d + 3) * k, v.w);
+            }
+        } else {
+            for (int d = 0; d < sd; ++d) atomicAdd(dst + (size_t)d * k, xp[d]);
+        }
         atomicAdd(scnt + sl * k + code, 1u);
     }
     __syncthreads();
@@ -692,13 +703,19 @@ static void accumulate_t(CudaDevice &dev, const Shape &sh, const float *x, const
     const size_t budget = dev.smem_limit() - 1024;
     const size_t per_sub = (size_t)k * (sd + 1) * sizeof(float);
     if (sd <= 32 && per_sub <= budget) {
-        int group = (int)std::min<size_t>(m, budget / per_sub);
+        // two CTAs of 1024 threads per SM when the codebooks allow it: the shared-memory atomics are latency-bound
+        const size_t half_budget = (budget - 2048) / 2;
+        int group = (int)std::min<size_t>(m, std::max<size_t>(1, (per_sub <= half_budget ? half_budget : budget) / per_sub));
+        group = (m + (m + group - 1) / group - 1) / ((m + group - 1) / group); // same number of CTAs, even share of subspaces
         const size_t smem = (size_t)group * per_sub;
+        const int ctas_per_sm = (int)std::max<size_t>(1, std::min<size_t>(2, budget / (smem + 1024)));
         auto kernel = accum_small_kernel<CodeT>;
         VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         const int threads = 1024;
         const unsigned long long pairs = (unsigned long long)sh.n_local * group;
-        unsigned gx = (unsigned)std::min<unsigned long long>((pairs + threads - 1) / threads, (unsigned long long)dev.sm_count());
+        const unsigned ny = (unsigned)((m + group - 1) / group);
+        unsigned gx = (unsigned)std::min<unsigned long long>((pairs + threads - 1) / threads,
+                                                             std::max<unsigned long long>(1, (unsigned long long)dev.sm_count() * ctas_per_sm / ny));
         dim3 grid(std::max(1u, gx), (m + group - 1) / group);
         KernelScope ks(dev, "accumulate_fast");
         kernel<<<grid, threads, smem, st>>>(x, sh.n_local, sh.ld, m, k, sd, group, codes, active, sums, counts);
