@@ -491,63 +491,92 @@ __global__ void pq_operand_b_kernel(const float *cb, int k, float *bop, uint4 *c
 // unless it is centroid 0's, and equal distances keep the lowest index.
 template <bool TRAIN, bool EUCLID> __global__ void __launch_bounds__(256) pq_marked_kernel(const PqTcParams Q)
 {
+    // Each step a CTA reads 256 x 16 mark bytes (all loads independent), collects the marked pairs in shared memory --
+    // the list holds the worst case of a step -- and its eight warps then take the pairs in turn, so the work is balanced
+    // whatever the distribution of the marks.
+    __shared__ uint16_t s_list[256 * 16 * 2];
+    __shared__ uint32_t s_count;
     const AssignParams &P = Q.a;
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int m = P.m, k = P.k, half = m >> 1;
-    const unsigned long long total = P.n * (unsigned long long)half;
-    const unsigned long long nwarps = (unsigned long long)gridDim.x * (blockDim.x >> 5);
+    const unsigned long long total = P.n * (unsigned long long)half; // mark bytes; the buffer is zero-padded to 16
+    const unsigned long long total16 = (total + 15) / 16;
     uint32_t moved_lo = 0, moved_hi = 0;
-    for (unsigned long long base = ((unsigned long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 32ull; base < total; base += nwarps * 32ull) {
-        const unsigned long long mine = base + lane;
-        const uint32_t f = mine < total ? Q.marks[mine] : 0u;
-        uint32_t pending = __ballot_sync(0xffffffffu, f != 0u);
-        while (pending) {
-            const int src = __ffs(pending) - 1;
-            pending &= pending - 1;
-            const uint32_t bits = __shfl_sync(0xffffffffu, f, src);
-            const unsigned long long e = base + src;
-            const unsigned long long row = e / half;
-            const int rem = (int)(e % half);
-            for (int h = 0; h < 2; ++h) {
-                if (!(bits >> h & 1u)) continue;
-                const int s = (rem >> 1) * 4 + (rem & 1) * 2 + h;
-                float x[SDW];
-                load_slice<SDW>(x, P.x + row * P.ld + (size_t)s * SDW, P.x_vec4 != 0);
-                const float *cbs = P.centroids + (size_t)s * k * SDW;
-                float bd = VQB_INF, d0 = 0.0f;
-                int bi = 0x7fffffff;
-                for (int j = lane; j < k; j += 32) {
-                    float c[SDW];
-                    load_centroid<SDW>(c, cbs + (size_t)j * SDW);
-                    float d = reg_dist<SDW, M_SQ>(x, c, 0.0f, 0.0f, 0.0f);
-                    if (EUCLID) d = __fsqrt_rn(d);
-                    if (j == 0) d0 = d;
-                    if (d < bd) {
-                        bd = d;
-                        bi = j;
-                    }
-                }
+    for (unsigned long long base = (unsigned long long)blockIdx.x * 256ull; base < total16; base += (unsigned long long)gridDim.x * 256ull) {
+        if (threadIdx.x == 0) s_count = 0u;
+        __syncthreads();
+        const unsigned long long mine = base + threadIdx.x;
+        if (mine < total16) {
+            const uint4 f = __ldg(reinterpret_cast<const uint4 *>(Q.marks) + mine);
+            const uint32_t w[4] = {f.x, f.y, f.z, f.w};
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    const float od = __shfl_xor_sync(0xffffffffu, bd, o);
-                    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                    if (od < bd || (od == bd && oi < bi)) {
-                        bd = od;
-                        bi = oi;
-                    }
-                }
-                d0 = __shfl_sync(0xffffffffu, d0, 0);
-                int idx = (bi == 0x7fffffff || !(d0 == d0)) ? 0 : bi; // nothing below +inf, or the scan started at a NaN
-                if (lane == 0) {
-                    bool moved = false;
-                    store_result<SDW, uint8_t, TRAIN>(P, row, s, idx, cbs, moved);
-                    if (moved) {
-                        if (s < 32) moved_lo |= 1u << s;
-                        else moved_hi |= 1u << (s - 32);
-                    }
+            for (int wi = 0; wi < 4; ++wi) {
+                uint32_t word = w[wi];
+                while (word) {
+                    const int bit = __ffs(word) - 1; // bit (8 byte + h): pair h of mark byte `byte`
+                    word &= word - 1;
+                    if ((bit & 7) < 2) s_list[atomicAdd(&s_count, 1u)] = (uint16_t)((threadIdx.x * 16u + (uint32_t)(wi * 4 + (bit >> 3))) * 2u + (uint32_t)(bit & 7));
                 }
             }
         }
+        __syncthreads();
+        const uint32_t cnt = s_count;
+        for (uint32_t i = warp; i < cnt; i += 8) {
+            const uint32_t ent = s_list[i];
+            const unsigned long long e = base * 16ull + (ent >> 1);
+            const int h = (int)(ent & 1u);
+            if (e >= total) continue;
+            const unsigned long long row = e / half;
+            const int rem = (int)(e % half);
+            const int s = (rem >> 1) * 4 + (rem & 1) * 2 + h;
+            float x[SDW];
+            load_slice<SDW>(x, P.x + row * P.ld + (size_t)s * SDW, P.x_vec4 != 0);
+            const float *cbs = P.centroids + (size_t)s * k * SDW;
+            float bd = VQB_INF, d0 = 0.0f;
+            int bi = 0x7fffffff;
+            float c[BN / 32][SDW]; // this lane's centroids j = lane, lane + 32, ...: all requested before the first is used
+#pragma unroll
+            for (int u = 0; u < BN / 32; ++u) {
+                const int j = lane + 32 * u;
+                if (j < k) {
+                    load_centroid<SDW>(c[u], cbs + (size_t)j * SDW);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < SDW; ++i) c[u][i] = 0.0f;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < BN / 32; ++u) {
+                const int j = lane + 32 * u;
+                float d = reg_dist<SDW, M_SQ>(x, c[u], 0.0f, 0.0f, 0.0f);
+                if (EUCLID) d = __fsqrt_rn(d);
+                if (j == 0) d0 = d;
+                if (j < k && d < bd) {
+                    bd = d;
+                    bi = j;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float od = __shfl_xor_sync(0xffffffffu, bd, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (od < bd || (od == bd && oi < bi)) {
+                    bd = od;
+                    bi = oi;
+                }
+            }
+            d0 = __shfl_sync(0xffffffffu, d0, 0);
+            const int idx = (bi == 0x7fffffff || !(d0 == d0)) ? 0 : bi; // nothing below +inf, or the scan started at a NaN
+            if (lane == 0) {
+                bool moved = false;
+                store_result<SDW, uint8_t, TRAIN>(P, row, s, idx, cbs, moved);
+                if (moved) {
+                    if (s < 32) moved_lo |= 1u << s;
+                    else moved_hi |= 1u << (s - 32);
+                }
+            }
+        }
+        __syncthreads(); // the list is rewritten by the next step
     }
     if (TRAIN && lane == 0) {
         for (int s = 0; s < m; ++s)
@@ -585,7 +614,10 @@ static void launch_t(CudaDevice &dev, const CUtensorMap &mb, const PqTcParams &q
     }
     {
         KernelScope ks(dev, TRAIN ? "assign_train_marked" : "pq_encode_marked");
-        pq_marked_kernel<TRAIN, EUCLID><<<dev.sm_count() * 4, 256, 0, dev.stream()>>>(q);
+        // one step (4 KiB of mark bytes) per CTA where the grid allows: the steps are latency-bound and independent
+        const unsigned long long steps = ((q.a.n * (unsigned long long)(q.a.m / 2) + 15) / 16 + 255) / 256;
+        const unsigned mgrid = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>(steps, (unsigned long long)dev.sm_count() * 64));
+        pq_marked_kernel<TRAIN, EUCLID><<<mgrid, 256, 0, dev.stream()>>>(q);
         VQB_CUDA_CHECK(cudaGetLastError());
         dev.count_launch();
     }
@@ -605,7 +637,7 @@ void launch_pq_tc(CudaDevice &dev, const AssignParams &p, int metric, bool train
         VQB_CUDA_CHECK(cudaGetLastError());
         dev.count_launch();
     }
-    const size_t mark_bytes = (size_t)p.n * (size_t)(p.m / 2);
+    const size_t mark_bytes = ((size_t)p.n * (size_t)(p.m / 2) + 15) & ~(size_t)15; // read 16 bytes at a time
     uint8_t *marks = static_cast<uint8_t *>(dev.alloc(mark_bytes));
     dev.zero(marks, mark_bytes);
     const CUtensorMap mb = make_tensor_map_2d(bop, KOP, (unsigned long long)p.m * BN, KOP, BN, CU_TENSOR_MAP_SWIZZLE_128B);
