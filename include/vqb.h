@@ -45,6 +45,7 @@ extern "C" {
 #define VQB_ERR_NO_DEVICE 102
 #define VQB_ERR_UNSUPPORTED 103
 #define VQB_ERR_CALLBACK 104
+#define VQB_ERR_NOT_COMPARABLE 105         /* a NaN where the reference calls partial_cmp(..).unwrap() (src/tsvq.rs:104,109) */
 
 /* ---- Distance (src/distances.rs:73-88) --------------------------------- */
 enum vqb_metric {
@@ -115,6 +116,17 @@ int vqb_comm_destroy(vqb_ctx *ctx);
  * the reference's DimensionMismatch. ------------------------------------- */
 int vqb_distance_rows(vqb_ctx *ctx, int metric, double p, const float *a, size_t da, const float *b,
                       size_t db, size_t n, float *out);
+
+/* ---- TSVQ (src/tsvq.rs) --------------------------------------------------------------------------------------
+ * vqb_tsvq_fit: TSVQ::new (205-211) -> TSVQNode::fit (71-148), nodes numbered breadth-first (left child before right).
+ * vqb_tsvq_quantize: TSVQ::quantize (231-249): n x dim binary16 leaf centroids; leaf_out (optional): the leaf's node id.
+ * vqb_tsvq_tree: centroids nodes x dim, left / right child ids (-1 = none).  The tree is built on one GPU. */
+typedef struct vqb_tsvq vqb_tsvq;
+int vqb_tsvq_fit(vqb_ctx *ctx, const float *x, size_t n, size_t dim, size_t max_depth, int metric, double p, vqb_tsvq **out);
+int vqb_tsvq_quantize(vqb_tsvq *t, const float *x, size_t n, size_t dim, uint16_t *out_f16, uint32_t *leaf_out);
+int vqb_tsvq_shape(const vqb_tsvq *t, size_t *nodes, size_t *dim);
+int vqb_tsvq_tree(const vqb_tsvq *t, float *centroids_out, int32_t *left_out, int32_t *right_out);
+int vqb_tsvq_destroy(vqb_tsvq *t);
 
 /* ---- evaluation metrics of the reference's harness, computed on the device --------------------------------
  * mse_out: mean squared reconstruction error, calculate_reconstruction_error (src/bin/utils.rs:50-67);

@@ -82,6 +82,10 @@ def lib():
         L.vqo_bq_quantize.argtypes = [C.c_float, C.c_uint8, C.c_uint8, C.c_void_p, C.c_size_t, C.c_void_p]
         L.vqo_mse_f16.restype = C.c_double
         L.vqo_mse_f16.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t]
+        L.vqo_tsvq_fit.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p,
+                                   C.c_void_p, C.POINTER(C.c_size_t)]
+        L.vqo_tsvq_quantize.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_double, C.c_void_p,
+                                        C.c_size_t, C.c_void_p, C.c_void_p]
         L.vqo_num_threads.restype = C.c_int
         L.vqo_set_num_threads.restype = None
         L.vqo_set_num_threads.argtypes = [C.c_int]
@@ -323,6 +327,33 @@ def bq_quantize(threshold: float, low: int, high: int, x) -> np.ndarray:
     out = np.empty(x.shape, np.uint8)
     lib().vqo_bq_quantize(threshold, low, high, _ptr(x), x.size, _ptr(out))
     return out
+
+
+def tsvq_fit(x, max_depth: int):
+    """TSVQ::new / TSVQNode::fit (src/tsvq.rs:71-148,205-211).  Returns (centroids nodes x dim, left, right), nodes numbered
+    breadth-first, -1 = no child."""
+    x = _f32(x)
+    n, dim = x.shape if x.ndim == 2 else (0, 0)
+    cap = max(1, min(2 ** (max_depth + 1) - 1 if max_depth < 40 else 2 * n, 2 * max(n, 1)))
+    cent = np.zeros((cap, max(dim, 1)), np.float32)
+    left = np.full(cap, -1, np.int32)
+    right = np.full(cap, -1, np.int32)
+    nn = C.c_size_t(0)
+    _check(lib().vqo_tsvq_fit(_ptr(x), n, dim, max_depth, cap, _ptr(cent), _ptr(left), _ptr(right), C.byref(nn)))
+    k = int(nn.value)
+    return cent[:k, :dim].copy(), left[:k].copy(), right[:k].copy()
+
+
+def tsvq_quantize(centroids, left, right, x, metric: int = EUCLIDEAN, p: float = 0.0):
+    """TSVQ::quantize (src/tsvq.rs:231-249).  Returns (f16 bits n x dim, leaf node per row)."""
+    cent, x = _f32(centroids), _f32(x)
+    left = np.ascontiguousarray(left, np.int32)
+    right = np.ascontiguousarray(right, np.int32)
+    n, dim = x.shape
+    out = np.empty((n, dim), np.uint16)
+    leaf = np.empty(n, np.uint32)
+    _check(lib().vqo_tsvq_quantize(_ptr(cent), _ptr(left), _ptr(right), dim, metric, p, _ptr(x), n, _ptr(out), _ptr(leaf)))
+    return out, leaf
 
 
 def recall_at_k(original, approx, k: int = 10) -> float:

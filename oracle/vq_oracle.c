@@ -677,3 +677,121 @@ double vqo_mse_f16(const float *x, const uint16_t *q_f16, size_t n, size_t dim)
     }
     return total / (double)n;
 }
+
+/* ------------------------------------------------------------------------ */
+/* Tree-structured VQ -- src/tsvq.rs.                                         */
+/* TSVQNode::fit (71-148): centroid = mean_vector of the node's rows (here    */
+/* always in data order, one admissible order for nodes above 1024 rows);     */
+/* leaf when max_depth == 0 or <= 1 row; variance per dimension = serial f32  */
+/* sum of (v - c)^2 in data order (86-98); split dimension = max_by with      */
+/* partial_cmp, i.e. the LAST of equal maxima (101-105); median of the sorted */
+/* values, mean of the two middle ones for an even count (108-116); stable    */
+/* partition v <= median / v > median (119-122); a child exists only when its */
+/* side is non-empty and smaller than the node (127-141).  Nodes are numbered */
+/* breadth-first, the left child before the right one.                        */
+/* A NaN among the values being compared makes the reference panic on         */
+/* `partial_cmp(..).unwrap()`; here that is status 105.                       */
+/* ------------------------------------------------------------------------ */
+#define VQO_NOT_COMPARABLE 105
+
+static int cmp_f32(const void *a, const void *b)
+{
+    const float x = *(const float *)a, y = *(const float *)b;
+    return (x > y) - (x < y);
+}
+
+int vqo_tsvq_fit(const float *x, size_t n, size_t dim, size_t max_depth, size_t cap_nodes, float *centroids,
+                 int32_t *left, int32_t *right, size_t *n_nodes_out)
+{
+    if (n == 0) return fail(VQO_EMPTY_INPUT, "Empty input: at least one vector is required.");
+    typedef struct { size_t start, count, depth; } Seg;
+    uint32_t *perm = (uint32_t *)malloc(n * sizeof(uint32_t)), *tmp = (uint32_t *)malloc(n * sizeof(uint32_t));
+    Seg *segs = (Seg *)malloc(cap_nodes * sizeof(Seg));
+    float *var = (float *)malloc(dim * sizeof(float)), *vals = (float *)malloc(n * sizeof(float));
+    int rc = VQO_OK;
+    for (size_t i = 0; i < n; ++i) perm[i] = (uint32_t)i;
+    size_t n_nodes = 1;
+    segs[0].start = 0, segs[0].count = n, segs[0].depth = max_depth;
+    for (size_t node = 0; node < n_nodes && rc == VQO_OK; ++node) {
+        const Seg sg = segs[node];
+        const uint32_t *rows = perm + sg.start;
+        float *c = centroids + node * dim;
+        left[node] = right[node] = -1;
+        for (size_t t = 0; t < dim; ++t) c[t] = 0.0f;
+        for (size_t i = 0; i < sg.count; ++i)
+            for (size_t t = 0; t < dim; ++t) c[t] = c[t] + x[(size_t)rows[i] * dim + t];
+        const float len = (float)(double)sg.count;
+        for (size_t t = 0; t < dim; ++t) c[t] = c[t] / len;
+        if (sg.depth == 0 || sg.count <= 1) continue;
+        for (size_t t = 0; t < dim; ++t) var[t] = 0.0f;
+        for (size_t i = 0; i < sg.count; ++i)
+            for (size_t t = 0; t < dim; ++t) {
+                const float diff = x[(size_t)rows[i] * dim + t] - c[t];
+                const float sq = diff * diff;
+                var[t] = var[t] + sq;
+            }
+        size_t split = 0;
+        for (size_t t = 0; t < dim; ++t) {
+            if (var[t] != var[t]) rc = fail(VQO_NOT_COMPARABLE, "values are not comparable (NaN)");
+            if (t > 0 && !(var[t] < var[split])) split = t; /* max_by keeps the last of equal maxima */
+        }
+        if (rc != VQO_OK) break;
+        for (size_t i = 0; i < sg.count; ++i) {
+            vals[i] = x[(size_t)rows[i] * dim + split];
+            if (vals[i] != vals[i]) rc = fail(VQO_NOT_COMPARABLE, "values are not comparable (NaN)");
+        }
+        if (rc != VQO_OK) break;
+        qsort(vals, sg.count, sizeof(float), cmp_f32);
+        const float median = (sg.count % 2 == 0) ? (vals[sg.count / 2 - 1] + vals[sg.count / 2]) / 2.0f : vals[sg.count / 2];
+        size_t nl = 0, nr = 0;
+        for (size_t i = 0; i < sg.count; ++i) {
+            if (x[(size_t)rows[i] * dim + split] <= median) tmp[nl++] = rows[i];
+        }
+        for (size_t i = 0; i < sg.count; ++i) {
+            if (!(x[(size_t)rows[i] * dim + split] <= median)) tmp[nl + nr++] = rows[i];
+        }
+        memcpy(perm + sg.start, tmp, sg.count * sizeof(uint32_t));
+        if (nl > 0 && nl < sg.count) {
+            if (n_nodes >= cap_nodes) { rc = fail(VQO_INVALID_PARAMETER, "node capacity too small"); break; }
+            left[node] = (int32_t)n_nodes;
+            segs[n_nodes].start = sg.start, segs[n_nodes].count = nl, segs[n_nodes].depth = sg.depth - 1;
+            ++n_nodes;
+        }
+        if (nr > 0 && nr < sg.count) {
+            if (n_nodes >= cap_nodes) { rc = fail(VQO_INVALID_PARAMETER, "node capacity too small"); break; }
+            right[node] = (int32_t)n_nodes;
+            segs[n_nodes].start = sg.start + nl, segs[n_nodes].count = nr, segs[n_nodes].depth = sg.depth - 1;
+            ++n_nodes;
+        }
+    }
+    if (n_nodes_out) *n_nodes_out = n_nodes;
+    free(perm), free(tmp), free(segs), free(var), free(vals);
+    return rc;
+}
+
+/* TSVQ::quantize (src/tsvq.rs:231-249) with quantize_with_distance (162-181): descend towards the child whose centroid is */
+/* nearer under the metric, the left one on ties (`<=`), an only child unconditionally; the leaf's centroid as f16.        */
+int vqo_tsvq_quantize(const float *centroids, const int32_t *left, const int32_t *right, size_t dim, int metric, double p,
+                      const float *x, size_t n, uint16_t *out_f16, uint32_t *leaf_out)
+{
+    int rc = VQO_OK;
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; ++i) {
+        const float *v = x + i * dim;
+        int32_t node = 0;
+        for (;;) {
+            const int32_t l = left[node], r = right[node];
+            if (l >= 0 && r >= 0) {
+                const float dl = dist_nocheck(metric, p, v, centroids + (size_t)l * dim, dim);
+                const float dr = dist_nocheck(metric, p, v, centroids + (size_t)r * dim, dim);
+                node = (dl <= dr) ? l : r;
+            } else if (l >= 0) node = l;
+            else if (r >= 0) node = r;
+            else break;
+        }
+        if (leaf_out) leaf_out[i] = (uint32_t)node;
+        if (out_f16)
+            for (size_t t = 0; t < dim; ++t) out_f16[i * dim + t] = vqo_f32_to_f16(centroids[(size_t)node * dim + t]);
+    }
+    return rc;
+}

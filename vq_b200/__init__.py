@@ -599,6 +599,56 @@ class BinaryQuantizer:
         return out
 
 
+class TSVQ:
+    """TSVQ (src/tsvq.rs:189-250): ``TSVQ(training_data, max_depth, distance)`` builds the tree, ``quantize`` returns the
+    leaf centroid as f16.  ``tree()`` gives (centroids, left, right) with nodes numbered breadth-first."""
+
+    def __init__(self, training_data, max_depth: int, distance: Distance, *, ctx: Context | None = None):
+        ctx = ctx or default_context()
+        x = _rows(training_data, ctx)
+        h = C.c_void_p()
+        rc = _lib.load().vqb_tsvq_fit(ctx.handle, x.ptr, x.n, x.dim, int(max_depth), distance.metric, distance.p, C.byref(h))
+        if rc:
+            _raise(rc, ctx.handle)
+        self._h, self._ctx, self.distance = h, ctx, distance
+
+    def shape(self):
+        nodes, dim = C.c_size_t(), C.c_size_t()
+        _lib.load().vqb_tsvq_shape(self._h, C.byref(nodes), C.byref(dim))
+        return int(nodes.value), int(dim.value)
+
+    def tree(self):
+        nodes, dim = self.shape()
+        cent = np.empty((nodes, dim), np.float32)
+        left = np.empty(nodes, np.int32)
+        right = np.empty(nodes, np.int32)
+        rc = _lib.load().vqb_tsvq_tree(self._h, cent.ctypes.data, left.ctypes.data, right.ctypes.data)
+        if rc:
+            _raise(rc, self._ctx.handle)
+        return cent, left, right
+
+    def quantize(self, vector, return_leaf: bool = False):
+        """TSVQ::quantize (src/tsvq.rs:231-249): one f16 row per input vector."""
+        x = _Arr(vector, self._ctx)
+        out, optr = x.empty((x.n, x.dim), np.float16)
+        leaf, lptr = (x.empty((x.n,), np.uint32) if return_leaf else (None, None))
+        rc = _lib.load().vqb_tsvq_quantize(self._h, x.ptr, x.n, x.dim, optr, lptr)
+        if rc:
+            _raise(rc, self._ctx.handle)
+        if x.single:
+            out = out[0]
+            leaf = leaf[0] if leaf is not None else None
+        return (out, leaf) if return_leaf else out
+
+    def __del__(self):
+        try:
+            if self._h:
+                _lib.load().vqb_tsvq_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
 def evaluate(original, quantized_f16, k: int = 10, *, ctx: Context | None = None):
     """The reference harness's quality metrics on the device: (reconstruction error, recall@k), i.e.
     calculate_reconstruction_error and calculate_recall of src/bin/utils.rs:50-127 applied to the f16 output of a

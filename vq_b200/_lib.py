@@ -37,6 +37,11 @@ SIGNATURES = {
     "vqb_comm_init": (C.c_int, [_P, _P, C.c_int, C.c_int]),
     "vqb_comm_destroy": (C.c_int, [_P]),
     "vqb_distance_rows": (C.c_int, [_P, C.c_int, C.c_double, _P, _SZ, _P, _SZ, _SZ, _P]),
+    "vqb_tsvq_fit": (C.c_int, [_P, _P, _SZ, _SZ, _SZ, C.c_int, C.c_double, C.POINTER(_P)]),
+    "vqb_tsvq_quantize": (C.c_int, [_P, _P, _SZ, _SZ, _P, _P]),
+    "vqb_tsvq_shape": (C.c_int, [_P, C.POINTER(_SZ), C.POINTER(_SZ)]),
+    "vqb_tsvq_tree": (C.c_int, [_P, _P, _P, _P]),
+    "vqb_tsvq_destroy": (C.c_int, [_P]),
     "vqb_evaluate_f16": (C.c_int, [_P, _P, _P, _SZ, _SZ, _SZ, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "vqb_pq_tensor_scores": (C.c_int, [_P, _P, _SZ, _SZ, _P, _SZ, _P, _P, _P]),
     "vqb_dense_dots": (C.c_int, [_P, _P, _SZ, _SZ, _P, _SZ, _P, _P]),

@@ -14,6 +14,7 @@
 #include "../../include/vqb.h"
 #include "cuda_device.hpp"
 #include "opq_parts.hpp"
+#include "tsvq.hpp"
 
 namespace vqb {
 void nccl_unique_id(uint8_t *out128);
@@ -45,6 +46,13 @@ struct vqb_rvq {
     int metric;
     double p;
     float *codebooks; // device, stages x k x dim
+};
+
+struct vqb_tsvq {
+    vqb_ctx *ctx;
+    int metric;
+    double p;
+    TsvqTree tree;
 };
 
 struct vqb_opq {
@@ -359,6 +367,77 @@ int vqb_distance_rows(vqb_ctx *ctx, int metric, double p, const float *a, size_t
         dev.distance_rows(metric, p, ia.as<float>(), ib.as<float>(), da, n, o.as<float>());
         o.finish();
     });
+}
+
+int vqb_tsvq_fit(vqb_ctx *ctx, const float *x, size_t n, size_t dim, size_t max_depth, int metric, double p, vqb_tsvq **out)
+{
+    if (!ctx) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "ctx is NULL");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (!out) throw Error(VQB_ERR_BAD_ARGUMENT, "out is NULL");
+        *out = nullptr;
+        if (metric < 0 || metric > 6) throw Error(VQB_ERR_BAD_ARGUMENT, "unknown metric");
+        if (n == 0 || dim == 0) throw Error(VQB_ERR_EMPTY_INPUT, "Empty input: at least one vector is required."); // src/tsvq.rs:206-208
+        if (!x) throw Error(VQB_ERR_BAD_ARGUMENT, "x is NULL");
+        CudaDevice &dev = *ctx->dev;
+        In ix(dev, x, sizeof(float) * n * dim);
+        std::unique_ptr<vqb_tsvq> t(new vqb_tsvq{ctx, metric, p, TsvqTree{}});
+        tsvq_fit(dev, ix.as<float>(), n, dim, max_depth, t->tree);
+        *out = t.release();
+    });
+}
+
+int vqb_tsvq_quantize(vqb_tsvq *t, const float *x, size_t n, size_t dim, uint16_t *out_f16, uint32_t *leaf_out)
+{
+    if (!t) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "tsvq is NULL");
+    vqb_ctx *ctx = t->ctx;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (dim != t->tree.dim) throw Error(VQB_ERR_DIMENSION_MISMATCH, dim_mismatch(t->tree.dim, dim)); // src/tsvq.rs:232-240
+        if (n == 0) return;
+        if (!x) throw Error(VQB_ERR_BAD_ARGUMENT, "x is NULL");
+        check_minkowski(t->metric, t->p);
+        CudaDevice &dev = *ctx->dev;
+        In ix(dev, x, sizeof(float) * n * dim);
+        Out of(dev, out_f16, sizeof(uint16_t) * n * dim), ol(dev, leaf_out, sizeof(uint32_t) * n);
+        tsvq_quantize(dev, t->tree, t->metric, t->p, ix.as<float>(), n, of.as<uint16_t>(), ol.as<uint32_t>());
+        of.finish();
+        ol.finish();
+    });
+}
+
+int vqb_tsvq_shape(const vqb_tsvq *t, size_t *nodes, size_t *dim)
+{
+    if (!t) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "tsvq is NULL");
+    if (nodes) *nodes = t->tree.nodes;
+    if (dim) *dim = t->tree.dim;
+    return VQB_OK;
+}
+
+int vqb_tsvq_tree(const vqb_tsvq *t, float *centroids_out, int32_t *left_out, int32_t *right_out)
+{
+    if (!t) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "tsvq is NULL");
+    vqb_ctx *ctx = t->ctx;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (centroids_out) {
+            const size_t bytes = sizeof(float) * t->tree.nodes * t->tree.dim;
+            if (ctx->dev->is_device_pointer(centroids_out)) ctx->dev->copy(centroids_out, t->tree.centroids, bytes);
+            else ctx->dev->download(centroids_out, t->tree.centroids, bytes);
+        }
+        if (left_out) std::memcpy(left_out, t->tree.h_left.data(), sizeof(int32_t) * t->tree.nodes);
+        if (right_out) std::memcpy(right_out, t->tree.h_right.data(), sizeof(int32_t) * t->tree.nodes);
+    });
+}
+
+int vqb_tsvq_destroy(vqb_tsvq *t)
+{
+    if (!t) return VQB_OK;
+    vqb_ctx *ctx = t->ctx;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    guarded(ctx, [&] { tsvq_release(*ctx->dev, t->tree); });
+    delete t;
+    return VQB_OK;
 }
 
 int vqb_evaluate_f16(vqb_ctx *ctx, const float *x, const uint16_t *q_f16, size_t n, size_t dim, size_t k, float *mse_out,
