@@ -309,7 +309,8 @@ def run_secondary(args):
     """The other benchmark configurations on one GPU (measurement aid; the headline line is the default workload).
     sq / bq: 10,000,000 x 128 values in [-1,1), SQ [0,1] x 256 levels, BQ threshold 0.
     rvq: 1,000,000 x 128 Gaussian mixture (64 components, sigma 0.05), 8 stages, k=256, 10 iterations, Euclidean.
-    opq: 1,000,000 x 128 correlated rows, m=16, k=256, 10 outer x 5 LBG iterations."""
+    opq: 1,000,000 x 128 correlated rows, m=16, k=256, 10 outer x 5 LBG iterations.
+    tsvq: 1,000,000 x 128 uniform rows, depth 10, Euclidean (build + lookup of every row)."""
     import torch
 
     import vq_b200 as vq
@@ -361,6 +362,10 @@ def run_secondary(args):
             xh = synth.gaussian_mixture(rows, DIM, 11)
             fit = lambda xx: vq.ResidualQuantizer.fit(xx, 8, K, ITERS, 0.01, vq.Distance.Euclidean, FIT_SEED, ctx=ctx)  # noqa: E731
             kname, bytes_per_vec, cfg = "assign_train", 512, "rvq_1m_x128_8stages_k256_10iters_fit_plus_encode"
+        elif w == "tsvq":
+            xh = synth.uniform01(rows, DIM, 1)
+            fit = lambda xx: vq.TSVQ(xx, 10, vq.Distance.Euclidean, ctx=ctx)  # noqa: E731  (depth 10: benches/bench_tsvq.rs:11)
+            kname, bytes_per_vec, cfg = "tsvq_node_stats", 2 * 512, "tsvq_1m_x128_depth10_fit_plus_encode"
         else:
             xh = synth.correlated(rows, DIM, 3)
             fit = lambda xx: vq.OptimizedProductQuantizer.fit(xx, M, K, 5, 10, vq.Distance.Euclidean, FIT_SEED, ctx=ctx)  # noqa: E731
@@ -374,7 +379,7 @@ def run_secondary(args):
             return out
         cpu, e2e_fn, e2e_rows, h2d, d2h = None, None, 0, 0, 0
 
-    for _ in range(max(1, min(3, args.warmup)) if w in ("rvq", "opq") else max(3, args.warmup)):
+    for _ in range(max(1, min(3, args.warmup)) if w in ("rvq", "opq", "tsvq") else max(3, args.warmup)):
         step()
     sampler.start()
     ctx.timing(True)
@@ -414,7 +419,7 @@ def run_secondary(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="pq", choices=["pq", "sq", "bq", "rvq", "opq"],
+    ap.add_argument("--workload", default="pq", choices=["pq", "sq", "bq", "rvq", "opq", "tsvq"],
                     help="pq (default) is the headline benchmark; the others measure the remaining configurations on one GPU")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)

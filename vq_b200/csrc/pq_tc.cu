@@ -37,6 +37,7 @@
 //                sub-spaces 2t, 2t+1 of the group through accumulator t
 // Every wait is bounded; on expiry the CTA records a code, stops issuing, frees tensor memory and the host raises an error.
 #include <algorithm>
+#include <atomic>
 
 #include "assign_reg.cuh"
 #include "cuda_device.hpp"
@@ -601,10 +602,11 @@ template <bool TRAIN, bool EUCLID>
 static void launch_t(CudaDevice &dev, const CUtensorMap &mb, const PqTcParams &q, size_t smem, unsigned grid)
 {
     auto kernel = pq_tc_kernel<TRAIN, EUCLID>;
-    static bool configured = false; // one device context per process configuration; the attribute is sticky per function
-    if (!configured) {
+    static std::atomic<unsigned long long> configured{0}; // bit d: the attribute has been set on device d (it is per device and sticky)
+    const unsigned long long bit = 1ull << (dev.device() & 63);
+    if (!(configured.load(std::memory_order_relaxed) & bit)) {
         VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
+        configured.fetch_or(bit, std::memory_order_relaxed);
     }
     {
         KernelScope ks(dev, TRAIN ? "assign_train" : "pq_encode");

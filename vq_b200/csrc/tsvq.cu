@@ -49,10 +49,11 @@ __device__ __forceinline__ float key_f32(uint32_t k)
 }
 
 // Calls f(value) for column t of the node's rows in data order.  The additions behind f form one serial chain, so the loads
-// are what can overlap: 32 rows are in flight while the previous 32 are consumed.
+// are what can overlap: 48 rows are in flight while the previous 48 are consumed (one warp per 32 dimensions, so that the
+// 96 buffer registers per thread are affordable and a wide node spreads over several SMs).
 template <typename F> __device__ __forceinline__ void walk_rows(const float *x, size_t dim, const uint32_t *rows, unsigned long long count, size_t t, F f)
 {
-    constexpr int B = 32;
+    constexpr int B = 48;
     float cur[B], nxt[B];
     unsigned long long i = 0;
     if (count >= (unsigned long long)B) {
@@ -75,13 +76,13 @@ template <typename F> __device__ __forceinline__ void walk_rows(const float *x, 
     for (; i < count; ++i) f(x[(size_t)rows[i] * dim + t]);
 }
 
-// grid.x = nodes of the level (ids first .. first + gridDim.x), threads over dimensions
-__global__ void node_stats_kernel(const float *x, size_t dim, const uint32_t *perm, NodeInfo *nodes, int first, float *centroids, float *spread)
+// grid.x = nodes of the level (ids first .. first + gridDim.x), grid.y x 32 threads over dimensions
+__global__ void __launch_bounds__(32) node_stats_kernel(const float *x, size_t dim, const uint32_t *perm, NodeInfo *nodes, int first, float *centroids, float *spread)
 {
     const int node = first + blockIdx.x;
     const NodeInfo nd = nodes[node];
     const uint32_t *rows = perm + nd.start;
-    for (size_t t = threadIdx.x; t < dim; t += blockDim.x) {
+    for (size_t t = blockIdx.y * 32 + threadIdx.x; t < dim; t += (size_t)gridDim.y * 32) {
         float sum = 0.0f;
         walk_rows(x, dim, rows, nd.count, t, [&](float v) { sum = __fadd_rn(sum, v); });
         const float c = __fdiv_rn(sum, __ull2float_rn(nd.count)); // sum / (len as f32)
@@ -296,8 +297,8 @@ void tsvq_fit(CudaDevice &dev, const float *x, size_t n, size_t dim, size_t max_
             }
             {
                 KernelScope ks(dev, "tsvq_node_stats");
-                const int threads = (int)std::min<size_t>(1024, ((dim + 31) / 32) * 32);
-                node_stats_kernel<<<(unsigned)level_count, threads, 0, st>>>(x, dim, perm, nodes_d, (int)first, cent, spread);
+                const dim3 grid((unsigned)level_count, (unsigned)std::min<size_t>((dim + 31) / 32, 64));
+                node_stats_kernel<<<grid, 32, 0, st>>>(x, dim, perm, nodes_d, (int)first, cent, spread);
                 VQB_CUDA_CHECK(cudaGetLastError());
                 dev.count_launch();
             }
