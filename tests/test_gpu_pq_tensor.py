@@ -66,6 +66,10 @@ def test_ties_duplicates_and_specials_go_to_the_exact_scan(ctx, oracle):
     x[102] = 0.0
     x[103] = 1e-25                 # too small to scale: ranked by the exact scan
     x[104] = 3e18                  # squares overflow
+    x[105, :8] = 0.0
+    x[105, 0] = 1.3e19             # scores stay finite but the true distance to centroid 20 overflows f32
+    cb[0, 20] = 0.0
+    cb[0, 20, 0] = -1.3e19
     _, codes, marked = _scores(ctx, x, cb, want_scores=False)
     _, codes_o = oracle.pq_quantize(cb, x, ka.SQ)
     assert np.array_equal(codes, codes_o)

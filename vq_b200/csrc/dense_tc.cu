@@ -220,7 +220,8 @@ __global__ void __launch_bounds__(192, 1) dense_shortlist_kernel(const __grid_co
             const float limit = best + e2 + 1.05f * (float)(P.dim + 6) * 5.9604645e-8f * d_a + 2.4e-7f * (fabsf(best) + e2) + 1e-36f;
             // a row the comparisons cannot rank (NaN / infinity somewhere, or centroid 0 not comparable, on which the
             // reference's scan depends) is handed over with every centroid marked
-            const bool scan_all = col0_nan || !(second >= best) || !(limit == limit) || !(fabsf(limit) < VQB_DENSE_INF);
+            // (also when a true distance could overflow f32: then the reference's own comparisons see infinities)
+            const bool scan_all = col0_nan || !(second >= best) || !(limit == limit) || !(fabsf(limit) < VQB_DENSE_INF) || !(xn2 + cmax * cmax < 1e37f);
 
             // pass 2: one bit per centroid, set when S_j <= limit.  The sign of (limit - S_j) is shifted into the word,
             // so the bits arrive in reverse order and inverted.

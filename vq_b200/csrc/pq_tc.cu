@@ -311,7 +311,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                 const float best = fminf(fminf(b0, b1), fminf(b2, b3));
                 const float limit = best + (MARGIN_COEF * (xh2 + hmax2 + fabsf(best)) + 1e-36f);
                 // rows the test below cannot rank: NaN / infinity anywhere that matters, or values too small to scale
-                const bool rankable = !col0_nan && (fabsf(limit) >= 8.6736174e-19f /* 2^-60 */) && (fabsf(limit) < VQB_INF);
+                // (nor rows whose true distances could overflow f32: there the reference's own comparisons see infinities)
+                const bool rankable = !col0_nan && (fabsf(limit) >= 8.6736174e-19f /* 2^-60 */) && (fabsf(limit) < VQB_INF) && (xh2 + hmax2 < 1e37f);
                 const uint32_t eb = (__float_as_uint(limit) >> 23) & 0xFFu;
                 const float nbig = __uint_as_float(0x80000000u | ((314u - eb) << 23)); // -2^(60 - exponent(limit))
                 const float lb = -limit * nbig;                                       // exact scaling

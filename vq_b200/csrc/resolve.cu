@@ -262,6 +262,181 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
     }
 }
 
+// Training assignment, two passes per block of 256 rows.  Pass A reads only the shortlists: a row with a single candidate is
+// decided at once (that candidate is the reference's choice), the others are collected in a per-warp list.  Pass B stages
+// just the listed rows and runs the exact arithmetic with every lane busy.  After the first k-means iterations most rows have
+// one candidate, so most of the row matrix is never read here.
+template <typename CodeT> __global__ void __launch_bounds__(128, 1) resolve_train_kernel(const ResolveParams P)
+{
+    extern __shared__ __align__(16) float smem[];
+    const int dim = P.dim, k = P.k, cstride = dim + 1;
+    const int W = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float *cpad = smem;                                                                   // [k][dim + 1]
+    float *xs = smem + (size_t)k * cstride + (size_t)warp * dim * XS_STRIDE;              // [dim][33] per warp
+    uint16_t *list = reinterpret_cast<uint16_t *>(smem + (size_t)k * cstride + (size_t)W * dim * XS_STRIDE) + warp * 256; // [256] per warp
+    {
+        const int total4 = k * dim / 4, dim4 = dim / 4;
+        const float4 *src = reinterpret_cast<const float4 *>(P.codebook);
+        for (int base = 0; base < total4; base += 8 * (int)blockDim.x) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int t = base + u * (int)blockDim.x + (int)threadIdx.x;
+                v[u] = (t < total4) ? __ldg(src + t) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int t = base + u * (int)blockDim.x + (int)threadIdx.x;
+                if (t < total4) {
+                    float *d = cpad + (size_t)(t / dim4) * cstride + (size_t)(t % dim4) * 4;
+                    d[0] = v[u].x, d[1] = v[u].y, d[2] = v[u].z, d[3] = v[u].w;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    const bool euclid = P.euclid != 0;
+    const unsigned long long blocks = (P.n + 255) / 256;
+    bool moved = false;
+    CodeT *codes = reinterpret_cast<CodeT *>(P.codes);
+    for (unsigned long long blk = (unsigned long long)blockIdx.x * W + warp; blk < blocks; blk += (unsigned long long)gridDim.x * W) {
+        const unsigned long long base = blk * 256;
+        // ---- pass A
+        int cnt = 0;
+#pragma unroll 2
+        for (int t = 0; t < 8; ++t) {
+            const unsigned long long row = base + (unsigned long long)(t * 32 + lane);
+            bool need = false;
+            if (row < P.n) {
+                const uint4 lo = __ldg(reinterpret_cast<const uint4 *>(P.cand + row * 8)), hi = __ldg(reinterpret_cast<const uint4 *>(P.cand + row * 8) + 1);
+                const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                int ncand = 0;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ncand += __popc(w[e]);
+                if (ncand == 1) {
+                    const int best = next_bit(w, 0);
+                    const CodeT nc = (CodeT)(best < k ? best : 0);
+                    if (codes[row] != nc) moved = true;
+                    codes[row] = nc;
+                } else {
+                    need = true;
+                }
+            }
+            const unsigned bal = __ballot_sync(0xffffffffu, need);
+            if (need) list[cnt + __popc(bal & ((1u << lane) - 1u))] = (uint16_t)(t * 32 + lane);
+            cnt += __popc(bal);
+        }
+        __syncwarp();
+        // ---- pass B: 32 listed rows at a time
+        for (int i0 = 0; i0 < cnt; i0 += 32) {
+            const int nb = min(32, cnt - i0);
+            {
+                const int dim4 = dim / 4, total4 = nb * dim4;
+                for (int b0 = 0; b0 < total4; b0 += 8 * 32) {
+                    float4 v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int idx = b0 + u * 32 + lane;
+                        v[u] = (idx < total4) ? __ldg(reinterpret_cast<const float4 *>(P.x + (base + list[i0 + idx / dim4]) * dim) + idx % dim4)
+                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int idx = b0 + u * 32 + lane;
+                        if (idx < total4) {
+                            float *d = xs + (size_t)(idx % dim4) * 4 * XS_STRIDE + idx / dim4;
+                            d[0] = v[u].x, d[XS_STRIDE] = v[u].y, d[2 * XS_STRIDE] = v[u].z, d[3 * XS_STRIDE] = v[u].w;
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            const bool valid = lane < nb;
+            const unsigned long long row = valid ? base + list[i0 + lane] : 0ull;
+            const float *xcol = xs + lane;
+            int best = 0, ncand = 0;
+            uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (valid) {
+                const uint4 lo = __ldg(reinterpret_cast<const uint4 *>(P.cand + row * 8)), hi = __ldg(reinterpret_cast<const uint4 *>(P.cand + row * 8) + 1);
+                w[0] = lo.x, w[1] = lo.y, w[2] = lo.z, w[3] = lo.w, w[4] = hi.x, w[5] = hi.y, w[6] = hi.z, w[7] = hi.w;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ncand += __popc(w[e]);
+            }
+            // rows with many candidates (or marked "examine all"): the whole warp scans all centroids, as in resolve_kernel
+            const bool wide = valid && (ncand > 12 || ncand == 0);
+            unsigned wide_rows = __ballot_sync(0xffffffffu, wide);
+            while (wide_rows) {
+                const int r = __ffs(wide_rows) - 1;
+                wide_rows &= wide_rows - 1;
+                const float *xr = xs + r;
+                float bd = VQB_DENSE_INF, d0 = 0.0f;
+                int bi = 0x7fffffff;
+                for (int j = lane; j < k; j += 32) {
+                    const float *c = cpad + (size_t)j * cstride;
+                    float acc = 0.0f;
+                    for (int i = 0; i < dim; ++i) {
+                        const float d = __fsub_rn(xr[i * XS_STRIDE], c[i]);
+                        acc = __fadd_rn(acc, __fmul_rn(d, d));
+                    }
+                    const float d = euclid ? __fsqrt_rn(acc) : acc;
+                    if (j == 0) d0 = d;
+                    if (d < bd) {
+                        bd = d;
+                        bi = j;
+                    }
+                }
+                d0 = __shfl_sync(0xffffffffu, d0, 0);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float od = __shfl_xor_sync(0xffffffffu, bd, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                    if (od < bd || (od == bd && oi < bi)) {
+                        bd = od;
+                        bi = oi;
+                    }
+                }
+                int res = (bi == 0x7fffffff) ? 0 : bi;
+                if (!(d0 == d0)) res = 0;
+                if (bd == VQB_DENSE_INF) res = 0;
+                if (lane == r) best = res;
+            }
+            if (valid) {
+                if (!wide) {
+                    float bd = VQB_DENSE_INF;
+                    int bi = -1;
+                    int j = next_bit(w, 0);
+                    while (j < k) {
+                        int js[4];
+                        js[0] = j;
+#pragma unroll
+                        for (int t = 1; t < 4; ++t) js[t] = (js[t - 1] < 256) ? next_bit(w, js[t - 1] + 1) : 256;
+                        float d[4];
+                        exact_dist4(xcol, cpad + (size_t)min(js[0], k - 1) * cstride, cpad + (size_t)min(js[1], k - 1) * cstride,
+                                    cpad + (size_t)min(js[2], k - 1) * cstride, cpad + (size_t)min(js[3], k - 1) * cstride, dim, euclid, d);
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            if (js[t] >= k) break;
+                            if (js[t] == 0) {
+                                bd = d[t];
+                                bi = 0;
+                            } else {
+                                argmin_update(d[t], js[t], bd, bi);
+                            }
+                        }
+                        j = (js[3] < 256) ? next_bit(w, js[3] + 1) : 256;
+                    }
+                    best = bi < 0 ? 0 : bi;
+                }
+                const CodeT nc = (CodeT)best;
+                if (codes[row] != nc) moved = true;
+                codes[row] = nc;
+            }
+            __syncwarp();
+        }
+    }
+    if (__any_sync(0xffffffffu, moved) && lane == 0) atomicOr(P.changed, 1u);
+}
+
 template <int MODE, typename CodeT> void launch_t(CudaDevice &dev, const ResolveParams &p, const char *name)
 {
     const int threads = 128;
@@ -276,15 +451,29 @@ template <int MODE, typename CodeT> void launch_t(CudaDevice &dev, const Resolve
     dev.count_launch();
 }
 
+template <typename CodeT> void launch_train(CudaDevice &dev, const ResolveParams &p)
+{
+    const int threads = 128;
+    const size_t smem = ((size_t)p.k * (p.dim + 1) + (size_t)(threads / 32) * p.dim * XS_STRIDE) * sizeof(float) + (size_t)(threads / 32) * 256 * sizeof(uint16_t);
+    auto kernel = resolve_train_kernel<CodeT>;
+    VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const unsigned long long blocks = (p.n + 255) / 256;
+    const unsigned grid = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((blocks + 3) / 4, (unsigned long long)dev.sm_count()));
+    KernelScope ks(dev, "resolve_train");
+    kernel<<<grid, threads, smem, dev.stream()>>>(p);
+    VQB_CUDA_CHECK(cudaGetLastError());
+    dev.count_launch();
+}
+
 } // namespace
 
 void launch_resolve(CudaDevice &dev, const ResolveParams &p, int mode, size_t cb)
 {
     if (p.n == 0) return;
     if (mode == R_TRAIN) {
-        if (cb == 1) launch_t<R_TRAIN, uint8_t>(dev, p, "resolve_train");
-        else if (cb == 2) launch_t<R_TRAIN, uint16_t>(dev, p, "resolve_train");
-        else launch_t<R_TRAIN, uint32_t>(dev, p, "resolve_train");
+        if (cb == 1) launch_train<uint8_t>(dev, p);
+        else if (cb == 2) launch_train<uint16_t>(dev, p);
+        else launch_train<uint32_t>(dev, p);
     } else if (mode == R_RVQ_UPDATE) {
         launch_t<R_RVQ_UPDATE, uint32_t>(dev, p, "resolve_rvq_update");
     } else {
