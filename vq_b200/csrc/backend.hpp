@@ -71,6 +71,16 @@ class Device {
         (void)sh;
         (void)x;
     }
+    // One-sided Jacobi sweeps on the device, until no pair of columns rotates.  gt / vt (host, n x n, f64) hold the
+    // working matrix G = A V and V TRANSPOSED (row p = column p), and are updated in place.  Returns false when the
+    // device does not take the shape; the caller then runs the sweeps on the host.  Default: host.
+    virtual bool svd_sweeps(double *gt, double *vt, size_t n)
+    {
+        (void)gt;
+        (void)vt;
+        (void)n;
+        return false;
+    }
     // Nearest centroid under squared Euclidean (src/utils.rs:59-73); codes are read as the previous
     // assignment and overwritten; changed[s] becomes non-zero if any row of subspace s moved (76-80).
     // Subspaces with active[s] == 0 are left untouched.
@@ -125,6 +135,7 @@ bool opq_fit(Device &dev, Comm *comm, const float *x, size_t n_local, size_t dim
              RestartFn restart, void *user, int flags, float *rotation_host, float *codebooks);
 
 // Thin one-sided Jacobi SVD of a square matrix (f64): a = u * diag(s) * v^T, all row-major n x n.
-void jacobi_svd(const double *a, size_t n, double *u, double *s, double *v);
+// With a device the sweeps run there (Device::svd_sweeps) when it takes the shape.
+void jacobi_svd(const double *a, size_t n, double *u, double *s, double *v, Device *dev = nullptr);
 
 } // namespace vqb

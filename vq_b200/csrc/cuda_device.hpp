@@ -33,6 +33,7 @@ class CudaDevice : public Device {
     size_t code_bytes(size_t k) const override { return k <= 256 ? 1 : (k <= 65536 ? 2 : 4); }
 
     void prepare_rows(const Shape &sh, const float *x) override;
+    bool svd_sweeps(double *gt, double *vt, size_t n) override;
     void patch_centroids(const Shape &sh, const float *x, uint64_t row_begin, const RowPatch *patches, size_t n_patches,
                          float *centroids, Comm *comm) override;
     void assign_train(const Shape &sh, const float *x, const float *centroids, void *codes, const uint32_t *active,

@@ -204,7 +204,7 @@ bool opq_fit(Device &dev, Comm *comm, const float *x, size_t n_local, size_t dim
         dev.cross_cov(rec.as<float>(), rotated.as<float>(), n_local, dim, a_d.as<double>());            // 172-179
         if (multi) comm->allreduce_sum_f64(a_d.as<double>(), dim * dim);
         dev.download(a.data(), a_d.p, sizeof(double) * dim * dim);
-        jacobi_svd(a.data(), dim, u.data(), sv.data(), v.data()); // 180-182
+        jacobi_svd(a.data(), dim, u.data(), sv.data(), v.data(), &dev); // 180-182
         for (size_t i = 0; i < dim; ++i)                          // rotation = V * U^T (183)
             for (size_t j = 0; j < dim; ++j) {
                 double acc = 0.0;
@@ -219,7 +219,7 @@ bool opq_fit(Device &dev, Comm *comm, const float *x, size_t n_local, size_t dim
 
 // One-sided (Hestenes) Jacobi SVD in f64.  Columns with a vanishing singular value get an orthonormal
 // completion so that U stays orthogonal (V * U^T must be a rotation even for rank-deficient input).
-void jacobi_svd(const double *a, size_t n, double *u, double *s, double *v)
+void jacobi_svd(const double *a, size_t n, double *u, double *s, double *v, Device *dev)
 {
     // gt / vt hold the working matrices TRANSPOSED (row p = column p of g = a * v), so that each plane rotation
     // streams two contiguous rows.
@@ -228,7 +228,8 @@ void jacobi_svd(const double *a, size_t n, double *u, double *s, double *v)
         for (size_t j = 0; j < n; ++j) gt[j * n + i] = a[i * n + j];
     for (size_t i = 0; i < n; ++i) vt[i * n + i] = 1.0;
     const double eps = 1e-15;
-    for (int sweep = 0; sweep < 60; ++sweep) {
+    const bool on_device = dev && dev->svd_sweeps(gt.data(), vt.data(), n);
+    for (int sweep = 0; !on_device && sweep < 60; ++sweep) {
         bool rotated = false;
         for (size_t p = 0; p + 1 < n; ++p)
             for (size_t q = p + 1; q < n; ++q) {
