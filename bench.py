@@ -212,8 +212,11 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    pq = out = None
     for _ in range(max(3, args.warmup)):
-        one_step(x_dev, False)
+        # results are held exactly as in the timed loop, so that the caller-side allocator (torch's cache: two 256 MB
+        # output blocks alternate) is warm as well and no cudaMalloc lands inside a timed step
+        _f, _e, pq, out = one_step(x_dev, False)
 
     sampler = ClockSampler(local)
     if rank == 0:

@@ -4,6 +4,7 @@
 #include "cuda_device.hpp"
 
 #include <algorithm>
+#include <cstring>
 #include <vector>
 
 #include <cstdlib>
@@ -35,6 +36,12 @@ CudaDevice::CudaDevice(int device) : device_(device)
     smem_limit_ = prop.sharedMemPerBlockOptin;
     VQB_CUDA_CHECK(cudaStreamCreateWithFlags(&own_stream_, cudaStreamNonBlocking));
     stream_ = own_stream_;
+    if (cudaHostAlloc(reinterpret_cast<void **>(&stage_), STAGE_BYTES, cudaHostAllocDefault) != cudaSuccess) {
+        stage_ = nullptr; // pinned memory is an optimisation only
+        cudaGetLastError();
+    } else {
+        VQB_CUDA_CHECK(cudaEventCreateWithFlags(&stage_event_, cudaEventDisableTiming));
+    }
     {
         const char *e = std::getenv("VQB_NO_TENSOR"); // VQB_NO_TENSOR=1: CUDA-core kernels only (A/B comparisons)
         tensor_enabled_ = !(e && *e && *e != '0');
@@ -57,6 +64,8 @@ CudaDevice::~CudaDevice()
         cudaStreamSynchronize(own_stream_);
         for (int i = 0; i < 2; ++i)
             if (aux_[i]) cudaStreamDestroy(aux_[i]);
+        if (stage_event_) cudaEventDestroy(stage_event_);
+        if (stage_) cudaFreeHost(stage_);
         cudaFree(rownorm_);
         cudaFree(hn_scratch_);
         cudaFree(pq_scratch_);
@@ -160,9 +169,30 @@ void CudaDevice::upload(void *dst, const void *src, size_t bytes)
     VQB_CUDA_CHECK(cudaStreamSynchronize(stream_));
 }
 
+// Small downloads sit on the critical path of every k-means iteration (counts and "changed" flags): they go through a
+// pinned staging buffer together with the tensor-core error word -- one copy, one event -- and the host polls the event
+// instead of blocking in the driver, which keeps the latency at a few microseconds whatever the host scheduler does.
 void CudaDevice::download(void *dst, const void *src, size_t bytes)
 {
     if (!bytes) return;
+    if (stage_ && bytes <= STAGE_BYTES - 16) {
+        VQB_CUDA_CHECK(cudaMemcpyAsync(stage_ + 16, src, bytes, cudaMemcpyDeviceToHost, stream_));
+        if (tc_error_) VQB_CUDA_CHECK(cudaMemcpyAsync(stage_, tc_error_, sizeof(int), cudaMemcpyDeviceToHost, stream_));
+        VQB_CUDA_CHECK(cudaEventRecord(stage_event_, stream_));
+        cudaError_t q;
+        while ((q = cudaEventQuery(stage_event_)) == cudaErrorNotReady) {
+        }
+        VQB_CUDA_CHECK(q);
+        std::memcpy(dst, stage_ + 16, bytes);
+        if (tc_error_) {
+            const int code = *reinterpret_cast<const int *>(stage_);
+            if (code != 0) {
+                cudaMemsetAsync(tc_error_, 0, sizeof(int), stream_);
+                throw Error(100, "tensor-core kernel gave up waiting (stage " + std::to_string(code) + "); set VQB_NO_TENSOR=1 to use the CUDA-core path");
+            }
+        }
+        return;
+    }
     VQB_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, stream_));
     VQB_CUDA_CHECK(cudaStreamSynchronize(stream_));
     check_tc_error();

@@ -91,6 +91,9 @@ class CudaDevice : public Device {
     int sm_count_ = 148;
     size_t smem_limit_ = 0;
     cudaStream_t own_stream_ = nullptr, stream_ = nullptr, aux_[2] = {nullptr, nullptr};
+    static constexpr size_t STAGE_BYTES = 1u << 20; // pinned staging for small downloads
+    unsigned char *stage_ = nullptr;
+    cudaEvent_t stage_event_ = nullptr;
     std::atomic<uint64_t> launches_{0};
     // tensor-core path state (dense_tc.cu): row norms of the rows announced by prepare_rows, shortlist scratch
     bool tensor_enabled_ = true;
