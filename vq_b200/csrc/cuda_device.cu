@@ -69,6 +69,7 @@ CudaDevice::~CudaDevice()
         cudaFree(rownorm_);
         cudaFree(hn_scratch_);
         cudaFree(pq_scratch_);
+        cudaFree(pq_marks_);
         cudaFree(cand_);
         cudaFree(tc_stats_);
         cudaFree(tc_error_);
@@ -223,6 +224,21 @@ void CudaDevice::ensure_tc_buffers(size_t n)
         VQB_CUDA_CHECK(cudaMalloc(&cand_, n * DENSE_MASK_WORDS * sizeof(uint32_t)));
         rows_cap_ = n;
     }
+}
+
+uint8_t *CudaDevice::pq_mark_buffer(size_t bytes)
+{
+    if (bytes > pq_marks_cap_) {
+        VQB_CUDA_CHECK(cudaStreamSynchronize(stream_));
+        cudaFree(pq_marks_);
+        pq_marks_ = nullptr;
+        pq_marks_cap_ = 0;
+        const size_t cap = bytes + bytes / 4;
+        VQB_CUDA_CHECK(cudaMalloc(&pq_marks_, cap));
+        pq_marks_cap_ = cap;
+        VQB_CUDA_CHECK(cudaMemsetAsync(pq_marks_, 0, cap, stream_));
+    }
+    return pq_marks_;
 }
 
 // Called at host synchronisation points: a tensor-core kernel whose bounded wait expired leaves a code here.

@@ -34,6 +34,8 @@ class CudaDevice : public Device {
 
     void prepare_rows(const Shape &sh, const float *x) override;
     bool svd_sweeps(double *gt, double *vt, size_t n) override;
+    // Zero-filled map of at least `bytes` bytes for the product-quantizer tensor kernel; its users leave it zero-filled.
+    uint8_t *pq_mark_buffer(size_t bytes);
     void patch_centroids(const Shape &sh, const float *x, uint64_t row_begin, const RowPatch *patches, size_t n_patches,
                          float *centroids, Comm *comm) override;
     void assign_train(const Shape &sh, const float *x, const float *centroids, void *codes, const uint32_t *active,
@@ -100,6 +102,8 @@ class CudaDevice : public Device {
     const float *prepared_x_ = nullptr;
     size_t prepared_n_ = 0, prepared_dim_ = 0;
     float *rownorm_ = nullptr, *hn_scratch_ = nullptr, *pq_scratch_ = nullptr;
+    uint8_t *pq_marks_ = nullptr;
+    size_t pq_marks_cap_ = 0;
     bool pq_tensor_enabled_ = false;
     uint32_t *cand_ = nullptr;
     size_t rows_cap_ = 0;

@@ -509,8 +509,10 @@ template <bool TRAIN, bool EUCLID> __global__ void __launch_bounds__(256) pq_mar
         __syncthreads();
         const unsigned long long mine = base + threadIdx.x;
         if (mine < total16) {
-            const uint4 f = __ldg(reinterpret_cast<const uint4 *>(Q.marks) + mine);
+            const uint4 f = reinterpret_cast<const uint4 *>(Q.marks)[mine];
             const uint32_t w[4] = {f.x, f.y, f.z, f.w};
+            // the map is handed back all zero, so the next launch needs no memset
+            if (f.x | f.y | f.z | f.w) reinterpret_cast<uint4 *>(Q.marks)[mine] = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) {
                 uint32_t word = w[wi];
@@ -641,8 +643,7 @@ void launch_pq_tc(CudaDevice &dev, const AssignParams &p, int metric, bool train
         dev.count_launch();
     }
     const size_t mark_bytes = ((size_t)p.n * (size_t)(p.m / 2) + 15) & ~(size_t)15; // read 16 bytes at a time
-    uint8_t *marks = static_cast<uint8_t *>(dev.alloc(mark_bytes));
-    dev.zero(marks, mark_bytes);
+    uint8_t *marks = dev.pq_mark_buffer(mark_bytes); // all zero between launches: the follow-up kernel clears what it reads
     const CUtensorMap mb = make_tensor_map_2d(bop, KOP, (unsigned long long)p.m * BN, KOP, BN, CU_TENSOR_MAP_SWIZZLE_128B);
     PqTcParams q;
     q.a = p;
@@ -660,7 +661,6 @@ void launch_pq_tc(CudaDevice &dev, const AssignParams &p, int metric, bool train
     if (train) launch_t<true, false>(dev, mb, q, smem, grid);
     else if (metric == M_EUCLID) launch_t<false, true>(dev, mb, q, smem, grid);
     else launch_t<false, false>(dev, mb, q, smem, grid);
-    dev.release(marks);
 }
 
 } // namespace vqb
