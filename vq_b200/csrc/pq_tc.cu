@@ -25,11 +25,14 @@
 //   the reference prefers w over a = argmin S only if D_w <= D_a (1 + 4u) in its own arithmetic (10u relative each), i.e.
 //   S_w <= S_a + 2E + 25u (xh2 + |S_a| + E)  <=  S_a + 4.8e-6 (xh2 + 2HN) + 1.5e-6 (xh2 + |S_a|) + ...  <  limit.
 // The count uses t = sat((limit - S) * 2^p) with p chosen per row so that limit * 2^p ~ 2^60: a score differs from the
-// limit by nothing or by at least one unit in its last place (>= 2^-24 |limit|), so t is exactly 0 or 1, and
-// sum t * (1 + j / 512) yields count and index at once on the FMA pipe.
+// limit by nothing or by at least one unit in its last place (>= 2^-24 |limit|), so t is exactly 0 or 1, and the two sums
+// total = sum t * (1 + (j mod 32) / 512) and offs = sum (j / 32) * t * (1 + (j mod 32) / 512) yield count and index at once on
+// the FMA pipe.  Rows whose true distances could overflow f32 (|x|^2/2 + 2 HN >= 1e37) are marked as well: there the
+// reference's own comparisons see infinities.
 //
 // CTA (1 per SM, persistent, 448 threads), owning 4 consecutive sub-spaces (m / 4 groups share the row tiles):
-//   warp 0       loads the group's four operand-B tiles once (TMA, 128B swizzle, no multicast; 32 KiB each)
+//   warp 0       loads the group's four operand-B tiles once (TMA, 128B swizzle, no multicast; 32 KiB each) and, for an
+//                encode, the binary16 images of the group's centroids (16 KiB, bulk copy)
 //   warp 1       owns tensor memory (two 128 x 256 f32 accumulators) and issues the MMAs
 //   warps 2-5    read row slices from global memory, split them and write operand-A tiles (128 rows x 128 bytes, 128B
 //                swizzle) into a 4-stage ring, plus |x|^2/2 per row
