@@ -118,17 +118,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
     const unsigned long long tile0 = blockIdx.x / ngroups, tstep = gridDim.x / ngroups;
     const unsigned long long n_tiles = (P.n + BM - 1) / BM;
 
-    // the active sub-spaces of this group in issue order (identical in every thread)
-    int list[4], pos[4] = {-1, -1, -1, -1}, nact = 0;
+    // the active sub-spaces of this group in issue order (identical in every thread), packed four bits apiece so that the
+    // lookups below are shifts on a register: indexed local arrays would go through the L1 cache, which the row stream of
+    // the producer warps keeps flushing (each lookup then costs a trip to L2 on the critical path of a unit)
+    uint32_t list_p = 0, pos_p = 0xFFFFu; // list_p: nibble p = sub-space issued p-th; pos_p: nibble ss = its position, 0xF = inactive
+    int nact = 0;
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
         const int ss = issue_order(p);
         const bool act = !(TRAIN && P.active && P.active[g * 4 + ss] == 0);
         if (act) {
-            pos[ss] = nact;
-            list[nact++] = ss;
+            pos_p = (pos_p & ~(0xFu << (4 * ss))) | ((uint32_t)nact << (4 * ss));
+            list_p |= (uint32_t)ss << (4 * nact);
+            ++nact;
         }
     }
+    auto list_at = [&](int p) { return (int)((list_p >> (4 * p)) & 0xFu); };
+    auto pos_of = [&](int ss) { return (int)((pos_p >> (4 * ss)) & 0xFu); }; // 15 = inactive
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
@@ -164,21 +170,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
         // ------------------------------------------------ MMA issuer
         if (lane == 0 && nact > 0) {
             bool ok = mbar_wait(&bars->bfull, 0, abort_flag, Q.error, 12);
-            uint32_t it = 0, uses[2] = {0, 0};
+            uint32_t it = 0, uses0 = 0, uses1 = 0;
             for (unsigned long long tile = tile0; ok && tile < n_tiles && !*abort_flag; tile += tstep) {
                 for (int p = 0; ok && p < nact; ++p, ++it) {
-                    const int ss = list[p];
+                    const int ss = list_at(p);
                     const uint32_t b = (uint32_t)ss >> 1;
                     const int st = it % NSTAGE;
                     if (!mbar_wait(&bars->afull[st], (it / NSTAGE) & 1u, abort_flag, Q.error, 14)) {
                         ok = false;
                         break;
                     }
-                    if (!mbar_wait(&bars->tempty[b], (uses[b] & 1u) ^ 1u, abort_flag, Q.error, 13)) {
+                    const uint32_t ub = b ? uses1 : uses0;
+                    if (!mbar_wait(&bars->tempty[b], (ub & 1u) ^ 1u, abort_flag, Q.error, 13)) {
                         ok = false;
                         break;
                     }
-                    ++uses[b];
+                    if (b) ++uses1;
+                    else ++uses0;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t adesc = smem_desc_sw128(smem_u32(a_smem + (size_t)st * A_STAGE_BYTES));
                     const uint64_t bdesc = smem_desc_sw128(smem_u32(b_smem + (size_t)ss * B_BYTES));
@@ -215,7 +223,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
 #pragma unroll
             for (int ss4 = 0; ss4 < 4; ++ss4) { // static indexing of cur[]; issue order 0, 2, 1, 3
                 const int ss = issue_order(ss4);
-                if (pos[ss] < 0 || !ok) continue;
+                if (pos_of(ss) == 15 || !ok) continue;
                 const int st = it % NSTAGE;
                 if (!mbar_wait(&bars->aempty[st], ((it / NSTAGE) & 1u) ^ 1u, abort_flag, Q.error, 11)) {
                     ok = false;
@@ -267,8 +275,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
 #pragma unroll 1
             for (int h = 0; h < 2; ++h) {
                 const int ss = team * 2 + h;
-                if (pos[ss] < 0) continue;
-                const uint32_t it = tile_iter * (uint32_t)nact + (uint32_t)pos[ss];
+                if (pos_of(ss) == 15) continue;
+                const uint32_t it = tile_iter * (uint32_t)nact + (uint32_t)pos_of(ss);
                 if (!mbar_wait(&bars->tfull[team], uu & 1u, abort_flag, Q.error, 15)) break;
                 ++uu;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
