@@ -29,6 +29,7 @@
 
 #include "cuda_device.hpp"
 #include "dense_tc.hpp"
+#include "kernels_common.cuh"
 #include "tma_host.hpp"
 #include "umma.cuh"
 
@@ -69,8 +70,12 @@ __global__ void __launch_bounds__(192, 1) dense_shortlist_kernel(const __grid_co
     unsigned char *base = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char *c_smem = base;                                            // kchunks x 32 KiB
     unsigned char *x_smem = base + (size_t)MAX_KCHUNKS * C_CHUNK_BYTES;       // NSTAGE x 16 KiB
-    float *hn_s = reinterpret_cast<float *>(x_smem + (size_t)NSTAGE * X_STAGE_BYTES); // 256 floats
-    Barriers *bars = reinterpret_cast<Barriers *>(hn_s + BN);
+    float *hn_s = reinterpret_cast<float *>(x_smem + (size_t)NSTAGE * X_STAGE_BYTES); // 256 floats (diagnostics only)
+    // one more K = 8 step folds the half norms into the accumulator: operand A = (1, 1, 0, ...) for every row, operand B =
+    // (-hn_h, -hn_l, 0, ...) per centroid, hn split into two TF32 numbers; both tiles K-major with 32-byte rows, 32B swizzle
+    unsigned char *a1_smem = reinterpret_cast<unsigned char *>(hn_s + BN);            // 128 rows x 32 bytes
+    unsigned char *bh_smem = a1_smem + BM * 32;                                       // 256 rows x 32 bytes
+    Barriers *bars = reinterpret_cast<Barriers *>(bh_smem + BN * 32);
     volatile int *abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -91,7 +96,22 @@ __global__ void __launch_bounds__(192, 1) dense_shortlist_kernel(const __grid_co
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    for (int t = threadIdx.x; t < BN; t += blockDim.x) hn_s[t] = P.hn[t];
+    for (int t = threadIdx.x; t < BN; t += blockDim.x) {
+        const float hn = P.hn[t]; // +inf beyond k
+        hn_s[t] = hn;
+        const bool pad = !(hn < VQB_DENSE_INF);
+        const float hh = pad ? 1e30f : tf32_round(hn), hl = pad ? 0.0f : tf32_round(hn - hh);
+        unsigned char *rowp = bh_smem + (size_t)(t >> 3) * 256 + (size_t)(t & 7) * 32;
+        const int sw = ((t >> 2) & 1) * 16; // 32B swizzle: the two 16-byte halves of a row swap when bit 2 of the row is set
+        *reinterpret_cast<float4 *>(rowp + sw) = make_float4(-hh, -hl, 0.0f, 0.0f);
+        *reinterpret_cast<float4 *>(rowp + (16 - sw)) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (t < BM) {
+            unsigned char *ap = a1_smem + (size_t)(t >> 3) * 256 + (size_t)(t & 7) * 32;
+            *reinterpret_cast<float4 *>(ap + sw) = make_float4(1.0f, 1.0f, 0.0f, 0.0f);
+            *reinterpret_cast<float4 *>(ap + (16 - sw)) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic writes -> visible to the MMA's reads
     if (warp == 1) { // tensor memory: 512 columns = two 128 x 256 f32 accumulators
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -158,7 +178,10 @@ __global__ void __launch_bounds__(192, 1) dense_shortlist_kernel(const __grid_co
                         umma_tf32(d_tmem, adesc + (uint64_t)(2 * k8), bdesc + (uint64_t)(2 * k8), (kc | k8) ? 1u : 0u);
                     umma_commit(&bars->empty[s]); // the stage is free once these MMAs have read it
                 }
-                if (ok) umma_commit(&bars->tfull[b]);
+                if (ok) {
+                    umma_tf32(d_tmem, smem_desc_sw32(smem_u32(a1_smem)), smem_desc_sw32(smem_u32(bh_smem)), 1u); // D = x.c - hn
+                    umma_commit(&bars->tfull[b]);
+                }
             }
         }
     } else {
@@ -176,8 +199,9 @@ __global__ void __launch_bounds__(192, 1) dense_shortlist_kernel(const __grid_co
             const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + b * BN;
             const float xn2 = valid ? P.xnorm2[row] : 0.0f;
 
-            // pass 1: the two smallest scores; the next 32 columns are in flight while these are processed
-            float best = VQB_DENSE_INF, second = VQB_DENSE_INF;
+            // pass 1: the largest D = x.c - hn, i.e. the smallest score S = -D (four chains of 3-input max); the next 32 columns
+            // are in flight while these are processed
+            float m0 = -VQB_DENSE_INF, m1 = -VQB_DENSE_INF, m2 = -VQB_DENSE_INF, m3 = -VQB_DENSE_INF;
             bool col0_nan = false;
             uint32_t ra[32], rb[32];
             tmem_ld32_issue(taddr, ra);
@@ -187,43 +211,48 @@ __global__ void __launch_bounds__(192, 1) dense_shortlist_kernel(const __grid_co
                 tmem_ld32_issue(taddr + (cb + 1) * 32, rb);
                 if (P.debug_dots && valid) {
 #pragma unroll
-                    for (int t = 0; t < 32; ++t) P.debug_dots[row * BN + cb * 32 + t] = __uint_as_float(ra[t]);
+                    for (int t = 0; t < 32; ++t) P.debug_dots[row * BN + cb * 32 + t] = (cb * 32 + t < P.k) ? __uint_as_float(ra[t]) + hn_s[cb * 32 + t] : 0.0f;
                 }
                 if (cb == 0) {
-                    const float s0 = hn_s[0] - __uint_as_float(ra[0]);
+                    const float s0 = __uint_as_float(ra[0]);
                     col0_nan = !(s0 == s0);
                 }
 #pragma unroll
-                for (int t = 0; t < 32; ++t) {
-                    const float sc = hn_s[cb * 32 + t] - __uint_as_float(ra[t]);
-                    second = fmaxf(best, fminf(second, sc));
-                    best = fminf(best, sc);
+                for (int t = 0; t < 32; t += 8) {
+                    m0 = max3f(m0, __uint_as_float(ra[t]), __uint_as_float(ra[t + 1]));
+                    m1 = max3f(m1, __uint_as_float(ra[t + 2]), __uint_as_float(ra[t + 3]));
+                    m2 = max3f(m2, __uint_as_float(ra[t + 4]), __uint_as_float(ra[t + 5]));
+                    m3 = max3f(m3, __uint_as_float(ra[t + 6]), __uint_as_float(ra[t + 7]));
                 }
                 tmem_wait();
                 if (cb + 2 < BN / 32) tmem_ld32_issue(taddr + (cb + 2) * 32, ra);
                 if (P.debug_dots && valid) {
 #pragma unroll
-                    for (int t = 0; t < 32; ++t) P.debug_dots[row * BN + (cb + 1) * 32 + t] = __uint_as_float(rb[t]);
+                    for (int t = 0; t < 32; ++t)
+                        P.debug_dots[row * BN + (cb + 1) * 32 + t] = ((cb + 1) * 32 + t < P.k) ? __uint_as_float(rb[t]) + hn_s[(cb + 1) * 32 + t] : 0.0f;
                 }
 #pragma unroll
-                for (int t = 0; t < 32; ++t) {
-                    const float sc = hn_s[(cb + 1) * 32 + t] - __uint_as_float(rb[t]);
-                    second = fmaxf(best, fminf(second, sc));
-                    best = fminf(best, sc);
+                for (int t = 0; t < 32; t += 8) {
+                    m0 = max3f(m0, __uint_as_float(rb[t]), __uint_as_float(rb[t + 1]));
+                    m1 = max3f(m1, __uint_as_float(rb[t + 2]), __uint_as_float(rb[t + 3]));
+                    m2 = max3f(m2, __uint_as_float(rb[t + 4]), __uint_as_float(rb[t + 5]));
+                    m3 = max3f(m3, __uint_as_float(rb[t + 6]), __uint_as_float(rb[t + 7]));
                 }
                 tmem_wait();
             }
-            // E = 2.1e-3 |x| cmax (+ the rounding of the stored half norms);
+            const float best = -fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)); // smallest score
+            // E = 2.1e-3 |x| cmax (+ the rounding of the half norms);
             // limit = best + 2E + 1.05 (dim + 6) u (|x|^2 + 2 best + 2E) + rounding slack of the comparison itself
             const float e2 = 2.0f * 2.1e-3f * sqrtf(xn2) * cmax + 8e-6f * cmax * cmax;
             const float d_a = fmaxf(xn2 + 2.0f * best + e2, 0.0f);
             const float limit = best + e2 + 1.05f * (float)(P.dim + 6) * 5.9604645e-8f * d_a + 2.4e-7f * (fabsf(best) + e2) + 1e-36f;
+            const float lim_d = -limit; // centroid j is a candidate when D_j >= lim_d
             // a row the comparisons cannot rank (NaN / infinity somewhere, or centroid 0 not comparable, on which the
             // reference's scan depends) is handed over with every centroid marked
             // (also when a true distance could overflow f32: then the reference's own comparisons see infinities)
-            const bool scan_all = col0_nan || !(second >= best) || !(limit == limit) || !(fabsf(limit) < VQB_DENSE_INF) || !(xn2 + cmax * cmax < 1e37f);
+            const bool scan_all = col0_nan || !(best == best) || !(limit == limit) || !(fabsf(limit) < VQB_DENSE_INF) || !(xn2 + cmax * cmax < 1e37f);
 
-            // pass 2: one bit per centroid, set when S_j <= limit.  The sign of (limit - S_j) is shifted into the word,
+            // pass 2: one bit per centroid, set when D_j >= lim_d.  The sign of (D_j - lim_d) is shifted into the word,
             // so the bits arrive in reverse order and inverted.
             uint32_t words[BN / 32];
             tmem_ld32_issue(taddr, ra);
@@ -233,19 +262,13 @@ __global__ void __launch_bounds__(192, 1) dense_shortlist_kernel(const __grid_co
                 tmem_ld32_issue(taddr + (cb + 1) * 32, rb);
                 uint32_t m = 0;
 #pragma unroll
-                for (int t = 0; t < 32; ++t) {
-                    const float sc = hn_s[cb * 32 + t] - __uint_as_float(ra[t]);
-                    m = __funnelshift_l(__float_as_uint(limit - sc), m, 1);
-                }
+                for (int t = 0; t < 32; ++t) m = __funnelshift_l(__float_as_uint(__uint_as_float(ra[t]) - lim_d), m, 1);
                 words[cb] = ~__brev(m);
                 tmem_wait();
                 if (cb + 2 < BN / 32) tmem_ld32_issue(taddr + (cb + 2) * 32, ra);
                 m = 0;
 #pragma unroll
-                for (int t = 0; t < 32; ++t) {
-                    const float sc = hn_s[(cb + 1) * 32 + t] - __uint_as_float(rb[t]);
-                    m = __funnelshift_l(__float_as_uint(limit - sc), m, 1);
-                }
+                for (int t = 0; t < 32; ++t) m = __funnelshift_l(__float_as_uint(__uint_as_float(rb[t]) - lim_d), m, 1);
                 words[cb + 1] = ~__brev(m);
                 tmem_wait();
             }
@@ -343,7 +366,7 @@ bool dense_tc_applicable(size_t n, size_t dim, size_t k, int metric, const float
 
 size_t dense_tc_smem_bytes()
 {
-    return 1024 + (size_t)MAX_KCHUNKS * C_CHUNK_BYTES + (size_t)NSTAGE * X_STAGE_BYTES + BN * sizeof(float) + sizeof(Barriers) + 64;
+    return 1024 + (size_t)MAX_KCHUNKS * C_CHUNK_BYTES + (size_t)NSTAGE * X_STAGE_BYTES + BN * sizeof(float) + (size_t)(BM + BN) * 32 + sizeof(Barriers) + 64;
 }
 
 void dense_row_norms(CudaDevice &dev, const float *x, size_t n, size_t dim, float *out)

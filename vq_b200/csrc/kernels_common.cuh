@@ -89,6 +89,21 @@ __device__ __forceinline__ float min3f(float a, float b, float c)
     return r;
 }
 
+__device__ __forceinline__ float max3f(float a, float b, float c)
+{
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+// nearest TF32 number (10-bit mantissa), ties away from zero
+__device__ __forceinline__ float tf32_round(float v)
+{
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return __uint_as_float(r);
+}
+
 template <typename CodeT> __device__ __forceinline__ CodeT to_code(int j) { return (CodeT)j; }
 
 } // namespace vqb
