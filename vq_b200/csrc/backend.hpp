@@ -136,6 +136,7 @@ bool opq_fit(Device &dev, Comm *comm, const float *x, size_t n_local, size_t dim
 
 // Thin one-sided Jacobi SVD of a square matrix (f64): a = u * diag(s) * v^T, all row-major n x n.
 // With a device the sweeps run there (Device::svd_sweeps) when it takes the shape.
-void jacobi_svd(const double *a, size_t n, double *u, double *s, double *v, Device *dev = nullptr);
+// v0 (optional, orthogonal n x n): where the sweeps start; the factors satisfy a = u diag(s) v^T either way.
+void jacobi_svd(const double *a, size_t n, double *u, double *s, double *v, Device *dev = nullptr, const double *v0 = nullptr);
 
 } // namespace vqb

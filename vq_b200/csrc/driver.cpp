@@ -204,7 +204,10 @@ bool opq_fit(Device &dev, Comm *comm, const float *x, size_t n_local, size_t dim
         dev.cross_cov(rec.as<float>(), rotated.as<float>(), n_local, dim, a_d.as<double>());            // 172-179
         if (multi) comm->allreduce_sum_f64(a_d.as<double>(), dim * dim);
         dev.download(a.data(), a_d.p, sizeof(double) * dim * dim);
-        jacobi_svd(a.data(), dim, u.data(), sv.data(), v.data(), &dev); // 180-182
+        // The rotation moves little from one outer iteration to the next, so the sweeps start from the previous V: G = A V
+        // then has nearly orthogonal columns and two or three sweeps suffice.  V U^T (the orthogonal polar factor of A^T)
+        // does not depend on where the sweeps start.
+        jacobi_svd(a.data(), dim, u.data(), sv.data(), v.data(), &dev, it > 0 ? v.data() : nullptr); // 180-182
         for (size_t i = 0; i < dim; ++i)                          // rotation = V * U^T (183)
             for (size_t j = 0; j < dim; ++j) {
                 double acc = 0.0;
@@ -219,14 +222,25 @@ bool opq_fit(Device &dev, Comm *comm, const float *x, size_t n_local, size_t dim
 
 // One-sided (Hestenes) Jacobi SVD in f64.  Columns with a vanishing singular value get an orthonormal
 // completion so that U stays orthogonal (V * U^T must be a rotation even for rank-deficient input).
-void jacobi_svd(const double *a, size_t n, double *u, double *s, double *v, Device *dev)
+void jacobi_svd(const double *a, size_t n, double *u, double *s, double *v, Device *dev, const double *v0)
 {
     // gt / vt hold the working matrices TRANSPOSED (row p = column p of g = a * v), so that each plane rotation
     // streams two contiguous rows.
     std::vector<double> gt(n * n), vt(n * n, 0.0);
-    for (size_t i = 0; i < n; ++i)
-        for (size_t j = 0; j < n; ++j) gt[j * n + i] = a[i * n + j];
-    for (size_t i = 0; i < n; ++i) vt[i * n + i] = 1.0;
+    if (v0) { // start from G = A V0, V = V0 (v0 may alias v: it is consumed before v is written)
+        for (size_t i = 0; i < n; ++i)
+            for (size_t j = 0; j < n; ++j) vt[j * n + i] = v0[i * n + j];
+        for (size_t j = 0; j < n; ++j)     // column j of G = A * (column j of V0) = A * (row j of vt)
+            for (size_t i = 0; i < n; ++i) {
+                double acc = 0.0;
+                for (size_t t = 0; t < n; ++t) acc += a[i * n + t] * vt[j * n + t];
+                gt[j * n + i] = acc;
+            }
+    } else {
+        for (size_t i = 0; i < n; ++i)
+            for (size_t j = 0; j < n; ++j) gt[j * n + i] = a[i * n + j];
+        for (size_t i = 0; i < n; ++i) vt[i * n + i] = 1.0;
+    }
     const double eps = 1e-15;
     const bool on_device = dev && dev->svd_sweeps(gt.data(), vt.data(), n);
     for (int sweep = 0; !on_device && sweep < 60; ++sweep) {
