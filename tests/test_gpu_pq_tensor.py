@@ -81,3 +81,30 @@ def test_marked_share_on_the_benchmark_distribution(ctx):
     cb = synth.uniform01(16 * 256, 8, 2).reshape(16, 256, 8)
     _, _, marked = _scores(ctx, x, cb, want_scores=False)
     assert marked < 0.005 * x.shape[0] * 16, marked
+
+
+@pytest.mark.parametrize("n", [1, 5, 127, 128, 129, 257])
+@pytest.mark.parametrize("m,k", [(4, 2), (8, 3), (64, 256)])
+def test_tiny_and_ragged_row_counts(ctx, oracle, n, m, k):
+    rng = np.random.default_rng(n * 1000 + m)
+    x = rng.normal(size=(n, m * 8)).astype(np.float32)
+    cb = rng.normal(size=(m, k, 8)).astype(np.float32)
+    _, codes, _ = _scores(ctx, x, cb, want_scores=False)
+    _, codes_o = oracle.pq_quantize(cb, x, ka.SQ)
+    assert np.array_equal(codes, codes_o)
+
+
+def test_fit_with_retiring_subspaces_matches_oracle(oracle):
+    """Sub-spaces converge at different iterations, so later passes run with some of a group's four sub-spaces inactive."""
+    from tests.util import RecordingSeeder, by_stream
+
+    x = synth.gaussian_mixture(3000, 64, 5, components=4, sigma=0.01)   # few tight clusters: quick, uneven convergence
+    so, sg = RecordingSeeder(9), RecordingSeeder(9)
+    init = so.init_pq(3000, 8, 8)
+    sg.init_pq(3000, 8, 8)
+    cb_o, iters_o = oracle.pq_fit(x, 8, 8, 25, init, so.draw)
+    pq = vq.ProductQuantizer.fit(x, 8, 8, 25, vq.Distance.Euclidean, 9, init_idx=init, draw=sg.draw, accumulate=vq.ACCUM_ORDERED)
+    assert np.array_equal(pq.codebooks, cb_o)
+    assert np.array_equal(pq.iterations, iters_o)
+    assert len(set(int(v) for v in iters_o)) > 1 or int(iters_o[0]) < 25
+    assert by_stream(so.draws) == by_stream(sg.draws)
