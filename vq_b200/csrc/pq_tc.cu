@@ -508,6 +508,8 @@ template <bool TRAIN, bool EUCLID> __global__ void __launch_bounds__(256) pq_mar
     // the list holds the worst case of a step -- and its eight warps then take the pairs in turn, so the work is balanced
     // whatever the distribution of the marks.
     __shared__ uint16_t s_list[256 * 16 * 2];
+    __shared__ float s_x[256][SDW];
+    __shared__ uint8_t s_old[256];
     __shared__ uint32_t s_count;
     const AssignParams &P = Q.a;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -536,60 +538,89 @@ template <bool TRAIN, bool EUCLID> __global__ void __launch_bounds__(256) pq_mar
         }
         __syncthreads();
         const uint32_t cnt = s_count;
-        for (uint32_t i = warp; i < cnt; i += 8) {
-            const uint32_t ent = s_list[i];
-            const unsigned long long e = base * 16ull + (ent >> 1);
-            const int h = (int)(ent & 1u);
-            if (e >= total) continue;
-            const unsigned long long row = e / half;
-            const int rem = (int)(e % half);
-            const int s = (rem >> 1) * 4 + (rem & 1) * 2 + h;
-            float x[SDW];
-            load_slice<SDW>(x, P.x + row * P.ld + (size_t)s * SDW, P.x_vec4 != 0);
-            const float *cbs = P.centroids + (size_t)s * k * SDW;
-            float bd = VQB_INF, d0 = 0.0f;
-            int bi = 0x7fffffff;
-            float c[BN / 32][SDW]; // this lane's centroids j = lane, lane + 32, ...: all requested before the first is used
+        // rounds of up to 256 pairs: first every thread fetches one pair's row slice (and previous code) -- one trip to memory
+        // for the whole round instead of one per pair and warp -- then the warps take the pairs in turn
+        for (uint32_t r0 = 0; r0 < cnt; r0 += 256) {
+            const uint32_t rc = min(256u, cnt - r0);
+            if (threadIdx.x < rc) {
+                const uint32_t ent = s_list[r0 + threadIdx.x];
+                const unsigned long long e = base * 16ull + (ent >> 1);
+                if (e < total) {
+                    const unsigned long long row = e / half;
+                    const int rem = (int)(e % half);
+                    const int s = (rem >> 1) * 4 + (rem & 1) * 2 + (int)(ent & 1u);
+                    float x[SDW];
+                    load_slice<SDW>(x, P.x + row * P.ld + (size_t)s * SDW, P.x_vec4 != 0);
 #pragma unroll
-            for (int u = 0; u < BN / 32; ++u) {
-                const int j = lane + 32 * u;
-                if (j < k) {
-                    load_centroid<SDW>(c[u], cbs + (size_t)j * SDW);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < SDW; ++i) c[u][i] = 0.0f;
+                    for (int i = 0; i < SDW; ++i) s_x[threadIdx.x][i] = x[i];
+                    if (TRAIN) s_old[threadIdx.x] = reinterpret_cast<const uint8_t *>(P.codes)[row * (unsigned long long)m + s];
                 }
             }
+            __syncthreads();
+            for (uint32_t i = warp; i < rc; i += 8) {
+                const uint32_t ent = s_list[r0 + i];
+                const unsigned long long e = base * 16ull + (ent >> 1);
+                const int h = (int)(ent & 1u);
+                if (e >= total) continue;
+                const unsigned long long row = e / half;
+                const int rem = (int)(e % half);
+                const int s = (rem >> 1) * 4 + (rem & 1) * 2 + h;
+                float x[SDW];
 #pragma unroll
-            for (int u = 0; u < BN / 32; ++u) {
-                const int j = lane + 32 * u;
-                float d = reg_dist<SDW, M_SQ>(x, c[u], 0.0f, 0.0f, 0.0f);
-                if (EUCLID) d = __fsqrt_rn(d);
-                if (j == 0) d0 = d;
-                if (j < k && d < bd) {
-                    bd = d;
-                    bi = j;
-                }
-            }
+                for (int t = 0; t < SDW; ++t) x[t] = s_x[i][t];
+                const float *cbs = P.centroids + (size_t)s * k * SDW;
+                float bd = VQB_INF, d0 = 0.0f;
+                int bi = 0x7fffffff;
+                float c[BN / 32][SDW]; // this lane's centroids j = lane, lane + 32, ...: all requested before the first is used
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float od = __shfl_xor_sync(0xffffffffu, bd, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (od < bd || (od == bd && oi < bi)) {
-                    bd = od;
-                    bi = oi;
+                for (int u = 0; u < BN / 32; ++u) {
+                    const int j = lane + 32 * u;
+                    if (j < k) {
+                        load_centroid<SDW>(c[u], cbs + (size_t)j * SDW);
+                    } else {
+#pragma unroll
+                        for (int t = 0; t < SDW; ++t) c[u][t] = 0.0f;
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < BN / 32; ++u) {
+                    const int j = lane + 32 * u;
+                    float d = reg_dist<SDW, M_SQ>(x, c[u], 0.0f, 0.0f, 0.0f);
+                    if (EUCLID) d = __fsqrt_rn(d);
+                    if (j == 0) d0 = d;
+                    if (j < k && d < bd) {
+                        bd = d;
+                        bi = j;
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float od = __shfl_xor_sync(0xffffffffu, bd, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                    if (od < bd || (od == bd && oi < bi)) {
+                        bd = od;
+                        bi = oi;
+                    }
+                }
+                d0 = __shfl_sync(0xffffffffu, d0, 0);
+                const int idx = (bi == 0x7fffffff || !(d0 == d0)) ? 0 : bi; // nothing below +inf, or the scan started at a NaN
+                if (lane == 0) {
+                    bool moved = false;
+                    if (TRAIN) {
+                        if (s_old[i] != (uint8_t)idx) {
+                            moved = true;
+                            reinterpret_cast<uint8_t *>(P.codes)[row * (unsigned long long)m + s] = (uint8_t)idx;
+                        }
+                    } else {
+                        store_result<SDW, uint8_t, TRAIN>(P, row, s, idx, cbs, moved);
+                    }
+                    if (moved) {
+                        if (s < 32) moved_lo |= 1u << s;
+                        else moved_hi |= 1u << (s - 32);
+                    }
                 }
             }
-            d0 = __shfl_sync(0xffffffffu, d0, 0);
-            const int idx = (bi == 0x7fffffff || !(d0 == d0)) ? 0 : bi; // nothing below +inf, or the scan started at a NaN
-            if (lane == 0) {
-                bool moved = false;
-                store_result<SDW, uint8_t, TRAIN>(P, row, s, idx, cbs, moved);
-                if (moved) {
-                    if (s < 32) moved_lo |= 1u << s;
-                    else moved_hi |= 1u << (s - 32);
-                }
-            }
+            __syncthreads(); // the staged slices are rewritten by the next round
         }
         __syncthreads(); // the list is rewritten by the next step
     }
