@@ -139,6 +139,29 @@ int main()
         CHECK(panics_with([] { BinaryQuantizer::fit(0.0f, 1, 1); }, "Low quantization level must be less than high quantization level"));
     }
 
+    // tests/test_tsvq.rs:11-22: ten copies of one vector, depth 3: the quantized vector equals it within 1e-6
+    {
+        Vector<float> v({1, 2, 3, 4, 5});
+        std::vector<Vector<float>> data(10, v);
+        TSVQ tsvq(data, 3, Distance::SquaredEuclidean());
+        Vector<f16> q = tsvq.quantize(v);
+        CHECK(q.len() == v.len());
+        for (size_t i = 0; i < v.len(); ++i) CHECK(approx_eq(q.data[i].to_f32(), v.data[i], 1e-6f));
+        CHECK(panics_with([&] { tsvq.quantize(Vector<float>({1, 2, 3})); }, "Dimension mismatch: expected 5, got 3"));
+        CHECK(panics_with([] { TSVQ(std::vector<Vector<float>>{}, 3, Distance::Euclidean()); }, "Empty input"));
+    }
+    // tests/test_tsvq.rs:24-43: 1000 random vectors of width 10, depth 3: every output has the input's length and is finite
+    {
+        auto data = generate_test_data(1000, 10);
+        TSVQ tsvq(data, 3, Distance::SquaredEuclidean());
+        bool ok = true;
+        for (size_t i = 0; i < data.size(); i += 37) {
+            Vector<f16> q = tsvq.quantize(data[i]);
+            ok = ok && q.len() == data[i].len();
+            for (size_t t = 0; t < q.len(); ++t) ok = ok && std::isfinite(q.data[t].to_f32());
+        }
+        CHECK(ok);
+    }
     // tests/test_tsvq.rs:11-22 pins f16 exactness on representable values; same property through PQ's f16 output
     {
         std::vector<Vector<float>> same(10, Vector<float>({1, 2, 3, 4, 5, 6}));

@@ -306,6 +306,30 @@ class OptimizedProductQuantizer {
     std::shared_ptr<vqb_opq> h_;
 };
 
+// TSVQ (src/tsvq.rs:189-250)
+class TSVQ {
+  public:
+    TSVQ(const std::vector<Vector<float>> &training_data, size_t max_depth, Distance distance_) : distance(distance_)
+    {
+        vqb_ctx *c = detail::context();
+        size_t dim = 0;
+        std::vector<float> flat = detail::pack_rows(training_data, &dim);
+        vqb_tsvq *h = nullptr;
+        detail::check(vqb_tsvq_fit(c, flat.data(), training_data.size(), dim, max_depth, distance.metric, distance.p, &h), c);
+        h_ = std::shared_ptr<vqb_tsvq>(h, vqb_tsvq_destroy);
+    }
+    Vector<f16> quantize(const Vector<float> &vector) const
+    {
+        std::vector<uint16_t> out(vector.len());
+        detail::check(vqb_tsvq_quantize(h_.get(), vector.data.data(), 1, vector.len(), out.data(), nullptr), detail::context());
+        return detail::to_f16(out);
+    }
+    Distance distance;
+
+  private:
+    std::shared_ptr<vqb_tsvq> h_;
+};
+
 struct ScalarQuantizer {
     float min, max;
     size_t levels;
