@@ -36,11 +36,17 @@ METRIC_NAME, UNIT = "pq_fit_plus_encode_throughput", "Mvec/s"
 # algorithmic bytes per vector (what must cross HBM): training pass = 512 B row + 16 B old codes + 16 B new codes;
 # encode = 512 B row + 256 B f16 output.
 TRAIN_BYTES_PER_VEC, ENCODE_BYTES_PER_VEC = 544, 768
-# DRAM traffic per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the 1M-row workload,
-# from the captures summarised under profiles/ (valid for the 1M-row, 1-GPU workload).
-# assign_train: pq_tc_kernel, 530.6 B read + 27 B written per row on a 262144-row capture, scaled to 1M rows (traffic grows
-# with the rows: every row is read once) -- profiles/pq_tc_kernel_pq_1m.md; the encode launch was not captured.
+# DRAM traffic per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum): assign_train = pq_tc_kernel,
+# 530.6 B read + 27 B written per row on a 262144-row capture, scaled to 1M rows (traffic grows with the rows: every row
+# is read once); the encode launch was not captured.
 NCU_TRAFFIC_BYTES = {"assign_train": 558.0e6, "pq_encode": None}
+
+
+def workload_config(rows: int, world: int) -> dict:
+    """The workload both arms report: same keys, same values."""
+    return {"workload": "pq_1m_x128_m16_k256_10iters_fit_plus_encode", "rows": rows, "dim": DIM, "m": M, "k": K,
+            "lbg_iters": ITERS, "distance": "Euclidean", "parallelism": f"rows sharded over {world} GPU(s)",
+            "l2": "256 MiB flush write before every step; the 512 MB row matrix exceeds L2 at N=1"}
 
 
 def measured_peaks():
@@ -102,14 +108,15 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_reference(rows: int, steps: int, warmup: int):
+def cpu_reference(rows: int, steps: int, warmup: int, x=None):
     """The reference's algorithm on the host cores: oracle/ (C restatement, OpenMP over points, all threads)."""
     import oracle
     from vq_b200 import synth
     from vq_b200.seeding import LbgSeeder
     oracle.build()
     oracle.use_all_host_threads()
-    x = synth.uniform01(rows, DIM, DATA_SEED)
+    if x is None:
+        x = synth.uniform01(rows, DIM, DATA_SEED)
     times = []
     for it in range(warmup + steps):
         seeder = LbgSeeder(FIT_SEED)
@@ -124,7 +131,8 @@ def cpu_reference(rows: int, steps: int, warmup: int):
     fit_s = sum(t[0] for t in times) / len(times)
     enc_s = sum(t[1] for t in times) / len(times)
     return {"value": rows / (fit_s + enc_s) / 1e6, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
-            "sample": f"{rows} of {N_ROWS} rows, full algorithm (10 LBG iterations + encode), scaled per vector",
+            "sample": (f"all {rows} rows, full algorithm (10 LBG iterations + encode), {len(times)} run(s)" if rows == N_ROWS else
+                       f"{rows} of {N_ROWS} rows, full algorithm (10 LBG iterations + encode), scaled per vector"),
             "train_s_per_1m_rows": fit_s * N_ROWS / rows, "encode_mvec_per_s": rows / enc_s / 1e6}
 
 
@@ -132,17 +140,90 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    rows = args.rows or 32768
+    rows = args.rows or N_ROWS  # the whole workload: about 6 s per step on 16 host threads
     cb = cpu_reference(rows, max(1, args.steps), max(0, min(args.warmup, 1)))
     step_s = rows / (cb["value"] * 1e6)
     line = {"impl": "reference", "metric": METRIC_NAME, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "pq_1m_x128_m16_k256_10iters_fit_plus_encode", "rows_timed": rows},
+            "config": workload_config(N_ROWS, args.gpus), "rows_timed": rows,
             "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
+
+
+def full_size_parity(vq, ctx, dist, rank, world, x_dev, x_host, begin, n_local, n_global, init, pq10, out10):
+    """The parity figures at the benchmark's own size, outside every timed region (reported, never timed):
+    centroid error after one iteration against the oracle on all rows, final-MSE ratio with 10-iteration codebooks, code
+    mismatches and near-ties on >= 100,000 rows given identical codebooks, and (N > 1) bit-identical codebooks on all ranks.
+    Rank 0 also times the oracle's full-size fit + encode it needs for this: that is the CPU baseline."""
+    import torch
+    from vq_b200 import synth
+    from vq_b200.seeding import LbgSeeder
+
+    # every rank: one library iteration from the same initial rows (a collective when sharded)
+    seeder = LbgSeeder(FIT_SEED)
+    for i in range(M):
+        seeder.init_indices(i, n_global, K)
+    pq1 = vq.ProductQuantizer.fit(x_dev, M, K, 1, vq.Distance.Euclidean, FIT_SEED, ctx=ctx, init_idx=init, draw=seeder.draw)
+    cb1, cb10 = pq1.codebooks, pq10.codebooks
+    identical = None
+    if world > 1:  # every rank must hold the same bits
+        digest = torch.tensor([int(np.frombuffer(cb10.tobytes(), dtype=np.uint32).astype(np.uint64).sum() & 0x7FFFFFFFFFFFFFFF),
+                               int(np.bitwise_xor.reduce(np.frombuffer(cb10.tobytes(), dtype=np.uint32)))], dtype=torch.int64, device="cuda")
+        lo, hi = digest.clone(), digest.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        identical = bool(torch.equal(lo, hi))
+    if rank != 0:
+        return None, None
+    try:
+        import oracle
+        oracle.build()
+        oracle.use_all_host_threads()
+        x_all = x_host.numpy() if world == 1 else synth.uniform01(n_global, DIM, DATA_SEED)
+        s1 = LbgSeeder(FIT_SEED)
+        for i in range(M):
+            s1.init_indices(i, n_global, K)
+        ocb1, _ = oracle.pq_fit(x_all, M, K, 1, init, s1.draw)
+        rel = np.linalg.norm(cb1.astype(np.float64) - ocb1, axis=2) / np.maximum(np.linalg.norm(ocb1.astype(np.float64), axis=2), 1e-30)
+        s10 = LbgSeeder(FIT_SEED)
+        for i in range(M):
+            s10.init_indices(i, n_global, K)
+        t0 = time.perf_counter()
+        ocb10, _ = oracle.pq_fit(x_all, M, K, ITERS, init, s10.draw)
+        t1 = time.perf_counter()
+        o16_all, _codes_all = oracle.pq_quantize(ocb10, x_all, oracle.EUCLIDEAN)
+        t2 = time.perf_counter()
+        shard = x_all[begin:begin + n_local]
+        mse_oracle = oracle.mse_f16(shard, o16_all[begin:begin + n_local])
+        lib16 = out10.cpu().numpy() if hasattr(out10, "cpu") else np.asarray(out10)
+        mse_lib = oracle.mse_f16(shard, lib16.view(np.uint16))
+        # identical codebooks (the library's), >= 100,000 rows: codes must agree outside near-ties
+        rows = min(n_local, 131072)
+        sample = shard[:rows]
+        _o, codes_o = oracle.pq_quantize(cb10, sample, oracle.EUCLIDEAN)
+        _g, codes_g = pq10.quantize(sample, return_codes=True)
+        mism = int((codes_o != np.asarray(codes_g)).sum())
+        near = 0
+        sd = DIM // M
+        for s_ in range(M):  # the oracle's two smallest distances per (row, sub-space), relative gap < 1e-6
+            xs = sample[:, s_ * sd:(s_ + 1) * sd].astype(np.float64)
+            cs = cb10[s_].astype(np.float64)
+            d = (xs * xs).sum(1)[:, None] - 2.0 * xs @ cs.T + (cs * cs).sum(1)[None, :]
+            two = np.partition(d, 1, axis=1)[:, :2]
+            near += int(((two[:, 1] - two[:, 0]) < 1e-6 * np.maximum(two[:, 1], 1e-30)).sum())
+        parity = {"centroid_rel_err_iter1": float(rel.max()), "centroid_rel_err_bar": 1e-3,
+                  "mse_library": float(mse_lib), "mse_oracle": float(mse_oracle), "mse_ratio": float(mse_lib / mse_oracle), "mse_ratio_bar": "within 1 %",
+                  "code_rows": rows, "code_mismatches": mism, "near_ties": near,
+                  "codebooks_identical_on_all_ranks": identical, "rows_fitted_by_oracle": int(n_global)}
+        cpu = {"value": n_global / ((t1 - t0) + (t2 - t1)) / 1e6, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+               "sample": f"all {n_global} rows, full algorithm (10 LBG iterations + encode), one run",
+               "train_s_per_1m_rows": (t1 - t0) * N_ROWS / n_global, "encode_mvec_per_s": n_global / (t2 - t1) / 1e6}
+        return parity, cpu
+    except Exception as exc:  # the oracle is only a checker; the bench line survives without it
+        return {"error": f"{type(exc).__name__}: {exc}"[:200], "codebooks_identical_on_all_ranks": identical}, None
 
 
 def run_ours(args):
@@ -221,20 +302,28 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ctx.timing(True)
-    ctx.timing_report()
     launches0 = ctx.launch_count()
     fit_s, enc_s = [], []
-    for _ in range(args.steps):
+    for _ in range(args.steps):  # the loop behind `value`: no per-kernel events in it
         f, e, pq, out = one_step(x_dev, True)
         fit_s.append(max_over_ranks(f))
         enc_s.append(max_over_ranks(e))
         if os.environ.get("VQB_BENCH_DEBUG"):
             print(f"[rank {rank}] fit {f * 1e3:.3f} ms encode {e * 1e3:.3f} ms", file=sys.stderr, flush=True)
     launches = ctx.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else {}
+
+    # per-kernel breakdown (roofline inputs): the same steps again with CUDA events around every launch
+    ctx.timing(True)
+    ctx.timing_report()
+    breakdown_steps = max(1, min(5, args.steps))
+    for _ in range(breakdown_steps):
+        one_step(x_dev, True)
     kernels = ctx.timing_report()
     ctx.timing(False)
-    clocks = sampler.stop() if rank == 0 else {}
+    for v in kernels.values():
+        v["launches_per_step"] = v["launches"] / breakdown_steps
+        v["ms_per_step"] = v["ms"] / breakdown_steps
 
     # end to end: same public API, pinned host buffers in, host f16 out; copies inside the timed region
     e2e_s = []
@@ -243,19 +332,9 @@ def run_ours(args):
         if i > 0:
             e2e_s.append(max_over_ranks(f + e))
 
-    # parity spot check on the last device-resident step (rank 0, 512 rows): codes vs the CPU oracle given the
-    # trained codebooks; reported, never timed
-    parity = None
-    if rank == 0:
-        try:
-            import oracle
-            cb = pq.codebooks
-            sample = x_host.numpy()[:512]
-            _o16, codes_o = oracle.pq_quantize(cb, sample, oracle.EUCLIDEAN)
-            _g16, codes_g = pq.quantize(sample, return_codes=True)
-            parity = {"rows": 512, "code_mismatches": int((codes_o != codes_g).sum())}
-        except Exception as exc:  # the oracle is only a checker; the bench line survives without it
-            parity = {"error": str(exc)[:100]}
+    parity, cpu = None, None
+    if not args.kernels_only:
+        parity, cpu = full_size_parity(vq, ctx, dist, rank, world, x_dev, x_host, begin, n_local, n_global, init, pq, out)
 
     if rank != 0:
         if world > 1:
@@ -283,19 +362,17 @@ def run_ours(args):
 
     dominant = max(kernels, key=lambda kname: kernels[kname]["ms"]) if kernels else None
     roofline = roof("assign_train", TRAIN_BYTES_PER_VEC)
-    cb_rows = 32768
-    cpu = None if (args.kernels_only or world > 1) else cpu_reference(cb_rows, 1, 0)  # rank 0 at N=1 only
+    if world > 1:
+        cpu = None  # the CPU baseline is reported by rank 0 at N=1 only
     e2e_step = sum(e2e_s) / len(e2e_s) if e2e_s else float("nan")
     line = {
         "metric": METRIC_NAME, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "pq_1m_x128_m16_k256_10iters_fit_plus_encode", "rows": n_global, "dim": DIM, "m": M, "k": K,
-                   "lbg_iters": ITERS, "distance": "Euclidean", "parallelism": f"rows sharded over {world} GPU(s)",
-                   "l2": "256 MiB flush write before every step; the 512 MB row matrix exceeds L2 at N=1"},
+        "config": workload_config(n_global, world),
         "train_s": train_s, "encode_s": encode_s, "encode_mvec_per_s": n_global / encode_s / 1e6,
         "roofline": roofline, "roofline_encode": roof("pq_encode", ENCODE_BYTES_PER_VEC),
-        "dominant_kernel": dominant, "kernels": kernels,
+        "dominant_kernel": dominant, "kernels": kernels, "kernels_note": f"separate pass of {breakdown_steps} step(s) with CUDA events around every launch",
         "cpu_baseline": cpu,
         "e2e": {"value": n_global / e2e_step / 1e6, "unit": UNIT,
                 "h2d_bytes_per_step": 2 * n_local * DIM * 4 + int(init.nbytes), "d2h_bytes_per_step": n_local * DIM * 2 + ITERS * (M * K + M) * 4,

@@ -93,9 +93,14 @@ const char *vqb_last_error(const vqb_ctx *ctx);
 int vqb_ctx_set_stream(vqb_ctx *ctx, void *cuda_stream);
 /* Back to the context's own (non-blocking) stream, the state after creation. */
 int vqb_ctx_reset_stream(vqb_ctx *ctx);
+/* Waits for the context's stream.  Also the place where a caller that passes DEVICE outputs (and therefore never
+ * triggers a download) learns that a tensor-core kernel gave up on one of its bounded waits: VQB_ERR_CUDA with a message. */
 int vqb_ctx_synchronize(vqb_ctx *ctx);
 /* Number of kernels this context has launched so far. */
 int vqb_ctx_launch_count(const vqb_ctx *ctx, uint64_t *out);
+/* How many times this context has asked CUDA for device or pinned memory so far (cudaMalloc, cudaMallocAsync,
+ * cudaHostAlloc).  No counterpart in the reference; lets an embedder (and the tests) check that a call allocated nothing. */
+int vqb_ctx_alloc_count(const vqb_ctx *ctx, uint64_t *out);
 
 /* Per-kernel timing with CUDA events on the launching stream (off by default; the reference times
  * with std::time::Instant around whole calls, src/bin/eval_pq.rs:42-44,50-60).  The report is JSON:
@@ -212,7 +217,10 @@ int vqb_opq_quantize(vqb_opq *opq, const float *x, size_t n, size_t dim, uint16_
  * For embedders that own all of HBM through their own pool, or that must not enter the CUDA allocator from a
  * request loop: the rotated rows that vqb_opq_quantize keeps in pool memory live here in a fixed array inside
  * the library image (VQB_OPQ_STATIC_MAX_FLOATS floats = 4 MiB, resident on every GPU that loads the library,
- * for the life of the process).
+ * for the life of the process), and the nearest-centroid step runs on the CUDA-core kernels, which work out of
+ * shared memory and registers (the tensor-core kernel of vqb_opq_quantize needs operand tiles and a mark map in
+ * device memory).  The call makes no cudaMalloc / cudaMallocAsync / cudaFree and creates no event, on its first
+ * use of a context as on any later one (vqb_ctx_alloc_count stays unchanged across it).
  *   - x, out_f16 and codes must be DEVICE pointers (either output may be NULL, not both); host pointers are
  *     refused because staging them would allocate;
  *   - n * dim must not exceed VQB_OPQ_STATIC_MAX_FLOATS, otherwise VQB_ERR_UNSUPPORTED with a message;

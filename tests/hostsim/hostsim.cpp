@@ -74,8 +74,8 @@ class HostDevice : public Device {
             std::memcpy(centroids + ((size_t)patches[p].subspace * sh.k + patches[p].cluster) * sh.sd, &stage[p * sh.sd],
                         sh.sd * sizeof(float));
     }
-    void assign_train(const Shape &sh, const float *x, const float *centroids, void *codes_v, const uint32_t *active,
-                      uint32_t *changed) override
+    bool assign_train(const Shape &sh, const float *x, const float *centroids, void *codes_v, const uint32_t *active,
+                      const IterBuffers &buf, bool) override
     {
         uint32_t *codes = (uint32_t *)codes_v;
         for (size_t s = 0; s < sh.m; ++s) {
@@ -91,37 +91,62 @@ class HostDevice : public Device {
                         best = (uint32_t)j;
                     }
                 }
-                if (codes[i * sh.m + s] != best) changed[s] = 1;
+                if (codes[i * sh.m + s] != best) buf.moved[s] |= 0x3F800000u; // the bits of 1.0f, as the kernels write them
                 codes[i * sh.m + s] = best;
             }
         }
+        return false; // the sums are always a separate pass here
     }
-    void accumulate(const Shape &sh, const float *x, const void *codes_v, const uint32_t *active, bool, float *sums,
-                    uint32_t *counts) override
+    static void add_count(const IterBuffers &buf, size_t at)
+    {
+        if (buf.counts_f32) {
+            float c;
+            std::memcpy(&c, &buf.counts[at], 4);
+            c += 1.0f;
+            std::memcpy(&buf.counts[at], &c, 4);
+        } else {
+            buf.counts[at]++;
+        }
+    }
+    void accumulate(const Shape &sh, const float *x, const void *codes_v, const uint32_t *active, bool, const IterBuffers &buf) override
     {
         const uint32_t *codes = (const uint32_t *)codes_v;
-        std::memset(sums, 0, sizeof(float) * sh.m * sh.k * sh.sd);
-        std::memset(counts, 0, sizeof(uint32_t) * sh.m * sh.k);
         for (size_t s = 0; s < sh.m; ++s) {
             if (active && !active[s]) continue;
             for (size_t i = 0; i < sh.n_local; ++i) {
                 size_t j = codes[i * sh.m + s];
-                float *dst = sums + (s * sh.k + j) * sh.sd;
+                float *dst = buf.sums + (s * sh.k + j) * sh.sd;
                 const float *v = x + i * sh.ld + s * sh.sd;
                 for (size_t c = 0; c < sh.sd; ++c) dst[c] = dst[c] + v[c];
-                counts[s * sh.k + j]++;
+                add_count(buf, s * sh.k + j);
             }
         }
     }
-    void finalize(const Shape &sh, const float *sums, const uint32_t *counts, const uint32_t *active, float *centroids) override
+    void update_centroids(const Shape &sh, const IterBuffers &buf, const uint32_t *active, float *centroids, IterStatus &st) override
     {
+        const size_t wps = (sh.k + 31) / 32;
+        st.moved.assign(sh.m, 0);
+        st.has_empty.assign(sh.m, 0);
+        st.empty_bits.assign(sh.m * wps, 0u);
         for (size_t s = 0; s < sh.m; ++s) {
-            if (active && !active[s]) continue;
+            const bool act = !active || active[s];
+            st.moved[s] = act && buf.moved[s] != 0;
+            buf.moved[s] = 0;
+            if (!act) continue;
             for (size_t j = 0; j < sh.k; ++j) {
-                uint32_t c = counts[s * sh.k + j];
-                if (!c) continue;
-                for (size_t t = 0; t < sh.sd; ++t)
-                    centroids[(s * sh.k + j) * sh.sd + t] = sums[(s * sh.k + j) * sh.sd + t] / (float)c;
+                float cf;
+                if (buf.counts_f32) std::memcpy(&cf, &buf.counts[s * sh.k + j], 4);
+                else cf = (float)buf.counts[s * sh.k + j];
+                if (cf == 0.0f) {
+                    st.empty_bits[s * wps + j / 32] |= 1u << (j % 32);
+                    st.has_empty[s] = 1;
+                    continue;
+                }
+                for (size_t t = 0; t < sh.sd; ++t) {
+                    centroids[(s * sh.k + j) * sh.sd + t] = buf.sums[(s * sh.k + j) * sh.sd + t] / cf;
+                    buf.sums[(s * sh.k + j) * sh.sd + t] = 0.0f;
+                }
+                buf.counts[s * sh.k + j] = 0;
             }
         }
     }

@@ -153,6 +153,12 @@ class Context:
         _lib.load().vqb_ctx_launch_count(self.handle, C.byref(n))
         return int(n.value)
 
+    def alloc_count(self) -> int:
+        """How often this context has asked CUDA for device or pinned memory so far."""
+        n = C.c_uint64(0)
+        _lib.load().vqb_ctx_alloc_count(self.handle, C.byref(n))
+        return int(n.value)
+
     def timing(self, enable: bool):
         rc = _lib.load().vqb_ctx_timing(self.handle, 1 if enable else 0)
         if rc:

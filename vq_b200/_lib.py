@@ -31,6 +31,7 @@ SIGNATURES = {
     "vqb_ctx_reset_stream": (C.c_int, [_P]),
     "vqb_ctx_synchronize": (C.c_int, [_P]),
     "vqb_ctx_launch_count": (C.c_int, [_P, C.POINTER(C.c_uint64)]),
+    "vqb_ctx_alloc_count": (C.c_int, [_P, C.POINTER(C.c_uint64)]),
     "vqb_ctx_timing": (C.c_int, [_P, C.c_int]),
     "vqb_ctx_timing_report": (C.c_int, [_P, C.c_char_p, _SZ]),
     "vqb_comm_unique_id": (C.c_int, [_P]),

@@ -305,6 +305,13 @@ int vqb_ctx_launch_count(const vqb_ctx *ctx, uint64_t *out)
     return VQB_OK;
 }
 
+int vqb_ctx_alloc_count(const vqb_ctx *ctx, uint64_t *out)
+{
+    if (!ctx || !out) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "NULL argument");
+    *out = ctx->dev->device_allocs();
+    return VQB_OK;
+}
+
 int vqb_ctx_timing(vqb_ctx *ctx, int enable)
 {
     if (!ctx) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "ctx is NULL");

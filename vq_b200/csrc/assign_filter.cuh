@@ -244,7 +244,7 @@ __global__ void __launch_bounds__((SD == 8 && V == 2) ? 1024 : 512, 1) assign_fi
         }
     }
     if (TRAIN) {
-        if (__any_sync(0xffffffffu, moved) && lane == 0) atomicOr(P.changed + s, 1u);
+        if (__any_sync(0xffffffffu, moved) && lane == 0) atomicOr(P.changed + s, VQB_MOVED_BITS);
     }
 }
 

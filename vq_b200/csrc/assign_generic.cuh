@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(256) assign_generic_kernel(const GenericParams
         }
     }
     if (MODE == G_TRAIN) {
-        if (__any_sync(0xffffffffu, moved) && lane == 0) atomicOr(P.changed + s, 1u);
+        if (__any_sync(0xffffffffu, moved) && lane == 0) atomicOr(P.changed + s, VQB_MOVED_BITS);
     }
     if (MODE == G_RVQ_UPDATE) {
 #pragma unroll

@@ -250,7 +250,7 @@ __global__ void __launch_bounds__(512, 1) assign_reg_kernel(const AssignParams P
         }
     }
     if (TRAIN) {
-        if (__any_sync(0xffffffffu, moved) && lane == 0) atomicOr(P.changed + s, 1u);
+        if (__any_sync(0xffffffffu, moved) && lane == 0) atomicOr(P.changed + s, VQB_MOVED_BITS);
     }
 }
 

@@ -10,6 +10,7 @@
 #include <cstdint>
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 namespace vqb {
 
@@ -29,6 +30,28 @@ struct RowPatch {
 // n_local rows of `ld` floats; subspace s covers columns [s*sd, (s+1)*sd); k centroids per subspace.
 struct Shape {
     size_t n_local = 0, ld = 0, m = 0, sd = 0, k = 0;
+};
+
+// What one k-means iteration gathers on the device, in ONE allocation so that one all-reduce covers it:
+//   sums[m][k][sd] f32 | counts[m][k] | moved[m]
+// counts hold u32 values, or f32 values when counts_f32 is set (exact below 2^24 rows, which lets the three parts
+// travel as a single f32 all-reduce).  moved[s] is zero or has the bits of 1.0f OR-ed in (non-zero either way; a sum of
+// such words over ranks read as f32 stays non-zero).  The buffer starts zero-filled; update_centroids hands it back
+// zero-filled.
+struct IterBuffers {
+    float *sums = nullptr;
+    uint32_t *counts = nullptr;
+    uint32_t *moved = nullptr;
+    bool counts_f32 = false;
+    size_t words(const Shape &sh) const { return sh.m * sh.k * sh.sd + sh.m * sh.k + sh.m; }
+};
+
+// What the host learns from one iteration (src/utils.rs:76-80,95-106): which subspaces saw a row move and which
+// (subspace, cluster) slots received no row.
+struct IterStatus {
+    std::vector<uint8_t> moved;          // [m]
+    std::vector<uint8_t> has_empty;      // [m]
+    std::vector<uint32_t> empty_bits;    // [m][ceil(k / 32)], bit j of subspace s = cluster j is empty
 };
 
 class Comm {
@@ -82,17 +105,20 @@ class Device {
         return false;
     }
     // Nearest centroid under squared Euclidean (src/utils.rs:59-73); codes are read as the previous
-    // assignment and overwritten; changed[s] becomes non-zero if any row of subspace s moved (76-80).
+    // assignment and overwritten; buf.moved[s] becomes non-zero if any row of subspace s moved (76-80).
     // Subspaces with active[s] == 0 are left untouched.
-    virtual void assign_train(const Shape &sh, const float *x, const float *centroids, void *codes,
-                              const uint32_t *active, uint32_t *changed) = 0;
-    // sums[s][j][:] = sum of the rows assigned to (s, j), counts[s][j] = how many (src/utils.rs:83-92,
-    // src/vector.rs:297-314).  ordered = ascending row order per cluster.
+    // With fuse_sums the device MAY also add every row to buf.sums / buf.counts of its new cluster in the same pass
+    // (order unspecified, like src/vector.rs:298-304); it returns true when it did, and the caller then skips accumulate.
+    virtual bool assign_train(const Shape &sh, const float *x, const float *centroids, void *codes,
+                              const uint32_t *active, const IterBuffers &buf, bool fuse_sums) = 0;
+    // buf.sums[s][j][:] += the rows assigned to (s, j), buf.counts[s][j] += how many (src/utils.rs:83-92,
+    // src/vector.rs:297-314); the buffer comes in zero-filled.  ordered = ascending row order per cluster.
     virtual void accumulate(const Shape &sh, const float *x, const void *codes, const uint32_t *active,
-                            bool ordered, float *sums, uint32_t *counts) = 0;
-    // centroids = sums / (counts as f32) where counts > 0 (src/vector.rs:315-316), active subspaces only.
-    virtual void finalize(const Shape &sh, const float *sums, const uint32_t *counts, const uint32_t *active,
-                          float *centroids) = 0;
+                            bool ordered, const IterBuffers &buf) = 0;
+    // centroids = sums / (counts as f32) where counts > 0 (src/vector.rs:315-316), active subspaces only; reports
+    // the iteration's flags to the host (complete on return) and clears the buffer for the next iteration.
+    virtual void update_centroids(const Shape &sh, const IterBuffers &buf, const uint32_t *active, float *centroids,
+                                  IterStatus &status) = 0;
     // Residual update of one RVQ stage (src/rvq.rs:111-138): argmin with `metric`, res -= centroid in place,
     // *norm_sum += sum over rows of sqrt(sum res^2) (f64, device scalar, not cleared here).
     virtual void rvq_update(float *res, size_t n, size_t dim, const float *centroids, size_t k, int metric,

@@ -4,6 +4,7 @@
 #include "cuda_device.hpp"
 
 #include <algorithm>
+#include <chrono>
 #include <cstring>
 #include <vector>
 
@@ -36,6 +37,7 @@ CudaDevice::CudaDevice(int device) : device_(device)
     smem_limit_ = prop.sharedMemPerBlockOptin;
     VQB_CUDA_CHECK(cudaStreamCreateWithFlags(&own_stream_, cudaStreamNonBlocking));
     stream_ = own_stream_;
+    ++device_allocs_;
     if (cudaHostAlloc(reinterpret_cast<void **>(&stage_), STAGE_BYTES, cudaHostAllocDefault) != cudaSuccess) {
         stage_ = nullptr; // pinned memory is an optimisation only
         cudaGetLastError();
@@ -49,6 +51,13 @@ CudaDevice::CudaDevice(int device) : device_(device)
         // CUDA-core filter kernel); VQB_PQ_TENSOR=0 selects the filter kernel (A/B comparisons).
         const char *f = std::getenv("VQB_PQ_TENSOR");
         pq_tensor_enabled_ = tensor_enabled_ && !(f && *f == '0');
+        const char *fu = std::getenv("VQB_PQ_FUSE_SUMS"); // 0: cluster sums in a separate pass over the rows (A/B comparisons)
+        pq_fuse_sums_ = !(fu && *fu == '0');
+        const char *bm = std::getenv("VQB_DENSE_BLOCK_MB"); // block size of the full-width k-means passes (default 48 MiB)
+        if (bm && *bm) {
+            const long v = std::atol(bm);
+            if (v > 0) dense_block_bytes_ = (size_t)v << 20;
+        }
     }
     cudaMemPool_t pool;
     if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
@@ -73,6 +82,13 @@ CudaDevice::~CudaDevice()
         cudaFree(cand_);
         cudaFree(tc_stats_);
         cudaFree(tc_error_);
+        cudaFree(status_counter_);
+        if (status_host_) cudaFreeHost(status_host_);
+        for (auto &sp : spans_) {
+            event_pool_.push_back(sp.a);
+            event_pool_.push_back(sp.b);
+        }
+        for (cudaEvent_t e : event_pool_) cudaEventDestroy(e);
         cudaStreamDestroy(own_stream_);
     }
 }
@@ -81,20 +97,32 @@ void CudaDevice::set_timing(bool on)
 {
     if (!on) {
         for (auto &sp : spans_) {
-            cudaEventDestroy(sp.a);
-            cudaEventDestroy(sp.b);
+            event_pool_.push_back(sp.a);
+            event_pool_.push_back(sp.b);
         }
         spans_.clear();
     }
     timing_ = on;
 }
 
+cudaEvent_t CudaDevice::take_event()
+{
+    if (!event_pool_.empty()) {
+        cudaEvent_t e = event_pool_.back();
+        event_pool_.pop_back();
+        return e;
+    }
+    cudaEvent_t e;
+    VQB_CUDA_CHECK(cudaEventCreate(&e));
+    return e;
+}
+
 void CudaDevice::timing_begin(const char *name)
 {
     Span sp;
     sp.name = name;
-    VQB_CUDA_CHECK(cudaEventCreate(&sp.a));
-    VQB_CUDA_CHECK(cudaEventCreate(&sp.b));
+    sp.a = take_event();
+    sp.b = take_event();
     VQB_CUDA_CHECK(cudaEventRecord(sp.a, stream_));
     spans_.push_back(sp);
 }
@@ -115,8 +143,8 @@ std::string CudaDevice::timing_report()
             e.first += 1;
             e.second += ms;
         }
-        cudaEventDestroy(sp.a);
-        cudaEventDestroy(sp.b);
+        event_pool_.push_back(sp.a);
+        event_pool_.push_back(sp.b);
     }
     spans_.clear();
     std::string out = "{";
@@ -137,7 +165,13 @@ cudaStream_t CudaDevice::aux_stream(int i)
 
 void CudaDevice::make_current() const { VQB_CUDA_CHECK(cudaSetDevice(device_)); }
 
-void CudaDevice::synchronize() { VQB_CUDA_CHECK(cudaStreamSynchronize(stream_)); }
+// A tensor-core kernel whose bounded wait expired stops early and leaves a code in the error word; callers that pass device
+// outputs never download anything, so this is where they learn of it.
+void CudaDevice::synchronize()
+{
+    if (tc_error_) check_tc_error();
+    else VQB_CUDA_CHECK(cudaStreamSynchronize(stream_));
+}
 
 bool CudaDevice::is_device_pointer(const void *p) const
 {
@@ -154,6 +188,7 @@ bool CudaDevice::is_device_pointer(const void *p) const
 void *CudaDevice::alloc(size_t bytes)
 {
     void *p = nullptr;
+    ++device_allocs_;
     VQB_CUDA_CHECK(cudaMallocAsync(&p, bytes ? bytes : 1, stream_));
     return p;
 }
@@ -205,6 +240,7 @@ void CudaDevice::download(void *dst, const void *src, size_t bytes)
 void CudaDevice::ensure_tc_buffers(size_t n)
 {
     if (!hn_scratch_) {
+        device_allocs_ += 4;
         VQB_CUDA_CHECK(cudaMalloc(&hn_scratch_, 260 * sizeof(float)));
         VQB_CUDA_CHECK(cudaMalloc(&pq_scratch_, pq_tc_scratch_floats() * sizeof(float)));
         VQB_CUDA_CHECK(cudaMemsetAsync(pq_scratch_, 0, pq_tc_scratch_floats() * sizeof(float), stream_));
@@ -220,6 +256,7 @@ void CudaDevice::ensure_tc_buffers(size_t n)
         rownorm_ = nullptr;
         cand_ = nullptr;
         rows_cap_ = 0;
+        device_allocs_ += 2;
         VQB_CUDA_CHECK(cudaMalloc(&rownorm_, n * sizeof(float)));
         VQB_CUDA_CHECK(cudaMalloc(&cand_, n * DENSE_MASK_WORDS * sizeof(uint32_t)));
         rows_cap_ = n;
@@ -234,6 +271,7 @@ uint8_t *CudaDevice::pq_mark_buffer(size_t bytes)
         pq_marks_ = nullptr;
         pq_marks_cap_ = 0;
         const size_t cap = bytes + bytes / 4;
+        ++device_allocs_;
         VQB_CUDA_CHECK(cudaMalloc(&pq_marks_, cap));
         pq_marks_cap_ = cap;
         VQB_CUDA_CHECK(cudaMemsetAsync(pq_marks_, 0, cap, stream_));
@@ -257,6 +295,7 @@ void CudaDevice::check_tc_error()
 void CudaDevice::prepare_rows(const Shape &sh, const float *x)
 {
     prepared_x_ = nullptr;
+    bop_fresh_ = nullptr;
     if (!tensor_enabled_ || sh.m != 1 || sh.ld != sh.sd || sh.n_local == 0) return;
     if (!dense_tc_applicable(sh.n_local, sh.sd, sh.k, M_SQ, x)) return;
     ensure_tc_buffers(sh.n_local);
@@ -293,9 +332,15 @@ void CudaDevice::pq_tensor_debug(const float *x, size_t n, size_t m, const float
     p.x_vec4 = 1;
     if (!pq_tc_applicable(p, M_SQ)) throw Error(103, "shape not covered by the product-quantizer tensor-core path");
     ensure_tc_buffers(0);
+    bop_fresh_ = nullptr;
     unsigned long long before = 0, after = 0;
     download(&before, pq_scratch_ + pq_tc_stats_offset_floats(), sizeof before);
-    launch_pq_tc(*this, p, M_SQ, false, 4, pq_scratch_, tc_error_, scores);
+    PqTcBuffers tb;
+    tb.scratch = pq_scratch_;
+    tb.marks = pq_mark_buffer(pq_tc_mark_bytes(n, m));
+    tb.error_word = tc_error_;
+    tb.dbg_scores = scores;
+    launch_pq_tc(*this, p, M_SQ, false, 4, tb);
     download(&after, pq_scratch_ + pq_tc_stats_offset_floats(), sizeof after);
     *marked = after - before;
 }
@@ -355,6 +400,7 @@ void CudaDevice::patch_centroids(const Shape &sh, const float *x, uint64_t row_b
                                  size_t n_patches, float *centroids, Comm *comm)
 {
     if (n_patches == 0) return;
+    bop_fresh_ = nullptr; // the centroids change behind the fused update's back
     RowPatch *pd = (RowPatch *)alloc(sizeof(RowPatch) * n_patches);
     uint32_t *stage = (uint32_t *)alloc(sizeof(uint32_t) * n_patches * sh.sd);
     upload(pd, patches, sizeof(RowPatch) * n_patches);
@@ -378,26 +424,41 @@ void CudaDevice::patch_centroids(const Shape &sh, const float *x, uint64_t row_b
 // ------------------------------------------------------------------------------------------------
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-void CudaDevice::assign_train(const Shape &sh, const float *x, const float *centroids, void *codes,
-                              const uint32_t *active, uint32_t *changed)
+bool CudaDevice::assign_train(const Shape &sh, const float *x, const float *centroids, void *codes, const uint32_t *active,
+                              const IterBuffers &buf, bool fuse_sums)
 {
-    if (sh.n_local == 0) return;
+    if (sh.n_local == 0) return false;
+    uint32_t *changed = buf.moved;
     if (prepared_x_ == x && prepared_n_ == sh.n_local && prepared_dim_ == sh.sd && sh.m == 1 &&
         dense_tc_applicable(sh.n_local, sh.sd, sh.k, M_SQ, x)) {
-        // full-width k-means step: tensor-core shortlist, then the exact decision among the candidates
-        dense_shortlist(*this, x, sh.n_local, sh.sd, centroids, sh.k, rownorm_, hn_scratch_, cand_, nullptr, tc_error_, nullptr);
-        ResolveParams r = {};
-        r.x = x;
-        r.n = sh.n_local;
-        r.dim = (int)sh.sd;
-        r.k = (int)sh.k;
-        r.codebook = centroids;
-        r.cand = cand_;
-        r.euclid = 0;
-        r.codes = codes;
-        r.changed = changed;
-        launch_resolve(*this, r, R_TRAIN, code_bytes(sh.k));
-        return;
+        // full-width k-means step: tensor-core shortlist, then the exact decision among the candidates.  The rows are walked
+        // in blocks that fit the L2 cache, so the second kernel (and, with fuse_sums, the third) finds its rows there.
+        size_t block_rows = std::max<size_t>(1024, dense_block_bytes_ / (sh.sd * sizeof(float)));
+        const size_t wave = (size_t)sm_count_ * 128; // one 128-row tile per persistent CTA
+        if (block_rows >= wave) block_rows -= block_rows % wave;
+        const size_t cb = code_bytes(sh.k);
+        for (size_t r0 = 0; r0 < sh.n_local; r0 += block_rows) {
+            const size_t rows = std::min(block_rows, sh.n_local - r0);
+            const float *xb = x + r0 * sh.sd;
+            dense_shortlist(*this, xb, rows, sh.sd, centroids, sh.k, rownorm_ + r0, hn_scratch_, cand_, nullptr, tc_error_, nullptr);
+            ResolveParams r = {};
+            r.x = xb;
+            r.n = rows;
+            r.dim = (int)sh.sd;
+            r.k = (int)sh.k;
+            r.codebook = centroids;
+            r.cand = cand_;
+            r.euclid = 0;
+            r.codes = static_cast<uint8_t *>(codes) + r0 * cb;
+            r.changed = changed;
+            launch_resolve(*this, r, R_TRAIN, cb);
+            if (fuse_sums) {
+                Shape blk = sh;
+                blk.n_local = rows;
+                accumulate(blk, xb, static_cast<uint8_t *>(codes) + r0 * cb, active, false, buf);
+            }
+        }
+        return fuse_sums;
     }
     AssignParams p = {};
     p.x = x;
@@ -413,10 +474,22 @@ void CudaDevice::assign_train(const Shape &sh, const float *x, const float *cent
     p.x_vec4 = aligned16(x) && (sh.ld % 4 == 0) && (sh.sd % 4 == 0);
     if (pq_tensor_enabled_ && pq_tc_applicable(p, M_SQ)) {
         ensure_tc_buffers(0);
-        launch_pq_tc(*this, p, M_SQ, true, code_bytes(sh.k), pq_scratch_, tc_error_);
-        return;
+        PqTcBuffers tb;
+        tb.scratch = pq_scratch_;
+        tb.marks = pq_mark_buffer(pq_tc_mark_bytes(sh.n_local, sh.m));
+        tb.error_word = tc_error_;
+        tb.prepare_operand = (bop_fresh_ != centroids);
+        const bool fuse = fuse_sums && pq_fuse_sums_;
+        if (fuse) {
+            tb.sums = buf.sums;
+            tb.counts = buf.counts;
+            tb.counts_f32 = buf.counts_f32;
+        }
+        launch_pq_tc(*this, p, M_SQ, true, code_bytes(sh.k), tb);
+        bop_fresh_ = nullptr;
+        return fuse;
     }
-    if (launch_assign_reg(*this, p, M_SQ, true, code_bytes(sh.k))) return;
+    if (launch_assign_reg(*this, p, M_SQ, true, code_bytes(sh.k))) return false;
     GenericParams g = {};
     g.x = x;
     g.n = sh.n_local;
@@ -429,10 +502,11 @@ void CudaDevice::assign_train(const Shape &sh, const float *x, const float *cent
     g.active = active;
     g.changed = changed;
     launch_assign_generic(*this, g, M_SQ, G_TRAIN, code_bytes(sh.k));
+    return false;
 }
 
-void CudaDevice::pq_encode(const Shape &sh, const float *x, const float *codebooks, int metric, double pm,
-                           uint16_t *out_f16, uint32_t *out_codes, float *out_f32)
+void CudaDevice::pq_encode_impl(const Shape &sh, const float *x, const float *codebooks, int metric, double pm,
+                                uint16_t *out_f16, uint32_t *out_codes, float *out_f32, bool cuda_cores_only)
 {
     if (sh.n_local == 0) return;
     const size_t dim = sh.m * sh.sd;
@@ -450,9 +524,14 @@ void CudaDevice::pq_encode(const Shape &sh, const float *x, const float *codeboo
     p.pv = (float)pm;
     p.x_vec4 = aligned16(x) && (sh.ld % 4 == 0) && (sh.sd % 4 == 0);
     p.out_vec = (!out_f16 || (aligned16(out_f16) && dim % 8 == 0)) && (!out_f32 || (aligned16(out_f32) && dim % 4 == 0));
-    if (pq_tensor_enabled_ && pq_tc_applicable(p, metric)) {
+    if (!cuda_cores_only && pq_tensor_enabled_ && pq_tc_applicable(p, metric)) {
         ensure_tc_buffers(0);
-        launch_pq_tc(*this, p, metric, false, 4, pq_scratch_, tc_error_);
+        bop_fresh_ = nullptr;
+        PqTcBuffers tb;
+        tb.scratch = pq_scratch_;
+        tb.marks = pq_mark_buffer(pq_tc_mark_bytes(sh.n_local, sh.m));
+        tb.error_word = tc_error_;
+        launch_pq_tc(*this, p, metric, false, 4, tb);
         return;
     }
     if (launch_assign_reg(*this, p, metric, false, 4)) return;
@@ -469,6 +548,18 @@ void CudaDevice::pq_encode(const Shape &sh, const float *x, const float *codeboo
     g.out_f32 = out_f32;
     g.pv = (float)pm;
     launch_assign_generic(*this, g, metric, G_ENCODE, 4);
+}
+
+void CudaDevice::pq_encode(const Shape &sh, const float *x, const float *codebooks, int metric, double pm, uint16_t *out_f16,
+                           uint32_t *out_codes, float *out_f32)
+{
+    pq_encode_impl(sh, x, codebooks, metric, pm, out_f16, out_codes, out_f32, false);
+}
+
+void CudaDevice::pq_encode_no_scratch(const Shape &sh, const float *x, const float *codebooks, int metric, double pm, uint16_t *out_f16,
+                                      uint32_t *out_codes)
+{
+    pq_encode_impl(sh, x, codebooks, metric, pm, out_f16, out_codes, nullptr, true);
 }
 
 void CudaDevice::rvq_update(float *res, size_t n, size_t dim, const float *centroids, size_t k, int metric, double pm,
@@ -585,9 +676,16 @@ void CudaDevice::rvq_quantize(const float *x, size_t n, size_t dim, const float 
 // ------------------------------------------------------------------------------------------------
 // FAST, narrow subspaces: one thread per (row, subspace); shared-memory sums laid out [s][d][code] so
 // that the 32 lanes of a warp (different rows, arbitrary codes) spread over the banks.
+// counts hold u32 values, or f32 values when counts_f32 is set (IterBuffers)
+__device__ __forceinline__ void add_count(uint32_t *counts, size_t at, uint32_t c, int counts_f32)
+{
+    if (counts_f32) atomicAdd(reinterpret_cast<float *>(counts) + at, (float)c);
+    else atomicAdd(counts + at, c);
+}
+
 template <typename CodeT>
 __global__ void accum_small_kernel(const float *x, unsigned long long n, unsigned long long ld, int m, int k, int sd,
-                                   int group, const CodeT *codes, const uint32_t *active, float *sums, uint32_t *counts)
+                                   int group, const CodeT *codes, const uint32_t *active, float *sums, uint32_t *counts, int counts_f32)
 {
     const bool vec4 = (sd % 4 == 0) && (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
     extern __shared__ __align__(16) float smem[];
@@ -628,14 +726,14 @@ __global__ void accum_small_kernel(const float *x, unsigned long long n, unsigne
         if (scnt[sl * k + j] != 0u) atomicAdd(sums + ((size_t)(g0 + sl) * k + j) * sd + d, ssum[((size_t)sl * sd + d) * k + j]);
     }
     for (int t = threadIdx.x; t < gcount * k; t += blockDim.x)
-        if (scnt[t] != 0u) atomicAdd(counts + (size_t)g0 * k + t, scnt[t]);
+        if (scnt[t] != 0u) add_count(counts, (size_t)g0 * k + t, scnt[t], counts_f32);
 }
 
 // FAST, wide rows: one warp per (row, subspace), lanes over dimensions; sums laid out [code][d].
 // With shared == false the atomics go straight to global memory (codebook too large for shared memory).
 template <typename CodeT, bool SHARED>
 __global__ void accum_wide_kernel(const float *x, unsigned long long n, unsigned long long ld, int m, int k, int sd,
-                                  const CodeT *codes, const uint32_t *active, float *sums, uint32_t *counts)
+                                  const CodeT *codes, const uint32_t *active, float *sums, uint32_t *counts, int counts_f32)
 {
     extern __shared__ __align__(16) float smem[];
     const int s = blockIdx.y;
@@ -679,14 +777,17 @@ __global__ void accum_wide_kernel(const float *x, unsigned long long n, unsigned
         }
 #pragma unroll
         for (int r = 0; r < RB; ++r)
-            if (lane == 0 && code[r] >= 0) atomicAdd((SHARED ? scnt : gcnt) + code[r], 1u);
+            if (lane == 0 && code[r] >= 0) {
+                if (SHARED) atomicAdd(scnt + code[r], 1u);
+                else add_count(gcnt, (size_t)code[r], 1u, counts_f32);
+            }
     }
     if (SHARED) {
         __syncthreads();
         for (int t = threadIdx.x; t < k * sd; t += blockDim.x)
             if (scnt[t / sd] != 0u) atomicAdd(gsum + t, ssum[t]);
         for (int t = threadIdx.x; t < k; t += blockDim.x)
-            if (scnt[t] != 0u) atomicAdd(gcnt + t, scnt[t]);
+            if (scnt[t] != 0u) add_count(gcnt, (size_t)t, scnt[t], counts_f32);
     }
 }
 
@@ -695,7 +796,7 @@ __global__ void accum_wide_kernel(const float *x, unsigned long long n, unsigned
 template <typename CodeT>
 __global__ void __launch_bounds__(256) accum_ordered_kernel(const float *x, unsigned long long n, unsigned long long ld, int m,
                                                             int k, int sd, const CodeT *codes, const uint32_t *active,
-                                                            float *sums, uint32_t *counts)
+                                                            float *sums, uint32_t *counts, int counts_f32)
 {
     __shared__ CodeT sc[2048];
     const int s = blockIdx.y;
@@ -725,14 +826,14 @@ __global__ void __launch_bounds__(256) accum_ordered_kernel(const float *x, unsi
         }
         if (mine) {
             sums[((size_t)s * k + j) * sd + d] = acc;
-            if (d == 0) counts[(size_t)s * k + j] = cnt;
+            if (d == 0) counts[(size_t)s * k + j] = counts_f32 ? __float_as_uint((float)cnt) : cnt;
         }
     }
 }
 
 template <typename CodeT>
 static void accumulate_t(CudaDevice &dev, const Shape &sh, const float *x, const CodeT *codes, const uint32_t *active,
-                         bool ordered, float *sums, uint32_t *counts)
+                         bool ordered, float *sums, uint32_t *counts, int counts_f32)
 {
     const int m = (int)sh.m, k = (int)sh.k, sd = (int)sh.sd;
     cudaStream_t st = dev.stream();
@@ -740,7 +841,7 @@ static void accumulate_t(CudaDevice &dev, const Shape &sh, const float *x, const
         const int sdc = std::min(sd, 256), cpb = std::max(1, 256 / sdc);
         dim3 grid((k + cpb - 1) / cpb, m);
         KernelScope ks(dev, "accumulate_ordered");
-        accum_ordered_kernel<CodeT><<<grid, 256, 0, st>>>(x, sh.n_local, sh.ld, m, k, sd, codes, active, sums, counts);
+        accum_ordered_kernel<CodeT><<<grid, 256, 0, st>>>(x, sh.n_local, sh.ld, m, k, sd, codes, active, sums, counts, counts_f32);
         VQB_CUDA_CHECK(cudaGetLastError());
         dev.count_launch();
         return;
@@ -764,7 +865,7 @@ static void accumulate_t(CudaDevice &dev, const Shape &sh, const float *x, const
                                                              std::max<unsigned long long>(1, (unsigned long long)dev.sm_count() * ctas_per_sm / ny));
         dim3 grid(std::max(1u, gx), (m + group - 1) / group);
         KernelScope ks(dev, "accumulate_fast");
-        kernel<<<grid, threads, smem, st>>>(x, sh.n_local, sh.ld, m, k, sd, group, codes, active, sums, counts);
+        kernel<<<grid, threads, smem, st>>>(x, sh.n_local, sh.ld, m, k, sd, group, codes, active, sums, counts, counts_f32);
         VQB_CUDA_CHECK(cudaGetLastError());
         dev.count_launch();
         return;
@@ -776,51 +877,175 @@ static void accumulate_t(CudaDevice &dev, const Shape &sh, const float *x, const
         VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)per_sub));
         unsigned gx = (unsigned)std::min<unsigned long long>((sh.n_local + 15) / 16, (unsigned long long)std::max(1, dev.sm_count() / m));
         dim3 grid(std::max(1u, gx), m);
-        kernel<<<grid, threads, per_sub, st>>>(x, sh.n_local, sh.ld, m, k, sd, codes, active, sums, counts);
+        kernel<<<grid, threads, per_sub, st>>>(x, sh.n_local, sh.ld, m, k, sd, codes, active, sums, counts, counts_f32);
     } else {
         unsigned gx = (unsigned)std::min<unsigned long long>((sh.n_local + 15) / 16, (unsigned long long)dev.sm_count() * 4);
         dim3 grid(std::max(1u, gx), m);
-        accum_wide_kernel<CodeT, false><<<grid, threads, 0, st>>>(x, sh.n_local, sh.ld, m, k, sd, codes, active, sums, counts);
+        accum_wide_kernel<CodeT, false><<<grid, threads, 0, st>>>(x, sh.n_local, sh.ld, m, k, sd, codes, active, sums, counts, counts_f32);
     }
     VQB_CUDA_CHECK(cudaGetLastError());
     dev.count_launch();
 }
 
 void CudaDevice::accumulate(const Shape &sh, const float *x, const void *codes, const uint32_t *active, bool ordered,
-                            float *sums, uint32_t *counts)
+                            const IterBuffers &buf)
 {
-    zero(sums, sizeof(float) * sh.m * sh.k * sh.sd);
-    zero(counts, sizeof(uint32_t) * sh.m * sh.k);
+    // the buffer arrives zero-filled (update_centroids clears what it has read); the ordered kernel overwrites every entry
     const size_t cb = code_bytes(sh.k);
-    if (cb == 1) accumulate_t<uint8_t>(*this, sh, x, (const uint8_t *)codes, active, ordered, sums, counts);
-    else if (cb == 2) accumulate_t<uint16_t>(*this, sh, x, (const uint16_t *)codes, active, ordered, sums, counts);
-    else accumulate_t<uint32_t>(*this, sh, x, (const uint32_t *)codes, active, ordered, sums, counts);
+    const int cf = buf.counts_f32 ? 1 : 0;
+    if (cb == 1) accumulate_t<uint8_t>(*this, sh, x, (const uint8_t *)codes, active, ordered, buf.sums, buf.counts, cf);
+    else if (cb == 2) accumulate_t<uint16_t>(*this, sh, x, (const uint16_t *)codes, active, ordered, buf.sums, buf.counts, cf);
+    else accumulate_t<uint32_t>(*this, sh, x, (const uint32_t *)codes, active, ordered, buf.sums, buf.counts, cf);
 }
 
-// centroid = sum / (count as f32), IEEE division (src/vector.rs:315-316); empty clusters keep their old
-// value until the host patches them (src/utils.rs:99-101).
-__global__ void finalize_kernel(const float *sums, const uint32_t *counts, const uint32_t *active, int k, int sd,
-                                unsigned long long total, float *centroids)
+// ------------------------------------------------------------------------------------------------
+// centroid update (src/utils.rs:95-106): centroid = sum / (count as f32), IEEE division (src/vector.rs:315-316); empty
+// clusters keep their old value until the host patches them (src/utils.rs:99-101).  The same launch reports the iteration's
+// flags to the host through the status page and clears sums, counts and flags for the next iteration.
+// One CTA of 8 warps per (sub-space, 32 clusters): a warp takes four clusters, its lanes the dimensions.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) update_centroids_kernel(float *sums, uint32_t *counts, uint32_t *moved, int counts_f32, const uint32_t *active,
+                                                               int k, int sd, float *centroids, StatusPage sp)
 {
-    for (unsigned long long t = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; t < total;
-         t += (unsigned long long)gridDim.x * blockDim.x) {
-        const unsigned long long cj = t / sd;
-        const int s = (int)(cj / k);
-        if (active && active[s] == 0) continue;
-        const uint32_t c = counts[cj];
-        if (c != 0u) centroids[t] = __fdiv_rn(sums[t], __uint2float_rn(c));
+    __shared__ uint32_t s_bits;
+    const int s = blockIdx.x, word = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool act = !active || active[s] != 0;
+    if (threadIdx.x == 0) s_bits = 0u;
+    __syncthreads();
+    if (act) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int j = word * 32 + warp * 4 + q;
+            if (j >= k) break;
+            const size_t cj = (size_t)s * k + j;
+            const uint32_t cw = counts[cj];
+            const float cf = counts_f32 ? __uint_as_float(cw) : __uint2float_rn(cw);
+            if (cf != 0.0f) {
+                for (int d = lane; d < sd; d += 32) {
+                    centroids[cj * sd + d] = __fdiv_rn(sums[cj * sd + d], cf);
+                    sums[cj * sd + d] = 0.0f;
+                }
+            } else if (lane == 0) {
+                atomicOr(&s_bits, 1u << (warp * 4 + q));
+            }
+            __syncwarp();
+            if (lane == 0) counts[cj] = 0u;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        sp.host_bitmap()[(size_t)s * sp.words_per_subspace + word] = s_bits;
+        if (word == 0) {
+            sp.host_moved()[s] = act ? moved[s] : 0u;
+            moved[s] = 0u;
+        }
+    }
+    status_publish(sp);
+}
+
+StatusPage CudaDevice::status_page(size_t m, size_t k, uint32_t blocks)
+{
+    const size_t need = StatusPage::words(m, k);
+    if (need > status_cap_words_) {
+        VQB_CUDA_CHECK(cudaStreamSynchronize(stream_));
+        if (status_host_) cudaFreeHost(status_host_);
+        status_host_ = nullptr;
+        status_cap_words_ = 0;
+        const size_t cap = std::max<size_t>(need + need / 2, 4096);
+        ++device_allocs_;
+        VQB_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void **>(&status_host_), cap * sizeof(uint32_t), cudaHostAllocMapped));
+        VQB_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void **>(&status_dev_), status_host_, 0));
+        std::memset(status_host_, 0, cap * sizeof(uint32_t));
+        status_cap_words_ = cap;
+        status_seq_ = 0;
+    }
+    if (!status_counter_) {
+        ++device_allocs_;
+        VQB_CUDA_CHECK(cudaMalloc(&status_counter_, sizeof(unsigned int)));
+        VQB_CUDA_CHECK(cudaMemsetAsync(status_counter_, 0, sizeof(unsigned int), stream_));
+    }
+    StatusPage sp;
+    sp.host_words = status_dev_;
+    sp.done_counter = status_counter_;
+    sp.tc_error = tc_error_;
+    sp.seq = ++status_seq_;
+    if (sp.seq == 0) sp.seq = ++status_seq_; // zero is the page's initial value
+    sp.total_blocks = blocks;
+    sp.m = (uint32_t)m;
+    sp.words_per_subspace = (uint32_t)((k + 31) / 32);
+    return sp;
+}
+
+// The host polls the page's sequence word (a read of its own memory) instead of queueing a copy and waiting on an event.
+void CudaDevice::wait_status(const StatusPage &sp, size_t m, size_t k, IterStatus &out)
+{
+    volatile uint32_t *page = status_host_;
+    const auto t0 = std::chrono::steady_clock::now();
+    for (uint64_t spin = 1;; ++spin) {
+        if (page[0] == sp.seq) break;
+        if ((spin & 0xFFFFu) == 0) {
+            const cudaError_t q = cudaStreamQuery(stream_);
+            if (q != cudaSuccess && q != cudaErrorNotReady) VQB_CUDA_CHECK(q);
+            if (q == cudaSuccess && page[0] != sp.seq) {
+                // the stream has drained: the write to the page must have landed by now
+                if (page[0] == sp.seq) break;
+                throw Error(100, "centroid update finished without reporting its status");
+            }
+            if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(120))
+                throw Error(100, "timed out waiting for the centroid update's status");
+        }
+    }
+    std::atomic_thread_fence(std::memory_order_acquire);
+    const size_t wps = (k + 31) / 32;
+    out.moved.assign(m, 0);
+    out.has_empty.assign(m, 0);
+    out.empty_bits.assign(m * wps, 0u);
+    const uint32_t *mv = status_host_ + 4, *bm = status_host_ + 4 + m;
+    for (size_t s = 0; s < m; ++s) {
+        out.moved[s] = mv[s] != 0u;
+        for (size_t w = 0; w < wps; ++w) {
+            out.empty_bits[s * wps + w] = bm[s * wps + w];
+            if (bm[s * wps + w]) out.has_empty[s] = 1;
+        }
+    }
+    const int code = (int)status_host_[1];
+    if (code != 0) {
+        cudaMemsetAsync(tc_error_, 0, sizeof(int), stream_);
+        throw Error(100, "tensor-core kernel gave up waiting (stage " + std::to_string(code) + "); set VQB_NO_TENSOR=1 to use the CUDA-core path");
     }
 }
 
-void CudaDevice::finalize(const Shape &sh, const float *sums, const uint32_t *counts, const uint32_t *active,
-                          float *centroids)
+void CudaDevice::update_centroids(const Shape &sh, const IterBuffers &buf, const uint32_t *active, float *centroids, IterStatus &status)
 {
-    const size_t total = sh.m * sh.k * sh.sd;
-    if (!total) return;
-    KernelScope ks(*this, "finalize");
-    finalize_kernel<<<blocks_for(total, 256, 2048), 256, 0, stream_>>>(sums, counts, active, (int)sh.k, (int)sh.sd, total, centroids);
-    VQB_CUDA_CHECK(cudaGetLastError());
-    count_launch();
+    const size_t m = sh.m, k = sh.k;
+    if (m * k * sh.sd == 0) {
+        status.moved.assign(m, 0);
+        status.has_empty.assign(m, 0);
+        status.empty_bits.clear();
+        return;
+    }
+    // shapes of the product-quantizer tensor kernel: the same launch writes the operand of the next assignment pass
+    const bool pq8 = pq_tensor_enabled_ && sh.sd == 8 && sh.m >= 4 && sh.m <= 64 && sh.m % 4 == 0 && k >= 2 && k <= 256 && pq_scratch_ != nullptr &&
+                     (reinterpret_cast<uintptr_t>(centroids) & 15u) == 0 && (reinterpret_cast<uintptr_t>(buf.sums) & 15u) == 0;
+    if (pq8) {
+        const StatusPage sp = status_page(m, k, (uint32_t)m);
+        launch_pq_update_centroids(*this, (int)m, (int)k, buf.sums, buf.counts, buf.moved, buf.counts_f32, active, centroids, pq_scratch_, sp);
+        bop_fresh_ = centroids;
+        wait_status(sp, m, k, status);
+        return;
+    }
+    const unsigned wps = (unsigned)((k + 31) / 32);
+    if (wps > 65535u) throw Error(103, "more than 2,097,120 clusters per sub-space are not supported");
+    const StatusPage sp = status_page(m, k, (uint32_t)(m * wps));
+    {
+        KernelScope ks(*this, "update_centroids");
+        update_centroids_kernel<<<dim3((unsigned)m, wps), 256, 0, stream_>>>(buf.sums, buf.counts, buf.moved, buf.counts_f32 ? 1 : 0, active, (int)k,
+                                                                            (int)sh.sd, centroids, sp);
+        VQB_CUDA_CHECK(cudaGetLastError());
+        count_launch();
+    }
+    wait_status(sp, m, k, status);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "backend.hpp"
+#include "iter_status.cuh"
 
 namespace vqb {
 
@@ -38,16 +39,20 @@ class CudaDevice : public Device {
     uint8_t *pq_mark_buffer(size_t bytes);
     void patch_centroids(const Shape &sh, const float *x, uint64_t row_begin, const RowPatch *patches, size_t n_patches,
                          float *centroids, Comm *comm) override;
-    void assign_train(const Shape &sh, const float *x, const float *centroids, void *codes, const uint32_t *active,
-                      uint32_t *changed) override;
+    bool assign_train(const Shape &sh, const float *x, const float *centroids, void *codes, const uint32_t *active,
+                      const IterBuffers &buf, bool fuse_sums) override;
     void accumulate(const Shape &sh, const float *x, const void *codes, const uint32_t *active, bool ordered,
-                    float *sums, uint32_t *counts) override;
-    void finalize(const Shape &sh, const float *sums, const uint32_t *counts, const uint32_t *active,
-                  float *centroids) override;
+                    const IterBuffers &buf) override;
+    void update_centroids(const Shape &sh, const IterBuffers &buf, const uint32_t *active, float *centroids,
+                          IterStatus &status) override;
     void rvq_update(float *res, size_t n, size_t dim, const float *centroids, size_t k, int metric, double p,
                     double *norm_sum) override;
     void pq_encode(const Shape &sh, const float *x, const float *codebooks, int metric, double p, uint16_t *out_f16,
                    uint32_t *out_codes, float *out_f32) override;
+    // The same encode on the CUDA-core kernels only: they work out of shared memory and registers and need no device
+    // memory besides inputs and outputs.  Results are identical to pq_encode.
+    void pq_encode_no_scratch(const Shape &sh, const float *x, const float *codebooks, int metric, double p, uint16_t *out_f16,
+                              uint32_t *out_codes);
     void rotate_rows(const float *rot, size_t dim, const float *x, size_t n, float *y) override;
     void cross_cov(const float *y, const float *x, size_t n, size_t dim, double *a) override;
 
@@ -75,6 +80,8 @@ class CudaDevice : public Device {
     size_t smem_limit() const { return smem_limit_; }
     uint64_t launches() const { return launches_.load(); }
     void count_launch(uint64_t n = 1) { launches_ += n; }
+    // How often this context has asked CUDA for device or pinned memory (cudaMalloc, cudaMallocAsync, cudaHostAlloc).
+    uint64_t device_allocs() const { return device_allocs_.load(); }
     void make_current() const;
     // Optional per-kernel timing with CUDA events on the launching stream (off by default).
     void set_timing(bool on);
@@ -96,7 +103,16 @@ class CudaDevice : public Device {
     static constexpr size_t STAGE_BYTES = 1u << 20; // pinned staging for small downloads
     unsigned char *stage_ = nullptr;
     cudaEvent_t stage_event_ = nullptr;
-    std::atomic<uint64_t> launches_{0};
+    std::atomic<uint64_t> launches_{0}, device_allocs_{0};
+    // page of mapped pinned memory the centroid-update kernels report to (iter_status.cuh)
+    uint32_t *status_host_ = nullptr, *status_dev_ = nullptr;
+    size_t status_cap_words_ = 0;
+    unsigned int *status_counter_ = nullptr;
+    uint32_t status_seq_ = 0;
+    StatusPage status_page(size_t m, size_t k, uint32_t blocks);
+    void wait_status(const StatusPage &sp, size_t m, size_t k, IterStatus &out);
+    // centroids whose operand B (pq_tc.cu) the scratch currently holds, written by the fused centroid update
+    const float *bop_fresh_ = nullptr;
     // tensor-core path state (dense_tc.cu): row norms of the rows announced by prepare_rows, shortlist scratch
     bool tensor_enabled_ = true;
     const float *prepared_x_ = nullptr;
@@ -110,6 +126,12 @@ class CudaDevice : public Device {
     unsigned long long *tc_stats_ = nullptr;
     int *tc_error_ = nullptr;
     void ensure_tc_buffers(size_t n);
+    void pq_encode_impl(const Shape &sh, const float *x, const float *codebooks, int metric, double p, uint16_t *out_f16,
+                        uint32_t *out_codes, float *out_f32, bool cuda_cores_only);
+    // VQB_PQ_FUSE_SUMS=0: the product-quantizer tensor kernel leaves the cluster sums to the separate pass (A/B comparisons)
+    bool pq_fuse_sums_ = true;
+    // rows of a full-width k-means pass are walked in blocks of this many bytes (VQB_DENSE_BLOCK_MB), small enough for L2
+    size_t dense_block_bytes_ = (size_t)48 << 20;
     void check_tc_error();
     bool timing_ = false;
     struct Span {
@@ -117,6 +139,8 @@ class CudaDevice : public Device {
         cudaEvent_t a, b;
     };
     std::vector<Span> spans_;
+    std::vector<cudaEvent_t> event_pool_; // timing events are created once and re-used
+    cudaEvent_t take_event();
 };
 
 // Brackets one kernel launch for the optional timing record.

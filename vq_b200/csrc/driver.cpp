@@ -49,6 +49,26 @@ void global_rows(Device &dev, Comm *comm, size_t n_local, uint64_t *n_global, ui
     *n_global = total;
 }
 
+// Closes an NCCL group when the scope is left, also by an exception.
+struct GroupGuard {
+    Comm *c;
+    bool open = true;
+    explicit GroupGuard(Comm *comm) : c(comm) { c->group_begin(); }
+    void close() // the normal path: errors of the group's collectives surface here
+    {
+        open = false;
+        c->group_end();
+    }
+    ~GroupGuard()
+    {
+        if (!open) return;
+        try {
+            c->group_end();
+        } catch (...) {
+        }
+    }
+};
+
 bool use_ordered(int flags, uint64_t n_global)
 {
     if (flags == VQB_ACCUM_ORDERED) return true;
@@ -68,6 +88,7 @@ void lbg_fit(Device &dev, Comm *comm, const Shape &sh, const float *x, size_t ma
         throw Error(VQB_ERR_INVALID_PARAMETER, "Invalid parameter: k must be greater than 0");
     if (n_global < k) // src/utils.rs:45-50
         throw Error(VQB_ERR_INVALID_PARAMETER, "Invalid parameter: Not enough data points for k clusters");
+    if (n_global >= (1ull << 32)) throw Error(VQB_ERR_UNSUPPORTED, "2^32 or more rows: cluster counts are 32-bit");
     if (!init_idx) throw Error(VQB_ERR_BAD_ARGUMENT, "init_idx is NULL");
     const bool multi = comm && comm->world() > 1;
     const bool ordered = use_ordered(flags, n_global);
@@ -90,13 +111,23 @@ void lbg_fit(Device &dev, Comm *comm, const Shape &sh, const float *x, size_t ma
     const size_t cb = dev.code_bytes(k);
     DevBuf codes(dev, sh.n_local * m * cb);
     dev.zero(codes.p, sh.n_local * m * cb); // src/utils.rs:55: previous assignments start at 0
-    DevBuf sums(dev, sizeof(float) * m * k * sd);
-    DevBuf cc(dev, sizeof(uint32_t) * (m * k + m)); // counts[m][k] then changed[m]
+    // sums | counts | moved flags of one iteration, one allocation, cleared here once and then by every centroid update
+    IterBuffers buf;
+    const size_t words = buf.words(sh);
+    DevBuf iter(dev, sizeof(float) * words);
+    dev.zero(iter.p, sizeof(float) * words);
+    buf.sums = iter.as<float>();
+    buf.counts = reinterpret_cast<uint32_t *>(buf.sums + m * k * sd);
+    buf.moved = buf.counts + m * k;
+    // below 2^24 rows every count is exact in f32, and sums, counts and flags then cross the ranks as ONE f32 all-reduce
+    buf.counts_f32 = multi && n_global < (1ull << 24);
+    if (multi && !buf.counts_f32 && comm->world() > 256)
+        throw Error(VQB_ERR_UNSUPPORTED, "more than 256 ranks with 2^24 or more rows are not supported");
     DevBuf act(dev, sizeof(uint32_t) * m);
-    uint32_t *counts_d = cc.as<uint32_t>();
-    uint32_t *changed_d = counts_d + m * k;
-    std::vector<uint32_t> active(m, 1), cc_h(m * k + m);
+    std::vector<uint32_t> active(m, 1);
     bool active_dirty = true;
+    IterStatus status;
+    const size_t wps = (k + 31) / 32;
 
     for (size_t it = 0; it < max_iters; ++it) {
         bool any = false;
@@ -106,23 +137,26 @@ void lbg_fit(Device &dev, Comm *comm, const Shape &sh, const float *x, size_t ma
             dev.upload(act.p, active.data(), sizeof(uint32_t) * m);
             active_dirty = false;
         }
-        dev.zero(changed_d, sizeof(uint32_t) * m);
-        dev.assign_train(sh, x, centroids, codes.p, act.as<uint32_t>(), changed_d);               // 59-80
-        dev.accumulate(sh, x, codes.p, act.as<uint32_t>(), ordered, sums.as<float>(), counts_d); // 83-92
-        if (multi) { // the only exchange of an iteration: ~144 KiB, fused into one launch where the backend can
-            comm->group_begin();
-            comm->allreduce_sum_f32(sums.as<float>(), m * k * sd);
-            comm->allreduce_sum_u32(counts_d, m * k + m);
-            comm->group_end();
+        const bool summed = dev.assign_train(sh, x, centroids, codes.p, act.as<uint32_t>(), buf, !ordered); // 59-80 (+ 83-92)
+        if (!summed) dev.accumulate(sh, x, codes.p, act.as<uint32_t>(), ordered, buf);                      // 83-92
+        if (multi) { // the only exchange of an iteration, ~144 KiB
+            if (buf.counts_f32) {
+                comm->allreduce_sum_f32(buf.sums, words);
+            } else {
+                GroupGuard gg(comm);
+                comm->allreduce_sum_f32(buf.sums, m * k * sd);
+                comm->allreduce_sum_u32(buf.counts, m * k + m);
+                gg.close();
+            }
         }
-        dev.finalize(sh, sums.as<float>(), counts_d, act.as<uint32_t>(), centroids); // 95-99
-        dev.download(cc_h.data(), cc.p, sizeof(uint32_t) * (m * k + m));
+        dev.update_centroids(sh, buf, act.as<uint32_t>(), centroids, status); // 95-99; flags on the host when it returns
         patches.clear();
         for (size_t s = 0; s < m; ++s) {
             if (!active[s]) continue;
             if (iterations) iterations[s] += 1;
+            if (!status.has_empty[s]) continue;
             for (size_t j = 0; j < k; ++j) // ascending j, one draw per empty cluster (95-101)
-                if (cc_h[s * k + j] == 0) {
+                if (status.empty_bits[s * wps + j / 32] >> (j % 32) & 1u) {
                     if (!draw) throw Error(VQB_ERR_CALLBACK, "an empty cluster needs a draw callback");
                     uint64_t r = draw(user, stream0 + s, n_global);
                     if (r >= n_global) throw Error(VQB_ERR_CALLBACK, "draw callback returned a row index out of range");
@@ -132,7 +166,7 @@ void lbg_fit(Device &dev, Comm *comm, const Shape &sh, const float *x, size_t ma
         if (!patches.empty())
             dev.patch_centroids(sh, x, row_begin, patches.data(), patches.size(), centroids, comm);
         for (size_t s = 0; s < m; ++s)
-            if (active[s] && cc_h[m * k + s] == 0) { // 104-106: stop after the update
+            if (active[s] && !status.moved[s]) { // 104-106: stop after the update
                 active[s] = 0;
                 active_dirty = true;
             }

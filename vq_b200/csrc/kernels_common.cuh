@@ -13,6 +13,9 @@ namespace vqb {
 enum : int { M_SQ = 0, M_EUCLID = 1, M_COSINE = 2, M_MANHATTAN = 3, M_CHEBYSHEV = 4, M_MINKOWSKI = 5, M_HAMMING = 6 };
 
 #define VQB_INF __int_as_float(0x7f800000)
+// What the assignment kernels OR into a sub-space's "some row moved" word: the bits of 1.0f, so that the word is non-zero
+// as an integer and, when the words of several ranks are added up as f32 in one all-reduce with the cluster sums, as a float.
+#define VQB_MOVED_BITS 0x3F800000u
 
 // ---- running state of one distance evaluation, advanced one dimension at a time ----------------
 // `b` carries the centroid's sum of squares for the cosine metric (src/distances.rs:141-144).

@@ -5,7 +5,10 @@
 // implicit synchronisation of cudaMalloc/cudaFree are not acceptable.  vqb_opq_quantize needs one piece of scratch
 // -- the rotated rows y = R x that sit between the rotation kernel and the nearest-centroid kernel -- and normally
 // takes it from the stream-ordered pool.  The entry point below keeps that scratch in a fixed array that is part
-// of the library image instead, and touches no allocator at all.
+// of the library image instead, and runs the nearest-centroid step on the CUDA-core kernels, which need no device
+// memory of their own (the tensor-core kernel vqb_opq_quantize prefers works through operand tiles and a mark map
+// that the context allocates on first use and grows with the batch).  Nothing on this path calls an allocator or
+// creates an event, whether or not the context has been used before.
 #include <mutex>
 
 #include "../../include/vqb.h"
@@ -70,7 +73,9 @@ extern "C" int vqb_opq_quantize_static(vqb_opq *oq, const float *x, size_t n, si
         sh.m = P.m;
         sh.sd = P.sd;
         sh.k = P.k;
-        dev.pq_encode(sh, y, P.codebooks, P.metric, P.p, out_f16, codes, nullptr);
+        // the CUDA-core nearest-centroid kernels: codebooks in shared memory, rows in registers, nothing else -- the tensor-core
+        // kernel vqb_opq_quantize uses keeps operand tiles and a mark map in device memory that the context allocates
+        dev.pq_encode_no_scratch(sh, y, P.codebooks, P.metric, P.p, out_f16, codes);
         return VQB_OK;
     } catch (const vqb::Error &e) {
         *P.err = e.what();

@@ -52,7 +52,9 @@ namespace vqb {
 
 namespace {
 
-constexpr int BM = 128, BN = 256, SDW = 8, KOP = 32, NSTAGE = 4, MAXM = 64, XH_RING = 8, NTHREADS = 448;
+constexpr int BM = 128, BN = 256, SDW = 8, KOP = 32, NSTAGE_MAX = 4, MAXM = 64, XH_RING = 8, NTHREADS = 448;
+// operand-A ring: four stages; three when the CTA also keeps the cluster sums of its four sub-spaces in shared memory
+__host__ __device__ constexpr int stages_for(bool fuse) { return fuse ? 3 : 4; }
 constexpr uint32_t A_STAGE_BYTES = BM * 128; // 16 KiB
 constexpr uint32_t B_BYTES = BN * 128;       // 32 KiB per sub-space
 constexpr float PAD_SCORE = 1e30f;           // score of the columns beyond k
@@ -66,7 +68,7 @@ constexpr size_t OFF_STATS = OFF_HMAX + MAXM;                   // 2 x u64: mark
 constexpr size_t SCRATCH_FLOATS = OFF_STATS + 4;
 
 struct alignas(8) PqBarriers {
-    unsigned long long afull[NSTAGE], aempty[NSTAGE], bfull, tfull[2], tempty[2];
+    unsigned long long afull[NSTAGE_MAX], aempty[NSTAGE_MAX], bfull, tfull[2], tempty[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -79,6 +81,10 @@ struct PqTcParams {
     unsigned long long *stats;
     int *error;
     float *dbg_scores; // optional [n][m][256]
+    // fused cluster sums (training only, may be null): every decided row is added to its new cluster in the same pass
+    float *sums;       // [m][k][8]
+    uint32_t *counts;  // [m][k], u32 or f32 values (counts_f32)
+    int counts_f32;
 };
 
 __device__ __forceinline__ float to_tf32(float v)
@@ -98,17 +104,29 @@ __device__ __forceinline__ float fma_sat(float a, float b, float c)
 // order in which the four sub-spaces of a group are issued: accumulator / team = ss >> 1 alternates
 __device__ __forceinline__ int issue_order(int p) { return ((p & 1) << 1) | (p >> 1); } // 0, 2, 1, 3
 
-template <bool TRAIN, bool EUCLID>
+// shared memory after the 1 KiB alignment: operand B, operand-A ring, |x|^2/2 ring, then either the binary16 images of
+// the centroids (encode) or the cluster sums and counts of the CTA's four sub-spaces (training with fused sums), barriers
+__host__ __device__ constexpr size_t smem_bytes_for(bool fuse)
+{
+    return 1024 + 4 * (size_t)B_BYTES + (size_t)stages_for(fuse) * A_STAGE_BYTES + (size_t)XH_RING * BM * sizeof(float) +
+           (fuse ? (size_t)4 * BN * (SDW + 1) * sizeof(float) : (size_t)4 * BN * 16) + sizeof(PqBarriers) + 64;
+}
+
+template <bool TRAIN, bool EUCLID, bool FUSE>
 __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constant__ CUtensorMap map_b, const PqTcParams Q)
 {
+    static_assert(!FUSE || TRAIN, "cluster sums are gathered by training passes only");
+    constexpr int NSTAGE = stages_for(FUSE);
     extern __shared__ unsigned char smem_raw[];
     const AssignParams &P = Q.a;
     unsigned char *base = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char *b_smem = base;                                           // 4 x 32 KiB
     unsigned char *a_smem = base + 4 * (size_t)B_BYTES;                     // NSTAGE x 16 KiB
     float *xh_ring = reinterpret_cast<float *>(a_smem + (size_t)NSTAGE * A_STAGE_BYTES); // [XH_RING][128]
-    const uint4 *c16_s = reinterpret_cast<const uint4 *>(xh_ring + XH_RING * BM);         // [4][256] binary16 images
-    PqBarriers *bars = reinterpret_cast<PqBarriers *>(xh_ring + XH_RING * BM + 4 * BN * 4);
+    const uint4 *c16_s = reinterpret_cast<const uint4 *>(xh_ring + XH_RING * BM);         // [4][256] binary16 images (encode)
+    float *ssum = xh_ring + XH_RING * BM;                                                 // [4][8][256] cluster sums (FUSE), same place
+    uint32_t *scnt = reinterpret_cast<uint32_t *>(ssum + 4 * SDW * BN);                   // [4][256]
+    PqBarriers *bars = reinterpret_cast<PqBarriers *>(xh_ring + XH_RING * BM + (FUSE ? 4 * BN * (SDW + 1) : 4 * BN * 4));
     volatile int *abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -154,6 +172,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    if (FUSE)
+        for (int t = threadIdx.x; t < 4 * BN * (SDW + 1); t += NTHREADS) ssum[t] = 0.0f; // sums and counts (0.0f == 0u)
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -270,6 +290,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
             const bool valid = row < P.n;
             uint32_t old2 = 0;
             if (TRAIN && valid) old2 = *reinterpret_cast<const uint16_t *>(reinterpret_cast<const uint8_t *>(P.codes) + row * (unsigned long long)m + g * 4 + team * 2);
+            // FUSE: this row's slices of the team's two sub-spaces, added to the cluster sums once the codes are known (the
+            // producers read the same bytes a moment ago, so this is an L2 hit, requested a whole unit before it is used)
+            float4 xs[4];
+            if (FUSE && valid) {
+                const float4 *src = reinterpret_cast<const float4 *>(P.x + row * P.ld + (size_t)g * 32 + team * 16);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) xs[i] = __ldg(src + i);
+            }
             int idxs[2] = {0, 0};
             uint32_t marked = 0, done = 0;
 #pragma unroll 1
@@ -409,6 +437,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                                 }
                             }
                     }
+                    if (FUSE) { // shared-memory sums [sub-space][dimension][code]: the lanes of a warp (different rows) spread over the banks
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+                            if ((done >> h & 1u) && !(marked >> h & 1u)) {
+                                float *dst = ssum + (size_t)((team * 2 + h) * SDW) * BN + idxs[h];
+                                const float4 a = xs[2 * h], b = xs[2 * h + 1];
+                                atomicAdd(dst, a.x);
+                                atomicAdd(dst + BN, a.y);
+                                atomicAdd(dst + 2 * BN, a.z);
+                                atomicAdd(dst + 3 * BN, a.w);
+                                atomicAdd(dst + 4 * BN, b.x);
+                                atomicAdd(dst + 5 * BN, b.y);
+                                atomicAdd(dst + 6 * BN, b.z);
+                                atomicAdd(dst + 7 * BN, b.w);
+                                atomicAdd(scnt + (team * 2 + h) * BN + idxs[h], 1u);
+                            }
+                    }
                 } else {
                     const int dim = m * SDW;
 #pragma unroll
@@ -437,7 +482,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
             moved_mask = __reduce_or_sync(0xffffffffu, moved_mask);
             if (lane == 0)
                 for (int ss = 0; ss < 4; ++ss)
-                    if (moved_mask & (1u << ss)) atomicOr(P.changed + g * 4 + ss, 1u);
+                    if (moved_mask & (1u << ss)) atomicOr(P.changed + g * 4 + ss, VQB_MOVED_BITS);
         }
     }
 
@@ -446,6 +491,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+    if (FUSE) { // the CTA's partial sums join the global ones (clusters this CTA never met are skipped)
+        for (int t = threadIdx.x; t < 4 * BN * SDW; t += NTHREADS) {
+            const int ss = t / (BN * SDW), rem = t % (BN * SDW), j = rem / SDW, d = rem % SDW;
+            if (j < k && scnt[ss * BN + j] != 0u) atomicAdd(Q.sums + ((size_t)(g * 4 + ss) * k + j) * SDW + d, ssum[(size_t)(ss * SDW + d) * BN + j]);
+        }
+        for (int t = threadIdx.x; t < 4 * BN; t += NTHREADS) {
+            const int ss = t / BN, j = t % BN;
+            const uint32_t c = scnt[t];
+            if (j < k && c != 0u) {
+                if (Q.counts_f32) atomicAdd(reinterpret_cast<float *>(Q.counts) + (size_t)(g * 4 + ss) * k + j, (float)c);
+                else atomicAdd(Q.counts + (size_t)(g * 4 + ss) * k + j, c);
+            }
+        }
     }
 }
 
@@ -604,6 +663,13 @@ template <bool TRAIN, bool EUCLID> __global__ void __launch_bounds__(256) pq_mar
                 }
                 d0 = __shfl_sync(0xffffffffu, d0, 0);
                 const int idx = (bi == 0x7fffffff || !(d0 == d0)) ? 0 : bi; // nothing below +inf, or the scan started at a NaN
+                if (TRAIN && Q.sums) { // the tensor kernel left this pair out of its sums
+                    if (lane < SDW) atomicAdd(Q.sums + ((size_t)s * k + idx) * SDW + lane, s_x[i][lane]);
+                    if (lane == SDW) {
+                        if (Q.counts_f32) atomicAdd(reinterpret_cast<float *>(Q.counts) + (size_t)s * k + idx, 1.0f);
+                        else atomicAdd(Q.counts + (size_t)s * k + idx, 1u);
+                    }
+                }
                 if (lane == 0) {
                     bool moved = false;
                     if (TRAIN) {
@@ -626,7 +692,7 @@ template <bool TRAIN, bool EUCLID> __global__ void __launch_bounds__(256) pq_mar
     }
     if (TRAIN && lane == 0) {
         for (int s = 0; s < m; ++s)
-            if ((s < 32 ? moved_lo >> s : moved_hi >> (s - 32)) & 1u) atomicOr(P.changed + s, 1u);
+            if ((s < 32 ? moved_lo >> s : moved_hi >> (s - 32)) & 1u) atomicOr(P.changed + s, VQB_MOVED_BITS);
     }
 }
 
@@ -642,11 +708,13 @@ bool pq_tc_applicable(const AssignParams &p, int metric)
 
 size_t pq_tc_scratch_floats() { return SCRATCH_FLOATS; }
 size_t pq_tc_stats_offset_floats() { return OFF_STATS; }
+size_t pq_tc_mark_bytes(size_t n, size_t m) { return (n * (m / 2) + 15) & ~(size_t)15; } // read 16 bytes at a time
 
-template <bool TRAIN, bool EUCLID>
-static void launch_t(CudaDevice &dev, const CUtensorMap &mb, const PqTcParams &q, size_t smem, unsigned grid)
+template <bool TRAIN, bool EUCLID, bool FUSE>
+static void launch_t(CudaDevice &dev, const CUtensorMap &mb, const PqTcParams &q, unsigned grid)
 {
-    auto kernel = pq_tc_kernel<TRAIN, EUCLID>;
+    auto kernel = pq_tc_kernel<TRAIN, EUCLID, FUSE>;
+    constexpr size_t smem = smem_bytes_for(FUSE);
     static std::atomic<unsigned long long> configured{0}; // bit d: the attribute has been set on device d (it is per device and sticky)
     const unsigned long long bit = 1ull << (dev.device() & 63);
     if (!(configured.load(std::memory_order_relaxed) & bit)) {
@@ -670,39 +738,132 @@ static void launch_t(CudaDevice &dev, const CUtensorMap &mb, const PqTcParams &q
     }
 }
 
-void launch_pq_tc(CudaDevice &dev, const AssignParams &p, int metric, bool train, size_t code_bytes, float *scratch, int *error_word,
-                  float *dbg_scores)
+void launch_pq_operand_b(CudaDevice &dev, const float *centroids, int m, int k, float *scratch)
+{
+    KernelScope ks(dev, "pq_operand_b");
+    pq_operand_b_kernel<<<m, BN, 0, dev.stream()>>>(centroids, k, scratch + OFF_BOP, reinterpret_cast<uint4 *>(scratch + OFF_C16), scratch + OFF_HMAX);
+    VQB_CUDA_CHECK(cudaGetLastError());
+    dev.count_launch();
+}
+
+void launch_pq_tc(CudaDevice &dev, const AssignParams &p, int metric, bool train, size_t code_bytes, const PqTcBuffers &b)
 {
     if (train && code_bytes != 1) throw Error(100, "pq tensor path: one-byte codes expected for k <= 256");
-    float *bop = scratch + OFF_BOP;
-    uint4 *c16 = reinterpret_cast<uint4 *>(scratch + OFF_C16);
-    float *hnmax = scratch + OFF_HMAX;
-    unsigned long long *stats = reinterpret_cast<unsigned long long *>(scratch + OFF_STATS);
-    {
-        KernelScope ks(dev, "pq_operand_b");
-        pq_operand_b_kernel<<<p.m, BN, 0, dev.stream()>>>(p.centroids, p.k, bop, c16, hnmax);
-        VQB_CUDA_CHECK(cudaGetLastError());
-        dev.count_launch();
-    }
-    const size_t mark_bytes = ((size_t)p.n * (size_t)(p.m / 2) + 15) & ~(size_t)15; // read 16 bytes at a time
-    uint8_t *marks = dev.pq_mark_buffer(mark_bytes); // all zero between launches: the follow-up kernel clears what it reads
+    float *bop = b.scratch + OFF_BOP;
+    if (b.prepare_operand) launch_pq_operand_b(dev, p.centroids, p.m, p.k, b.scratch);
     const CUtensorMap mb = make_tensor_map_2d(bop, KOP, (unsigned long long)p.m * BN, KOP, BN, CU_TENSOR_MAP_SWIZZLE_128B);
     PqTcParams q;
     q.a = p;
-    q.c16 = c16;
-    q.hnmax = hnmax;
-    q.marks = marks;
-    q.stats = stats;
-    q.error = error_word;
-    q.dbg_scores = dbg_scores;
-    const size_t smem = 1024 + 4 * (size_t)B_BYTES + (size_t)NSTAGE * A_STAGE_BYTES + ((size_t)XH_RING * BM + 4 * BN * 4) * sizeof(float) + sizeof(PqBarriers) + 64;
+    q.c16 = reinterpret_cast<uint4 *>(b.scratch + OFF_C16);
+    q.hnmax = b.scratch + OFF_HMAX;
+    q.marks = b.marks; // all zero between launches: the follow-up kernel clears what it reads
+    q.stats = reinterpret_cast<unsigned long long *>(b.scratch + OFF_STATS);
+    q.error = b.error_word;
+    q.dbg_scores = b.dbg_scores;
+    q.sums = train ? b.sums : nullptr;
+    q.counts = b.counts;
+    q.counts_f32 = b.counts_f32 ? 1 : 0;
     const unsigned long long tiles = (p.n + BM - 1) / BM;
     const unsigned ngroups = (unsigned)p.m / 4;
     const unsigned per = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>(tiles, (unsigned long long)dev.sm_count() / ngroups));
     const unsigned grid = per * ngroups;
-    if (train) launch_t<true, false>(dev, mb, q, smem, grid);
-    else if (metric == M_EUCLID) launch_t<false, true>(dev, mb, q, smem, grid);
-    else launch_t<false, false>(dev, mb, q, smem, grid);
+    if (train && q.sums) launch_t<true, false, true>(dev, mb, q, grid);
+    else if (train) launch_t<true, false, false>(dev, mb, q, grid);
+    else if (metric == M_EUCLID) launch_t<false, true, false>(dev, mb, q, grid);
+    else launch_t<false, false, false>(dev, mb, q, grid);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Centroid update of one k-means iteration for the shapes this file serves, in one launch (one CTA per sub-space, thread j =
+// cluster j): centroid = sum / count (src/vector.rs:315-316), the operand-B row, binary16 image and largest half norm the next
+// assignment pass needs, the iteration's flags for the host, and the sums / counts / flags cleared for the next iteration.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(BN) pq_update_centroids_kernel(float *sums, uint32_t *counts, uint32_t *moved, int counts_f32, const uint32_t *active,
+                                                                 int k, float *centroids, float *bop, uint4 *c16, float *hnmax, StatusPage sp)
+{
+    __shared__ float smax[BN];
+    const int s = blockIdx.x, j = threadIdx.x;
+    const bool act = !active || active[s] != 0;
+    bool empty = false;
+    if (act) {
+        float4 out[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        float hn = 0.0f;
+        uint4 img = make_uint4(0, 0, 0, 0);
+        if (j < k) {
+            const size_t cj = (size_t)s * k + j;
+            float4 *cp = reinterpret_cast<float4 *>(centroids + cj * SDW);
+            float4 *sp4 = reinterpret_cast<float4 *>(sums + cj * SDW);
+            const uint32_t cw = counts[cj];
+            const float cf = counts_f32 ? __uint_as_float(cw) : __uint2float_rn(cw);
+            float4 c0, c1;
+            if (cf != 0.0f) {
+                const float4 a = sp4[0], b = sp4[1];
+                c0 = make_float4(__fdiv_rn(a.x, cf), __fdiv_rn(a.y, cf), __fdiv_rn(a.z, cf), __fdiv_rn(a.w, cf));
+                c1 = make_float4(__fdiv_rn(b.x, cf), __fdiv_rn(b.y, cf), __fdiv_rn(b.z, cf), __fdiv_rn(b.w, cf));
+                cp[0] = c0;
+                cp[1] = c1;
+                sp4[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+                sp4[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                counts[cj] = 0u;
+            } else { // an empty cluster keeps its centroid until the host re-seeds it (src/utils.rs:99-101)
+                empty = true;
+                c0 = cp[0];
+                c1 = cp[1];
+            }
+            const float v[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            float hi[8], lo[8], a2 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                hi[i] = to_tf32(v[i]);
+                lo[i] = to_tf32(v[i] - hi[i]);
+                a2 = fmaf(v[i], v[i], a2);
+            }
+            hn = 0.5f * a2;
+            const float hh = to_tf32(hn), hl = to_tf32(hn - hh);
+            out[0] = out[4] = make_float4(-hi[0], -hi[1], -hi[2], -hi[3]);
+            out[1] = out[5] = make_float4(-hi[4], -hi[5], -hi[6], -hi[7]);
+            out[2] = make_float4(-lo[0], -lo[1], -lo[2], -lo[3]);
+            out[3] = make_float4(-lo[4], -lo[5], -lo[6], -lo[7]);
+            out[6] = make_float4(hh, hl, 0.f, 0.f);
+            img.x = f32_to_f16_bits(v[0]) | ((uint32_t)f32_to_f16_bits(v[1]) << 16);
+            img.y = f32_to_f16_bits(v[2]) | ((uint32_t)f32_to_f16_bits(v[3]) << 16);
+            img.z = f32_to_f16_bits(v[4]) | ((uint32_t)f32_to_f16_bits(v[5]) << 16);
+            img.w = f32_to_f16_bits(v[6]) | ((uint32_t)f32_to_f16_bits(v[7]) << 16);
+        } else {
+            out[6] = make_float4(to_tf32(PAD_SCORE), 0.f, 0.f, 0.f);
+        }
+        float4 *o = reinterpret_cast<float4 *>(bop + ((size_t)s * BN + j) * KOP);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = out[i];
+        c16[(size_t)s * BN + j] = img;
+        smax[j] = (j < k) ? fabsf(hn) : 0.0f;
+        __syncthreads();
+        for (int o2 = BN / 2; o2 > 0; o2 >>= 1) {
+            if (j < o2) smax[j] = fmaxf(smax[j], smax[j + o2]);
+            __syncthreads();
+        }
+        if (j == 0) hnmax[s] = smax[0];
+    }
+    // flags of this sub-space for the host: 8 bitmap words (bit = cluster without rows) and the "some row moved" word
+    const uint32_t bits = __ballot_sync(0xffffffffu, empty);
+    if ((j & 31) == 0) sp.host_bitmap()[(size_t)s * sp.words_per_subspace + (j >> 5)] = bits;
+    if (j == 0) {
+        sp.host_moved()[s] = act ? moved[s] : 0u;
+        moved[s] = 0u;
+    }
+    status_publish(sp);
+}
+
+void launch_pq_update_centroids(CudaDevice &dev, int m, int k, float *sums, uint32_t *counts, uint32_t *moved, bool counts_f32,
+                                const uint32_t *active, float *centroids, float *scratch, const StatusPage &sp)
+{
+    KernelScope ks(dev, "update_centroids");
+    pq_update_centroids_kernel<<<m, BN, 0, dev.stream()>>>(sums, counts, moved, counts_f32 ? 1 : 0, active, k, centroids, scratch + OFF_BOP,
+                                                            reinterpret_cast<uint4 *>(scratch + OFF_C16), scratch + OFF_HMAX, sp);
+    VQB_CUDA_CHECK(cudaGetLastError());
+    dev.count_launch();
 }
 
 } // namespace vqb

@@ -253,7 +253,7 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
         __syncwarp();
     }
     if (MODE == R_TRAIN) {
-        if (__any_sync(0xffffffffu, moved) && lane == 0) atomicOr(P.changed, 1u);
+        if (__any_sync(0xffffffffu, moved) && lane == 0) atomicOr(P.changed, VQB_MOVED_BITS);
     }
     if (MODE == R_RVQ_UPDATE) {
 #pragma unroll
@@ -434,7 +434,7 @@ template <typename CodeT> __global__ void __launch_bounds__(128, 1) resolve_trai
             __syncwarp();
         }
     }
-    if (__any_sync(0xffffffffu, moved) && lane == 0) atomicOr(P.changed, 1u);
+    if (__any_sync(0xffffffffu, moved) && lane == 0) atomicOr(P.changed, VQB_MOVED_BITS);
 }
 
 template <int MODE, typename CodeT> void launch_t(CudaDevice &dev, const ResolveParams &p, const char *name)
