@@ -438,49 +438,90 @@ def run_secondary(args):
         e2e_fn = lambda: q.quantize(xp.numpy())  # noqa: E731
         e2e_rows, h2d, d2h = xp.shape[0], xp.numel() * 4, xp.numel()
     else:
+        import oracle
+        from vq_b200.seeding import LbgSeeder
+        oracle.use_all_host_threads()
+        sample_rows = min(rows, 65536)  # bounded CPU sample, scaled per vector (the cost per vector does not depend on n)
         if w == "rvq":
             xh = synth.gaussian_mixture(rows, DIM, 11)
             fit = lambda xx: vq.ResidualQuantizer.fit(xx, 8, K, ITERS, 0.01, vq.Distance.Euclidean, FIT_SEED, ctx=ctx)  # noqa: E731
-            kname, bytes_per_vec, cfg = "assign_train", 512, "rvq_1m_x128_8stages_k256_10iters_fit_plus_encode"
+            # full-width passes: the shortlist kernel reads every row once (512 B) plus its norm and writes the candidate mask
+            kname, bytes_per_vec, cfg = "dense_shortlist", 512 + 4 + 32, "rvq_1m_x128_8stages_k256_10iters_fit_plus_encode"
+
+            def cpu_run(xs):
+                sd_ = LbgSeeder(FIT_SEED)
+                t0 = time.perf_counter()
+                cb, _r, _n = oracle.rvq_fit(xs, 8, K, ITERS, 0.01, oracle.EUCLIDEAN, sd_.init_indices, sd_.draw)
+                t1 = time.perf_counter()
+                oracle.rvq_quantize(cb, 0.01, xs, oracle.EUCLIDEAN)
+                return t1 - t0, time.perf_counter() - t1
         elif w == "tsvq":
             xh = synth.uniform01(rows, DIM, 1)
             fit = lambda xx: vq.TSVQ(xx, 10, vq.Distance.Euclidean, ctx=ctx)  # noqa: E731  (depth 10: benches/bench_tsvq.rs:11)
             kname, bytes_per_vec, cfg = "tsvq_node_stats", 2 * 512, "tsvq_1m_x128_depth10_fit_plus_encode"
+
+            def cpu_run(xs):
+                t0 = time.perf_counter()
+                cen, left, right = oracle.tsvq_fit(xs, 10)
+                t1 = time.perf_counter()
+                oracle.tsvq_quantize(cen, left, right, xs, oracle.EUCLIDEAN)
+                return t1 - t0, time.perf_counter() - t1
         else:
             xh = synth.correlated(rows, DIM, 3)
             fit = lambda xx: vq.OptimizedProductQuantizer.fit(xx, M, K, 5, 10, vq.Distance.Euclidean, FIT_SEED, ctx=ctx)  # noqa: E731
             kname, bytes_per_vec, cfg = "assign_train", TRAIN_BYTES_PER_VEC, "opq_1m_x128_m16_k256_10outer_x_5iters_fit_plus_encode"
+
+            def cpu_run(xs):
+                sd_ = LbgSeeder(FIT_SEED)
+                init_ = np.stack([sd_.init_indices(i, xs.shape[0], K) for i in range(M)])
+                t0 = time.perf_counter()
+                rot, cb = oracle.opq_fit(xs, M, K, 5, 10, oracle.EUCLIDEAN, init_, sd_.draw)
+                t1 = time.perf_counter()
+                oracle.opq_quantize(rot, cb, xs, oracle.EUCLIDEAN)
+                return t1 - t0, time.perf_counter() - t1
         x = torch.from_numpy(xh).cuda()
+        xp = torch.empty((rows, DIM), dtype=torch.float32, pin_memory=True)
+        xp.copy_(torch.from_numpy(xh))
 
         def step():
             t_fit, qz = timed(lambda: fit(x))
             t_enc, out = timed(lambda: qz.quantize(x))
             extra["train_s"], extra["encode_s"] = t_fit, t_enc
             return out
-        cpu, e2e_fn, e2e_rows, h2d, d2h = None, None, 0, 0, 0
 
-    for _ in range(max(1, min(3, args.warmup)) if w in ("rvq", "opq", "tsvq") else max(3, args.warmup)):
+        def e2e_fn():  # host rows in (pinned), host f16 out, through the same public calls
+            qz = fit(xp.numpy())
+            return qz.quantize(xp.numpy())
+        cpu_fit, cpu_enc = cpu_run(np.ascontiguousarray(xh[:sample_rows]))
+        cpu = {"value": sample_rows / (cpu_fit + cpu_enc) / 1e6, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+               "sample": f"{sample_rows} of {rows} rows, full algorithm, scaled per vector",
+               "train_s_per_1m_rows": cpu_fit * 1e6 / sample_rows, "encode_mvec_per_s": sample_rows / cpu_enc / 1e6}
+        e2e_rows, h2d, d2h = rows, 2 * rows * DIM * 4, rows * DIM * 2
+
+    heavy = w in ("rvq", "opq", "tsvq")
+    for _ in range(max(1, min(3, args.warmup)) if heavy else max(3, args.warmup)):
         step()
     sampler.start()
-    ctx.timing(True)
-    ctx.timing_report()
     l0 = ctx.launch_count()
     times = []
-    for _ in range(args.steps):
-        if w in ("sq", "bq"):
+    for _ in range(args.steps):  # the loop behind `value`: no per-kernel events in it
+        if not heavy:
             t, _o = timed(step)
         else:
             step()
             t = extra["train_s"] + extra["encode_s"]
         times.append(t)
     launches = ctx.launch_count() - l0
+    clocks = sampler.stop()
+    ctx.timing(True)  # per-kernel breakdown in a pass of its own
+    ctx.timing_report()
+    timed(step) if not heavy else step()
     kernels = ctx.timing_report()
     ctx.timing(False)
-    clocks = sampler.stop()
     step_s = sum(times) / len(times)
     e2e = None
-    if e2e_fn is not None:
-        ts = [timed(e2e_fn)[0] for _ in range(4)][1:]
+    if e2e_fn is not None and not args.kernels_only:
+        ts = [timed(e2e_fn)[0] for _ in range(2 if heavy else 4)][1:]
         e2e = {"value": e2e_rows / (sum(ts) / len(ts)) / 1e6, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                "rows": e2e_rows}
     kk = kernels.get(kname)
