@@ -147,6 +147,15 @@ int vqb_evaluate_f16(vqb_ctx *ctx, const float *x, const uint16_t *q_f16, size_t
 int vqb_dense_dots(vqb_ctx *ctx, const float *x, size_t n, size_t dim, const float *codebook, size_t k,
                    float *dots_out, unsigned long long *stats_out);
 
+/* The two dense contractions of OptimizedProductQuantizer::fit as calls of their own (they run inside vqb_opq_fit and
+ * vqb_opq_quantize; exposed so that their accuracy can be checked against f64):
+ *   vqb_opq_rotate_rows   y[r] = R x[r]                  src/opq.rs:186-194, 232-234   rot: dim x dim row-major
+ *   vqb_opq_cross_cov     a = sum_r y[r] x[r]^T (f64)     src/opq.rs:172-179            a_out: dim x dim row-major
+ * For 32 <= dim <= 128 in steps of 32 both run on the tensor cores with split-TF32 operands (f32-level accuracy); other
+ * widths take the FP32 kernels.  Pointers may be host or device. */
+int vqb_opq_rotate_rows(vqb_ctx *ctx, const float *rot, size_t dim, const float *x, size_t n, float *y_out);
+int vqb_opq_cross_cov(vqb_ctx *ctx, const float *y, const float *x, size_t n, size_t dim, double *a_out);
+
 /* Diagnostic for the tensor-core path of the product quantizer (sub-space width 8): the raw split-TF32 scores
  * |c_j|^2/2 - x.c_j (scores_out: n x m x 256, may be NULL), the codes the path produces (codes_out: n x m) and the number
  * of (row, sub-space) pairs it left to the exact scan.  Requires m % 4 == 0, 4 <= m <= 64, 2 <= k <= 256.

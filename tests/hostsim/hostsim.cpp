@@ -74,8 +74,8 @@ class HostDevice : public Device {
             std::memcpy(centroids + ((size_t)patches[p].subspace * sh.k + patches[p].cluster) * sh.sd, &stage[p * sh.sd],
                         sh.sd * sizeof(float));
     }
-    bool assign_train(const Shape &sh, const float *x, const float *centroids, void *codes_v, const uint32_t *active,
-                      const IterBuffers &buf, bool) override
+    void assign_train(const Shape &sh, const float *x, const float *centroids, void *codes_v, const uint32_t *active,
+                      const IterBuffers &buf) override
     {
         uint32_t *codes = (uint32_t *)codes_v;
         for (size_t s = 0; s < sh.m; ++s) {
@@ -95,7 +95,6 @@ class HostDevice : public Device {
                 codes[i * sh.m + s] = best;
             }
         }
-        return false; // the sums are always a separate pass here
     }
     static void add_count(const IterBuffers &buf, size_t at)
     {

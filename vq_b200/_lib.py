@@ -46,6 +46,8 @@ SIGNATURES = {
     "vqb_evaluate_f16": (C.c_int, [_P, _P, _P, _SZ, _SZ, _SZ, C.POINTER(C.c_float), C.POINTER(C.c_float)]),
     "vqb_pq_tensor_scores": (C.c_int, [_P, _P, _SZ, _SZ, _P, _SZ, _P, _P, _P]),
     "vqb_dense_dots": (C.c_int, [_P, _P, _SZ, _SZ, _P, _SZ, _P, _P]),
+    "vqb_opq_rotate_rows": (C.c_int, [_P, _P, _SZ, _P, _SZ, _P]),
+    "vqb_opq_cross_cov": (C.c_int, [_P, _P, _P, _SZ, _SZ, _P]),
     "vqb_lbg_fit": (C.c_int, [_P, _P, _SZ, _SZ, _SZ, _SZ, _P, DRAW_FN, _P, C.c_int, _P, C.POINTER(_SZ)]),
     "vqb_pq_fit": (C.c_int, [_P, _P, _SZ, _SZ, _SZ, _SZ, _SZ, C.c_int, C.c_double, _P, DRAW_FN, _P, C.c_int,
                              C.POINTER(_P)]),

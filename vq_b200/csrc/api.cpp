@@ -491,6 +491,36 @@ int vqb_pq_tensor_scores(vqb_ctx *ctx, const float *x, size_t n, size_t m, const
     });
 }
 
+int vqb_opq_rotate_rows(vqb_ctx *ctx, const float *rot, size_t dim, const float *x, size_t n, float *y_out)
+{
+    if (!ctx) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "ctx is NULL");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (!rot || !x || !y_out || n == 0 || dim == 0) throw Error(VQB_ERR_BAD_ARGUMENT, "NULL or empty argument");
+        CudaDevice &dev = *ctx->dev;
+        In ir(dev, rot, sizeof(float) * dim * dim), ix(dev, x, sizeof(float) * n * dim);
+        Out oy(dev, y_out, sizeof(float) * n * dim);
+        dev.rotate_rows(ir.as<float>(), dim, ix.as<float>(), n, oy.as<float>());
+        oy.finish();
+        dev.synchronize();
+    });
+}
+
+int vqb_opq_cross_cov(vqb_ctx *ctx, const float *y, const float *x, size_t n, size_t dim, double *a_out)
+{
+    if (!ctx) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "ctx is NULL");
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return guarded(ctx, [&] {
+        if (!y || !x || !a_out || n == 0 || dim == 0) throw Error(VQB_ERR_BAD_ARGUMENT, "NULL or empty argument");
+        CudaDevice &dev = *ctx->dev;
+        In iy(dev, y, sizeof(float) * n * dim), ix(dev, x, sizeof(float) * n * dim);
+        Out oa(dev, a_out, sizeof(double) * dim * dim);
+        dev.cross_cov(iy.as<float>(), ix.as<float>(), n, dim, oa.as<double>());
+        oa.finish();
+        dev.synchronize();
+    });
+}
+
 int vqb_lbg_fit(vqb_ctx *ctx, const float *x, size_t n, size_t d, size_t k, size_t max_iters, const uint64_t *init_idx,
                 vqb_draw_fn draw, void *user, int flags, float *centroids_out, size_t *iterations_out)
 {

@@ -107,10 +107,8 @@ class Device {
     // Nearest centroid under squared Euclidean (src/utils.rs:59-73); codes are read as the previous
     // assignment and overwritten; buf.moved[s] becomes non-zero if any row of subspace s moved (76-80).
     // Subspaces with active[s] == 0 are left untouched.
-    // With fuse_sums the device MAY also add every row to buf.sums / buf.counts of its new cluster in the same pass
-    // (order unspecified, like src/vector.rs:298-304); it returns true when it did, and the caller then skips accumulate.
-    virtual bool assign_train(const Shape &sh, const float *x, const float *centroids, void *codes,
-                              const uint32_t *active, const IterBuffers &buf, bool fuse_sums) = 0;
+    virtual void assign_train(const Shape &sh, const float *x, const float *centroids, void *codes,
+                              const uint32_t *active, const IterBuffers &buf) = 0;
     // buf.sums[s][j][:] += the rows assigned to (s, j), buf.counts[s][j] += how many (src/utils.rs:83-92,
     // src/vector.rs:297-314); the buffer comes in zero-filled.  ordered = ascending row order per cluster.
     virtual void accumulate(const Shape &sh, const float *x, const void *codes, const uint32_t *active,

@@ -13,6 +13,7 @@
 #include "assign_generic.cuh"
 #include "assign_reg.cuh"
 #include "dense_tc.hpp"
+#include "opq_tc.hpp"
 #include "pq_tc.hpp"
 #include "kernels_common.cuh"
 
@@ -51,14 +52,13 @@ CudaDevice::CudaDevice(int device) : device_(device)
         // CUDA-core filter kernel); VQB_PQ_TENSOR=0 selects the filter kernel (A/B comparisons).
         const char *f = std::getenv("VQB_PQ_TENSOR");
         pq_tensor_enabled_ = tensor_enabled_ && !(f && *f == '0');
-        const char *fu = std::getenv("VQB_PQ_FUSE_SUMS"); // 0: cluster sums in a separate pass over the rows (A/B comparisons)
-        pq_fuse_sums_ = !(fu && *fu == '0');
-        const char *bm = std::getenv("VQB_DENSE_BLOCK_MB"); // block size of the full-width k-means passes (default 48 MiB)
-        if (bm && *bm) {
-            const long v = std::atol(bm);
-            if (v > 0) dense_block_bytes_ = (size_t)v << 20;
-        }
     }
+    {
+        const char *o = std::getenv("VQB_OPQ_TENSOR"); // 0: rotation and cross-covariance on the CUDA-core kernels (A/B comparisons)
+        opq_tensor_enabled_ = tensor_enabled_ && !(o && *o == '0');
+    }
+    // the small fixed-size buffers of the tensor-core kernels exist from the start, so that no later call has to create them
+    if (tensor_enabled_) ensure_tc_buffers(0);
     cudaMemPool_t pool;
     if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
         unsigned long long keep = ~0ull; // keep freed blocks cached; repeated fits reuse them
@@ -77,6 +77,7 @@ CudaDevice::~CudaDevice()
         if (stage_) cudaFreeHost(stage_);
         cudaFree(rownorm_);
         cudaFree(hn_scratch_);
+        cudaFree(rot_split_);
         cudaFree(pq_scratch_);
         cudaFree(pq_marks_);
         cudaFree(cand_);
@@ -240,7 +241,8 @@ void CudaDevice::download(void *dst, const void *src, size_t bytes)
 void CudaDevice::ensure_tc_buffers(size_t n)
 {
     if (!hn_scratch_) {
-        device_allocs_ += 4;
+        device_allocs_ += 5;
+        VQB_CUDA_CHECK(cudaMalloc(&rot_split_, opq_tc_split_floats(128) * sizeof(float)));
         VQB_CUDA_CHECK(cudaMalloc(&hn_scratch_, 260 * sizeof(float)));
         VQB_CUDA_CHECK(cudaMalloc(&pq_scratch_, pq_tc_scratch_floats() * sizeof(float)));
         VQB_CUDA_CHECK(cudaMemsetAsync(pq_scratch_, 0, pq_tc_scratch_floats() * sizeof(float), stream_));
@@ -424,41 +426,27 @@ void CudaDevice::patch_centroids(const Shape &sh, const float *x, uint64_t row_b
 // ------------------------------------------------------------------------------------------------
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-bool CudaDevice::assign_train(const Shape &sh, const float *x, const float *centroids, void *codes, const uint32_t *active,
-                              const IterBuffers &buf, bool fuse_sums)
+void CudaDevice::assign_train(const Shape &sh, const float *x, const float *centroids, void *codes, const uint32_t *active,
+                              const IterBuffers &buf)
 {
-    if (sh.n_local == 0) return false;
+    if (sh.n_local == 0) return;
     uint32_t *changed = buf.moved;
     if (prepared_x_ == x && prepared_n_ == sh.n_local && prepared_dim_ == sh.sd && sh.m == 1 &&
         dense_tc_applicable(sh.n_local, sh.sd, sh.k, M_SQ, x)) {
-        // full-width k-means step: tensor-core shortlist, then the exact decision among the candidates.  The rows are walked
-        // in blocks that fit the L2 cache, so the second kernel (and, with fuse_sums, the third) finds its rows there.
-        size_t block_rows = std::max<size_t>(1024, dense_block_bytes_ / (sh.sd * sizeof(float)));
-        const size_t wave = (size_t)sm_count_ * 128; // one 128-row tile per persistent CTA
-        if (block_rows >= wave) block_rows -= block_rows % wave;
-        const size_t cb = code_bytes(sh.k);
-        for (size_t r0 = 0; r0 < sh.n_local; r0 += block_rows) {
-            const size_t rows = std::min(block_rows, sh.n_local - r0);
-            const float *xb = x + r0 * sh.sd;
-            dense_shortlist(*this, xb, rows, sh.sd, centroids, sh.k, rownorm_ + r0, hn_scratch_, cand_, nullptr, tc_error_, nullptr);
-            ResolveParams r = {};
-            r.x = xb;
-            r.n = rows;
-            r.dim = (int)sh.sd;
-            r.k = (int)sh.k;
-            r.codebook = centroids;
-            r.cand = cand_;
-            r.euclid = 0;
-            r.codes = static_cast<uint8_t *>(codes) + r0 * cb;
-            r.changed = changed;
-            launch_resolve(*this, r, R_TRAIN, cb);
-            if (fuse_sums) {
-                Shape blk = sh;
-                blk.n_local = rows;
-                accumulate(blk, xb, static_cast<uint8_t *>(codes) + r0 * cb, active, false, buf);
-            }
-        }
-        return fuse_sums;
+        // full-width k-means step: tensor-core shortlist, then the exact decision among the candidates
+        dense_shortlist(*this, x, sh.n_local, sh.sd, centroids, sh.k, rownorm_, hn_scratch_, cand_, nullptr, tc_error_, nullptr);
+        ResolveParams r = {};
+        r.x = x;
+        r.n = sh.n_local;
+        r.dim = (int)sh.sd;
+        r.k = (int)sh.k;
+        r.codebook = centroids;
+        r.cand = cand_;
+        r.euclid = 0;
+        r.codes = codes;
+        r.changed = changed;
+        launch_resolve(*this, r, R_TRAIN, code_bytes(sh.k));
+        return;
     }
     AssignParams p = {};
     p.x = x;
@@ -479,17 +467,11 @@ bool CudaDevice::assign_train(const Shape &sh, const float *x, const float *cent
         tb.marks = pq_mark_buffer(pq_tc_mark_bytes(sh.n_local, sh.m));
         tb.error_word = tc_error_;
         tb.prepare_operand = (bop_fresh_ != centroids);
-        const bool fuse = fuse_sums && pq_fuse_sums_;
-        if (fuse) {
-            tb.sums = buf.sums;
-            tb.counts = buf.counts;
-            tb.counts_f32 = buf.counts_f32;
-        }
         launch_pq_tc(*this, p, M_SQ, true, code_bytes(sh.k), tb);
         bop_fresh_ = nullptr;
-        return fuse;
+        return;
     }
-    if (launch_assign_reg(*this, p, M_SQ, true, code_bytes(sh.k))) return false;
+    if (launch_assign_reg(*this, p, M_SQ, true, code_bytes(sh.k))) return;
     GenericParams g = {};
     g.x = x;
     g.n = sh.n_local;
@@ -502,7 +484,7 @@ bool CudaDevice::assign_train(const Shape &sh, const float *x, const float *cent
     g.active = active;
     g.changed = changed;
     launch_assign_generic(*this, g, M_SQ, G_TRAIN, code_bytes(sh.k));
-    return false;
+    return;
 }
 
 void CudaDevice::pq_encode_impl(const Shape &sh, const float *x, const float *codebooks, int metric, double pm,
@@ -1100,6 +1082,10 @@ __global__ void __launch_bounds__(256) rotate_rows_kernel(const float *rot, int 
 void CudaDevice::rotate_rows(const float *rot, size_t dim, const float *x, size_t n, float *y)
 {
     if (n == 0 || dim == 0) return;
+    if (opq_tensor_enabled_ && opq_tc_applicable(dim, x, y) && (reinterpret_cast<uintptr_t>(rot) & 15u) == 0) {
+        launch_opq_rotate(*this, rot, dim, x, n, y, rot_split_, tc_error_);
+        return;
+    }
     const unsigned long long row_tiles = (n + 63) / 64;
     // gridDim.y is limited to 65535: walk the rows in slabs
     const unsigned long long slab = 65535ull;
@@ -1163,6 +1149,10 @@ void CudaDevice::cross_cov(const float *y, const float *x, size_t n, size_t dim,
 {
     zero(a, sizeof(double) * dim * dim);
     if (n == 0 || dim == 0) return;
+    if (opq_tensor_enabled_ && opq_tc_applicable(dim, x, y)) {
+        launch_opq_cross_cov(*this, y, x, n, dim, a, tc_error_);
+        return;
+    }
     const unsigned long long rows_per_cta = 2048;
     const unsigned long long splits = (n + rows_per_cta - 1) / rows_per_cta;
     const unsigned long long slab = 65535ull;

@@ -39,8 +39,8 @@ class CudaDevice : public Device {
     uint8_t *pq_mark_buffer(size_t bytes);
     void patch_centroids(const Shape &sh, const float *x, uint64_t row_begin, const RowPatch *patches, size_t n_patches,
                          float *centroids, Comm *comm) override;
-    bool assign_train(const Shape &sh, const float *x, const float *centroids, void *codes, const uint32_t *active,
-                      const IterBuffers &buf, bool fuse_sums) override;
+    void assign_train(const Shape &sh, const float *x, const float *centroids, void *codes, const uint32_t *active,
+                      const IterBuffers &buf) override;
     void accumulate(const Shape &sh, const float *x, const void *codes, const uint32_t *active, bool ordered,
                     const IterBuffers &buf) override;
     void update_centroids(const Shape &sh, const IterBuffers &buf, const uint32_t *active, float *centroids,
@@ -118,6 +118,8 @@ class CudaDevice : public Device {
     const float *prepared_x_ = nullptr;
     size_t prepared_n_ = 0, prepared_dim_ = 0;
     float *rownorm_ = nullptr, *hn_scratch_ = nullptr, *pq_scratch_ = nullptr;
+    float *rot_split_ = nullptr; // TF32 high and low parts of the rotation matrix of the current rotate_rows call (dim <= 128)
+    bool opq_tensor_enabled_ = true;
     uint8_t *pq_marks_ = nullptr;
     size_t pq_marks_cap_ = 0;
     bool pq_tensor_enabled_ = false;
@@ -128,10 +130,7 @@ class CudaDevice : public Device {
     void ensure_tc_buffers(size_t n);
     void pq_encode_impl(const Shape &sh, const float *x, const float *codebooks, int metric, double p, uint16_t *out_f16,
                         uint32_t *out_codes, float *out_f32, bool cuda_cores_only);
-    // VQB_PQ_FUSE_SUMS=0: the product-quantizer tensor kernel leaves the cluster sums to the separate pass (A/B comparisons)
-    bool pq_fuse_sums_ = true;
-    // rows of a full-width k-means pass are walked in blocks of this many bytes (VQB_DENSE_BLOCK_MB), small enough for L2
-    size_t dense_block_bytes_ = (size_t)48 << 20;
+
     void check_tc_error();
     bool timing_ = false;
     struct Span {

@@ -137,8 +137,8 @@ void lbg_fit(Device &dev, Comm *comm, const Shape &sh, const float *x, size_t ma
             dev.upload(act.p, active.data(), sizeof(uint32_t) * m);
             active_dirty = false;
         }
-        const bool summed = dev.assign_train(sh, x, centroids, codes.p, act.as<uint32_t>(), buf, !ordered); // 59-80 (+ 83-92)
-        if (!summed) dev.accumulate(sh, x, codes.p, act.as<uint32_t>(), ordered, buf);                      // 83-92
+        dev.assign_train(sh, x, centroids, codes.p, act.as<uint32_t>(), buf);          // 59-80
+        dev.accumulate(sh, x, codes.p, act.as<uint32_t>(), ordered, buf);              // 83-92
         if (multi) { // the only exchange of an iteration, ~144 KiB
             if (buf.counts_f32) {
                 comm->allreduce_sum_f32(buf.sums, words);

@@ -52,9 +52,7 @@ namespace vqb {
 
 namespace {
 
-constexpr int BM = 128, BN = 256, SDW = 8, KOP = 32, NSTAGE_MAX = 4, MAXM = 64, XH_RING = 8, NTHREADS = 448;
-// operand-A ring: four stages; three when the CTA also keeps the cluster sums of its four sub-spaces in shared memory
-__host__ __device__ constexpr int stages_for(bool fuse) { return fuse ? 3 : 4; }
+constexpr int BM = 128, BN = 256, SDW = 8, KOP = 32, NSTAGE = 4, MAXM = 64, XH_RING = 8, NTHREADS = 448;
 constexpr uint32_t A_STAGE_BYTES = BM * 128; // 16 KiB
 constexpr uint32_t B_BYTES = BN * 128;       // 32 KiB per sub-space
 constexpr float PAD_SCORE = 1e30f;           // score of the columns beyond k
@@ -68,7 +66,7 @@ constexpr size_t OFF_STATS = OFF_HMAX + MAXM;                   // 2 x u64: mark
 constexpr size_t SCRATCH_FLOATS = OFF_STATS + 4;
 
 struct alignas(8) PqBarriers {
-    unsigned long long afull[NSTAGE_MAX], aempty[NSTAGE_MAX], bfull, tfull[2], tempty[2];
+    unsigned long long afull[NSTAGE], aempty[NSTAGE], bfull, tfull[2], tempty[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -81,10 +79,6 @@ struct PqTcParams {
     unsigned long long *stats;
     int *error;
     float *dbg_scores; // optional [n][m][256]
-    // fused cluster sums (training only, may be null): every decided row is added to its new cluster in the same pass
-    float *sums;       // [m][k][8]
-    uint32_t *counts;  // [m][k], u32 or f32 values (counts_f32)
-    int counts_f32;
 };
 
 __device__ __forceinline__ float to_tf32(float v)
@@ -104,29 +98,19 @@ __device__ __forceinline__ float fma_sat(float a, float b, float c)
 // order in which the four sub-spaces of a group are issued: accumulator / team = ss >> 1 alternates
 __device__ __forceinline__ int issue_order(int p) { return ((p & 1) << 1) | (p >> 1); } // 0, 2, 1, 3
 
-// shared memory after the 1 KiB alignment: operand B, operand-A ring, |x|^2/2 ring, then either the binary16 images of
-// the centroids (encode) or the cluster sums and counts of the CTA's four sub-spaces (training with fused sums), barriers
-__host__ __device__ constexpr size_t smem_bytes_for(bool fuse)
-{
-    return 1024 + 4 * (size_t)B_BYTES + (size_t)stages_for(fuse) * A_STAGE_BYTES + (size_t)XH_RING * BM * sizeof(float) +
-           (fuse ? (size_t)4 * BN * (SDW + 1) * sizeof(float) : (size_t)4 * BN * 16) + sizeof(PqBarriers) + 64;
-}
+constexpr size_t PQ_TC_SMEM = 1024 + 4 * (size_t)B_BYTES + (size_t)NSTAGE * A_STAGE_BYTES + ((size_t)XH_RING * BM + 4 * BN * 4) * sizeof(float) + sizeof(PqBarriers) + 64;
 
-template <bool TRAIN, bool EUCLID, bool FUSE>
+template <bool TRAIN, bool EUCLID>
 __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constant__ CUtensorMap map_b, const PqTcParams Q)
 {
-    static_assert(!FUSE || TRAIN, "cluster sums are gathered by training passes only");
-    constexpr int NSTAGE = stages_for(FUSE);
     extern __shared__ unsigned char smem_raw[];
     const AssignParams &P = Q.a;
     unsigned char *base = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char *b_smem = base;                                           // 4 x 32 KiB
     unsigned char *a_smem = base + 4 * (size_t)B_BYTES;                     // NSTAGE x 16 KiB
     float *xh_ring = reinterpret_cast<float *>(a_smem + (size_t)NSTAGE * A_STAGE_BYTES); // [XH_RING][128]
-    const uint4 *c16_s = reinterpret_cast<const uint4 *>(xh_ring + XH_RING * BM);         // [4][256] binary16 images (encode)
-    float *ssum = xh_ring + XH_RING * BM;                                                 // [4][8][256] cluster sums (FUSE), same place
-    uint32_t *scnt = reinterpret_cast<uint32_t *>(ssum + 4 * SDW * BN);                   // [4][256]
-    PqBarriers *bars = reinterpret_cast<PqBarriers *>(xh_ring + XH_RING * BM + (FUSE ? 4 * BN * (SDW + 1) : 4 * BN * 4));
+    const uint4 *c16_s = reinterpret_cast<const uint4 *>(xh_ring + XH_RING * BM);         // [4][256] binary16 images
+    PqBarriers *bars = reinterpret_cast<PqBarriers *>(xh_ring + XH_RING * BM + 4 * BN * 4);
     volatile int *abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -172,8 +156,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if (FUSE)
-        for (int t = threadIdx.x; t < 4 * BN * (SDW + 1); t += NTHREADS) ssum[t] = 0.0f; // sums and counts (0.0f == 0u)
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -290,14 +272,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
             const bool valid = row < P.n;
             uint32_t old2 = 0;
             if (TRAIN && valid) old2 = *reinterpret_cast<const uint16_t *>(reinterpret_cast<const uint8_t *>(P.codes) + row * (unsigned long long)m + g * 4 + team * 2);
-            // FUSE: this row's slices of the team's two sub-spaces, added to the cluster sums once the codes are known (the
-            // producers read the same bytes a moment ago, so this is an L2 hit, requested a whole unit before it is used)
-            float4 xs[4];
-            if (FUSE && valid) {
-                const float4 *src = reinterpret_cast<const float4 *>(P.x + row * P.ld + (size_t)g * 32 + team * 16);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) xs[i] = __ldg(src + i);
-            }
             int idxs[2] = {0, 0};
             uint32_t marked = 0, done = 0;
 #pragma unroll 1
@@ -437,23 +411,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
                                 }
                             }
                     }
-                    if (FUSE) { // shared-memory sums [sub-space][dimension][code]: the lanes of a warp (different rows) spread over the banks
-#pragma unroll
-                        for (int h = 0; h < 2; ++h)
-                            if ((done >> h & 1u) && !(marked >> h & 1u)) {
-                                float *dst = ssum + (size_t)((team * 2 + h) * SDW) * BN + idxs[h];
-                                const float4 a = xs[2 * h], b = xs[2 * h + 1];
-                                atomicAdd(dst, a.x);
-                                atomicAdd(dst + BN, a.y);
-                                atomicAdd(dst + 2 * BN, a.z);
-                                atomicAdd(dst + 3 * BN, a.w);
-                                atomicAdd(dst + 4 * BN, b.x);
-                                atomicAdd(dst + 5 * BN, b.y);
-                                atomicAdd(dst + 6 * BN, b.z);
-                                atomicAdd(dst + 7 * BN, b.w);
-                                atomicAdd(scnt + (team * 2 + h) * BN + idxs[h], 1u);
-                            }
-                    }
                 } else {
                     const int dim = m * SDW;
 #pragma unroll
@@ -491,20 +448,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) pq_tc_kernel(const __grid_constan
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
-    }
-    if (FUSE) { // the CTA's partial sums join the global ones (clusters this CTA never met are skipped)
-        for (int t = threadIdx.x; t < 4 * BN * SDW; t += NTHREADS) {
-            const int ss = t / (BN * SDW), rem = t % (BN * SDW), j = rem / SDW, d = rem % SDW;
-            if (j < k && scnt[ss * BN + j] != 0u) atomicAdd(Q.sums + ((size_t)(g * 4 + ss) * k + j) * SDW + d, ssum[(size_t)(ss * SDW + d) * BN + j]);
-        }
-        for (int t = threadIdx.x; t < 4 * BN; t += NTHREADS) {
-            const int ss = t / BN, j = t % BN;
-            const uint32_t c = scnt[t];
-            if (j < k && c != 0u) {
-                if (Q.counts_f32) atomicAdd(reinterpret_cast<float *>(Q.counts) + (size_t)(g * 4 + ss) * k + j, (float)c);
-                else atomicAdd(Q.counts + (size_t)(g * 4 + ss) * k + j, c);
-            }
-        }
     }
 }
 
@@ -663,13 +606,6 @@ template <bool TRAIN, bool EUCLID> __global__ void __launch_bounds__(256) pq_mar
                 }
                 d0 = __shfl_sync(0xffffffffu, d0, 0);
                 const int idx = (bi == 0x7fffffff || !(d0 == d0)) ? 0 : bi; // nothing below +inf, or the scan started at a NaN
-                if (TRAIN && Q.sums) { // the tensor kernel left this pair out of its sums
-                    if (lane < SDW) atomicAdd(Q.sums + ((size_t)s * k + idx) * SDW + lane, s_x[i][lane]);
-                    if (lane == SDW) {
-                        if (Q.counts_f32) atomicAdd(reinterpret_cast<float *>(Q.counts) + (size_t)s * k + idx, 1.0f);
-                        else atomicAdd(Q.counts + (size_t)s * k + idx, 1u);
-                    }
-                }
                 if (lane == 0) {
                     bool moved = false;
                     if (TRAIN) {
@@ -710,11 +646,11 @@ size_t pq_tc_scratch_floats() { return SCRATCH_FLOATS; }
 size_t pq_tc_stats_offset_floats() { return OFF_STATS; }
 size_t pq_tc_mark_bytes(size_t n, size_t m) { return (n * (m / 2) + 15) & ~(size_t)15; } // read 16 bytes at a time
 
-template <bool TRAIN, bool EUCLID, bool FUSE>
+template <bool TRAIN, bool EUCLID>
 static void launch_t(CudaDevice &dev, const CUtensorMap &mb, const PqTcParams &q, unsigned grid)
 {
-    auto kernel = pq_tc_kernel<TRAIN, EUCLID, FUSE>;
-    constexpr size_t smem = smem_bytes_for(FUSE);
+    auto kernel = pq_tc_kernel<TRAIN, EUCLID>;
+    constexpr size_t smem = PQ_TC_SMEM;
     static std::atomic<unsigned long long> configured{0}; // bit d: the attribute has been set on device d (it is per device and sticky)
     const unsigned long long bit = 1ull << (dev.device() & 63);
     if (!(configured.load(std::memory_order_relaxed) & bit)) {
@@ -760,17 +696,13 @@ void launch_pq_tc(CudaDevice &dev, const AssignParams &p, int metric, bool train
     q.stats = reinterpret_cast<unsigned long long *>(b.scratch + OFF_STATS);
     q.error = b.error_word;
     q.dbg_scores = b.dbg_scores;
-    q.sums = train ? b.sums : nullptr;
-    q.counts = b.counts;
-    q.counts_f32 = b.counts_f32 ? 1 : 0;
     const unsigned long long tiles = (p.n + BM - 1) / BM;
     const unsigned ngroups = (unsigned)p.m / 4;
     const unsigned per = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>(tiles, (unsigned long long)dev.sm_count() / ngroups));
     const unsigned grid = per * ngroups;
-    if (train && q.sums) launch_t<true, false, true>(dev, mb, q, grid);
-    else if (train) launch_t<true, false, false>(dev, mb, q, grid);
-    else if (metric == M_EUCLID) launch_t<false, true, false>(dev, mb, q, grid);
-    else launch_t<false, false, false>(dev, mb, q, grid);
+    if (train) launch_t<true, false>(dev, mb, q, grid);
+    else if (metric == M_EUCLID) launch_t<false, true>(dev, mb, q, grid);
+    else launch_t<false, false>(dev, mb, q, grid);
 }
 
 // ------------------------------------------------------------------------------------------------

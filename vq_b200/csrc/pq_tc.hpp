@@ -23,10 +23,6 @@ struct PqTcBuffers {
     int *error_word = nullptr;    // set when a bounded wait expires
     bool prepare_operand = true;  // false: scratch already holds operand B of p.centroids (written by launch_pq_update_centroids)
     float *dbg_scores = nullptr;  // optional: n x m x 256 raw scores
-    // training passes only: when sums is set, every row is also added to the sums / counts of its new cluster
-    float *sums = nullptr;
-    uint32_t *counts = nullptr;
-    bool counts_f32 = false;
 };
 void launch_pq_tc(CudaDevice &dev, const AssignParams &p, int metric, bool train, size_t code_bytes, const PqTcBuffers &b);
 // number of (row, sub-space) pairs the tensor kernel has handed to the exact scan so far (first u64 of the statistics)
