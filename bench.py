@@ -219,8 +219,19 @@ def full_size_parity(vq, ctx, dist, rank, world, x_dev, x_host, begin, n_local, 
                   "code_rows": rows, "code_mismatches": mism, "near_ties": near,
                   "codebooks_identical_on_all_ranks": identical, "rows_fitted_by_oracle": int(n_global)}
         cpu = {"value": n_global / ((t1 - t0) + (t2 - t1)) / 1e6, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+               "variant": "tight (contiguous rows, no allocation per distance, one-pass gather)",
                "sample": f"all {n_global} rows, full algorithm (10 LBG iterations + encode), one run",
                "train_s_per_1m_rows": (t1 - t0) * N_ROWS / n_global, "encode_mvec_per_s": n_global / (t2 - t1) / 1e6}
+        if world == 1:  # the same fit with the reference's memory behaviour, on a bounded sample (it is several times slower)
+            fr = 16384
+            sf = LbgSeeder(FIT_SEED)
+            init_f = np.stack([sf.init_indices(i, fr, K) for i in range(M)])
+            tf0 = time.perf_counter()
+            oracle.pq_fit_faithful(x_all[:fr], M, K, ITERS, init_f, sf.draw)
+            tf = time.perf_counter() - tf0
+            cpu["faithful"] = {"variant": "faithful (a heap allocation per row and per distance2, O(n k) gather with cloned members)",
+                               "sample": f"{fr} of {n_global} rows, 10 LBG iterations, scaled per vector",
+                               "train_s_per_1m_rows": tf * N_ROWS / fr}
         return parity, cpu
     except Exception as exc:  # the oracle is only a checker; the bench line survives without it
         return {"error": f"{type(exc).__name__}: {exc}"[:200], "codebooks_identical_on_all_ranks": identical}, None
@@ -432,7 +443,14 @@ def run_secondary(args):
         for _ in range(3):
             (oracle.sq_quantize(0.0, 1.0, 256, q.step, host) if w == "sq" else oracle.bq_quantize(0.0, 0, 1, host))
         cpu = {"value": 3 * host.shape[0] / (time.perf_counter() - t0) / 1e6, "unit": UNIT, "cores": oracle.num_threads(),
-               "kind": "port", "sample": f"{host.shape[0]} rows x 128, 3 passes"}
+               "kind": "port", "variant": "rows in parallel (benches/bench_sq.rs:91-94)", "sample": f"{host.shape[0]} rows x 128, 3 passes"}
+        # the reference's evaluation binary walks the rows in a serial loop (src/bin/eval_sq.rs:45-46): one host thread
+        oracle.lib().vqo_set_num_threads(1)
+        t0 = time.perf_counter()
+        (oracle.sq_quantize(0.0, 1.0, 256, q.step, host) if w == "sq" else oracle.bq_quantize(0.0, 0, 1, host))
+        cpu["serial_outer_loop"] = {"value": host.shape[0] / (time.perf_counter() - t0) / 1e6, "unit": UNIT, "cores": 1,
+                                    "sample": f"{host.shape[0]} rows x 128, 1 pass"}
+        oracle.use_all_host_threads()
         xp = torch.empty((min(rows, 2_000_000), DIM), dtype=torch.float32, pin_memory=True)
         xp.copy_(x[: xp.shape[0]])
         e2e_fn = lambda: q.quantize(xp.numpy())  # noqa: E731

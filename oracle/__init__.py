@@ -184,6 +184,22 @@ def pq_fit(data, m: int, k: int, max_iters: int, init_idx, draw=None):
     return cb, iters
 
 
+def pq_fit_faithful(data, m: int, k: int, max_iters: int, init_idx, draw=None):
+    """vqo_pq_fit with the reference's memory behaviour (a heap allocation per row and per distance2, an O(n k) gather with
+    cloned members): same codebooks, much slower; exists only to be timed as the "faithful" CPU baseline."""
+    data = _f32(data)
+    n, dim = data.shape
+    idx = np.ascontiguousarray(init_idx, dtype=np.uint64)
+    cb = np.zeros((m, k, dim // m), np.float32)
+    L = lib()
+    L.vqo_pq_fit_faithful.restype = C.c_int
+    L.vqo_pq_fit_faithful.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p, DRAW_FN,
+                                      C.c_void_p, C.c_void_p]
+    fn = _draw_cb(draw)
+    _check(L.vqo_pq_fit_faithful(_ptr(data), n, dim, m, k, max_iters, _ptr(idx), fn, None, _ptr(cb)))
+    return cb
+
+
 def pq_quantize(codebooks, x, metric: int = EUCLIDEAN, p: float = 0.0):
     """src/pq.rs:146-187 per row.  Returns (f16 bits n x dim, codes n x m)."""
     cb = _f32(codebooks)

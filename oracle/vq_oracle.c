@@ -400,6 +400,126 @@ int vqo_pq_fit(const float *data, size_t n, size_t dim, size_t m, size_t k, size
     return VQO_OK;
 }
 
+/* ------------------------------------------------------------------------ */
+/* The same fit with the reference's MEMORY BEHAVIOUR, for timing only: the     */
+/* "faithful" CPU baseline.  Results equal vqo_pq_fit's bit for bit.            */
+/*   - every row of a subspace is its own heap allocation (src/pq.rs:110-117   */
+/*     builds a Vec<Vector<f32>> of slices; src/vector.rs:150-152)             */
+/*   - distance2 allocates the difference vector on every call                 */
+/*     (src/vector.rs:214-220 via Sub, 259-265)                                */
+/*   - the gather scans all n assignments once per cluster and clones the      */
+/*     members (src/utils.rs:83-92), then mean_vector (95-99)                  */
+/*   - rayon's decomposition: points for the assignment, clusters for the      */
+/*     gather; subspaces outermost and serial (src/pq.rs:106-121)              */
+/* ------------------------------------------------------------------------ */
+static float distance2_alloc(const float *a, const float *b, size_t d)
+{
+    float *diff = (float *)malloc(sizeof(float) * d); /* the `self - other` temporary */
+    for (size_t i = 0; i < d; ++i) diff[i] = a[i] - b[i];
+    float acc = 0.0f;
+    for (size_t i = 0; i < d; ++i) acc = acc + diff[i] * diff[i];
+    free(diff);
+    return acc;
+}
+
+static int lbg_faithful(float **rows, size_t n, size_t d, size_t k, size_t max_iters, const uint64_t *init_idx,
+                        vqo_draw_fn draw, void *user, size_t stream, float *centroids_out)
+{
+    if (k == 0) return fail(VQO_INVALID_PARAMETER, "Invalid parameter: k must be greater than 0");
+    if (n < k) return fail(VQO_INVALID_PARAMETER, "Invalid parameter: Not enough data points for k clusters");
+    float **cent = (float **)malloc(sizeof(float *) * k);
+    for (size_t j = 0; j < k; ++j) {
+        cent[j] = (float *)malloc(sizeof(float) * d);
+        memcpy(cent[j], rows[init_idx[j]], sizeof(float) * d);
+    }
+    size_t *assign = (size_t *)calloc(n ? n : 1, sizeof(size_t));
+    for (size_t it = 0; it < max_iters; ++it) {
+        int changed = 0;
+#pragma omp parallel for schedule(static) reduction(| : changed)
+        for (size_t i = 0; i < n; ++i) {
+            size_t best = 0;
+            float bd = distance2_alloc(rows[i], cent[0], d);
+            for (size_t j = 1; j < k; ++j) {
+                float dist = distance2_alloc(rows[i], cent[j], d);
+                if (dist < bd) {
+                    bd = dist;
+                    best = j;
+                }
+            }
+            if (best != assign[i]) changed = 1;
+            assign[i] = best;
+        }
+        /* per cluster: scan every assignment, clone the members, mean in data order (serial over j for the draws) */
+        for (size_t j0 = 0; j0 < k; j0 += 64) {
+            size_t j1 = j0 + 64 < k ? j0 + 64 : k;
+            size_t counts[64];
+#pragma omp parallel for schedule(dynamic, 1)
+            for (size_t j = j0; j < j1; ++j) {
+                size_t cnt = 0, cap = 16;
+                float **members = (float **)malloc(sizeof(float *) * cap);
+                for (size_t i = 0; i < n; ++i)
+                    if (assign[i] == j) {
+                        if (cnt == cap) {
+                            cap *= 2;
+                            members = (float **)realloc(members, sizeof(float *) * cap);
+                        }
+                        members[cnt] = (float *)malloc(sizeof(float) * d); /* the clone */
+                        memcpy(members[cnt], rows[i], sizeof(float) * d);
+                        ++cnt;
+                    }
+                if (cnt) {
+                    float *sum = (float *)calloc(d, sizeof(float));
+                    for (size_t t = 0; t < cnt; ++t)
+                        for (size_t c = 0; c < d; ++c) sum[c] = sum[c] + members[t][c];
+                    float len = (float)(double)cnt;
+                    for (size_t c = 0; c < d; ++c) cent[j][c] = sum[c] / len;
+                    free(sum);
+                }
+                for (size_t t = 0; t < cnt; ++t) free(members[t]);
+                free(members);
+                counts[j - j0] = cnt;
+            }
+            for (size_t j = j0; j < j1; ++j)
+                if (counts[j - j0] == 0) {
+                    uint64_t r = draw ? draw(user, stream, (uint64_t)n) : 0;
+                    if (r >= n) r = n - 1;
+                    memcpy(cent[j], rows[r], sizeof(float) * d);
+                }
+        }
+        if (!changed) break;
+    }
+    for (size_t j = 0; j < k; ++j) {
+        memcpy(centroids_out + j * d, cent[j], sizeof(float) * d);
+        free(cent[j]);
+    }
+    free(cent);
+    free(assign);
+    return VQO_OK;
+}
+
+int vqo_pq_fit_faithful(const float *data, size_t n, size_t dim, size_t m, size_t k, size_t max_iters,
+                        const uint64_t *init_idx, vqo_draw_fn draw, void *user, float *codebooks)
+{
+    if (n == 0) return fail(VQO_EMPTY_INPUT, "Empty input: at least one vector is required.");
+    if (m == 0 || dim < m || dim % m != 0) return fail(VQO_INVALID_PARAMETER, "Invalid parameter: bad m");
+    size_t sd = dim / m;
+    float **rows = (float **)malloc(sizeof(float *) * n);
+    for (size_t s = 0; s < m; ++s) {
+        for (size_t i = 0; i < n; ++i) { /* src/pq.rs:110-117: a fresh Vector per row and subspace */
+            rows[i] = (float *)malloc(sizeof(float) * sd);
+            memcpy(rows[i], data + i * dim + s * sd, sizeof(float) * sd);
+        }
+        int rc = lbg_faithful(rows, n, sd, k, max_iters, init_idx + s * k, draw, user, s, codebooks + s * k * sd);
+        for (size_t i = 0; i < n; ++i) free(rows[i]);
+        if (rc) {
+            free(rows);
+            return rc;
+        }
+    }
+    free(rows);
+    return VQO_OK;
+}
+
 /* argmin with the stored metric, strict '<' (src/pq.rs:166-174 and the same  */
 /* loop at rvq.rs:117-124,190-197; opq.rs:154-161,250-257).                   */
 static uint32_t argmin_metric(int metric, double p, const float *x, const float *cb, size_t k,

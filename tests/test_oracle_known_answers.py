@@ -242,3 +242,18 @@ def test_pq_matches_independent_numpy_restatement(oracle):
                     best = j
             assert codes[i, s] == best
             assert np.array_equal(out[i, s * sd:(s + 1) * sd], cb[s, best].astype(np.float16).view(np.uint16))
+
+
+def test_faithful_timing_variant_gives_the_same_codebooks(oracle):
+    """The "faithful" CPU baseline (per-row allocations, an allocation per distance2, O(n k) gather: the reference's memory
+    behaviour, src/pq.rs:110-117, src/vector.rs:214-220,259-265, src/utils.rs:83-92) only differs in speed."""
+    import numpy as np
+    from tests.util import RecordingSeeder
+    from vq_b200 import synth
+    x = synth.uniform01(900, 12, 4)
+    a, b = RecordingSeeder(3), RecordingSeeder(3)
+    init = a.init_pq(900, 3, 20)
+    b.init_pq(900, 3, 20)
+    cb, _ = oracle.pq_fit(x, 3, 20, 7, init, a.draw)
+    cbf = oracle.pq_fit_faithful(x, 3, 20, 7, init, b.draw)
+    assert np.array_equal(cb, cbf)

@@ -104,6 +104,16 @@ class Device {
         (void)n;
         return false;
     }
+    // rot_dev (device, n x n row-major f32) = V U^T of the SVD a = U S V^T (src/opq.rs:180-183), computed on the device from
+    // a_dev (device, n x n row-major f64) as the orthogonal polar factor of a^T.  Returns false when the device does not take
+    // the shape or the iteration did not converge (rank-deficient a); the caller then runs the Jacobi SVD.  Default: false.
+    virtual bool polar_rotation(const double *a_dev, size_t n, float *rot_dev)
+    {
+        (void)a_dev;
+        (void)n;
+        (void)rot_dev;
+        return false;
+    }
     // Nearest centroid under squared Euclidean (src/utils.rs:59-73); codes are read as the previous
     // assignment and overwritten; buf.moved[s] becomes non-zero if any row of subspace s moved (76-80).
     // Subspaces with active[s] == 0 are left untouched.

@@ -923,7 +923,7 @@ __global__ void __launch_bounds__(256) update_centroids_kernel(float *sums, uint
             moved[s] = 0u;
         }
     }
-    status_publish(sp);
+    status_publish(sp, threadIdx.x == 0);
 }
 
 StatusPage CudaDevice::status_page(size_t m, size_t k, uint32_t blocks)

@@ -35,6 +35,7 @@ class CudaDevice : public Device {
 
     void prepare_rows(const Shape &sh, const float *x) override;
     bool svd_sweeps(double *gt, double *vt, size_t n) override;
+    bool polar_rotation(const double *a_dev, size_t n, float *rot_dev) override;
     // Zero-filled map of at least `bytes` bytes for the product-quantizer tensor kernel; its users leave it zero-filled.
     uint8_t *pq_mark_buffer(size_t bytes);
     void patch_centroids(const Shape &sh, const float *x, uint64_t row_begin, const RowPatch *patches, size_t n_patches,

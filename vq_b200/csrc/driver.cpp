@@ -229,6 +229,7 @@ bool opq_fit(Device &dev, Comm *comm, const float *x, size_t n_local, size_t dim
     DevBuf a_d(dev, sizeof(double) * dim * dim), rot_d(dev, sizeof(float) * dim * dim);
     dev.copy(rotated.p, x, bytes); // src/opq.rs:121
     std::vector<double> a(dim * dim), u(dim * dim), sv(dim), v(dim * dim);
+    bool have_v = false; // v holds the previous outer iteration's right singular vectors
     for (size_t it = 0; it < opq_iters; ++it) { // 124
         if (restart) restart(user);             // the reference builds fresh StdRng(seed + i) here (140)
         lbg_fit(dev, comm, sh, rotated.as<float>(), max_iters, init_idx, draw, user, 0, flags, codebooks, nullptr);
@@ -237,18 +238,25 @@ bool opq_fit(Device &dev, Comm *comm, const float *x, size_t n_local, size_t dim
         dev.pq_encode(sh, rotated.as<float>(), codebooks, metric, p, nullptr, nullptr, rec.as<float>()); // 146-168
         dev.cross_cov(rec.as<float>(), rotated.as<float>(), n_local, dim, a_d.as<double>());            // 172-179
         if (multi) comm->allreduce_sum_f64(a_d.as<double>(), dim * dim);
-        dev.download(a.data(), a_d.p, sizeof(double) * dim * dim);
-        // The rotation moves little from one outer iteration to the next, so the sweeps start from the previous V: G = A V
-        // then has nearly orthogonal columns and two or three sweeps suffice.  V U^T (the orthogonal polar factor of A^T)
-        // does not depend on where the sweeps start.
-        jacobi_svd(a.data(), dim, u.data(), sv.data(), v.data(), &dev, it > 0 ? v.data() : nullptr); // 180-182
-        for (size_t i = 0; i < dim; ++i)                          // rotation = V * U^T (183)
-            for (size_t j = 0; j < dim; ++j) {
-                double acc = 0.0;
-                for (size_t t = 0; t < dim; ++t) acc += v[i * dim + t] * u[j * dim + t];
-                rotation_host[i * dim + j] = (float)acc;
-            }
-        dev.upload(rot_d.p, rotation_host, sizeof(float) * dim * dim);
+        // 180-183: rotation = V U^T.  On the device as the polar factor of A^T when that converges (full-rank A), else the SVD.
+        if (dev.polar_rotation(a_d.as<double>(), dim, rot_d.as<float>())) {
+            dev.download(rotation_host, rot_d.p, sizeof(float) * dim * dim);
+            have_v = false;
+        } else {
+            dev.download(a.data(), a_d.p, sizeof(double) * dim * dim);
+            // The rotation moves little from one outer iteration to the next, so the sweeps start from the previous V: G = A V
+            // then has nearly orthogonal columns and two or three sweeps suffice.  V U^T (the orthogonal polar factor of A^T)
+            // does not depend on where the sweeps start.
+            jacobi_svd(a.data(), dim, u.data(), sv.data(), v.data(), &dev, have_v ? v.data() : nullptr); // 180-182
+            have_v = true;
+            for (size_t i = 0; i < dim; ++i)                          // rotation = V * U^T (183)
+                for (size_t j = 0; j < dim; ++j) {
+                    double acc = 0.0;
+                    for (size_t t = 0; t < dim; ++t) acc += v[i * dim + t] * u[j * dim + t];
+                    rotation_host[i * dim + j] = (float)acc;
+                }
+            dev.upload(rot_d.p, rotation_host, sizeof(float) * dim * dim);
+        }
         dev.rotate_rows(rot_d.as<float>(), dim, x, n_local, rotated.as<float>()); // 186-194, from the ORIGINAL rows
     }
     return true;

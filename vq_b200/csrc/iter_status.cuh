@@ -26,12 +26,15 @@ struct StatusPage {
 };
 
 #ifdef __CUDACC__
-// Every thread of every CTA calls this after its writes to the page.  The last CTA to arrive publishes the sequence number.
-__device__ __forceinline__ void status_publish(const StatusPage &sp)
+// Every thread of every CTA calls this at the end of the kernel; `wrote` = this thread stored something into the page.  Only
+// those threads pay for a system-scope fence (the others may have a hundred bytes of ordinary global stores in flight, which
+// the next kernel on the stream sees anyway).  The last CTA to arrive publishes the sequence number.
+__device__ __forceinline__ void status_publish(const StatusPage &sp, bool wrote)
 {
-    __threadfence_system(); // this thread's page writes are visible to the host before anything that follows
+    if (wrote) __threadfence_system(); // this thread's page writes are visible to the host before anything that follows
     __syncthreads();
     if (threadIdx.x == 0 && threadIdx.y == 0) {
+        __threadfence_system(); // orders what the barrier made visible to this thread before the arrival below
         if (atomicAdd(sp.done_counter, 1u) == sp.total_blocks - 1u) {
             *sp.done_counter = 0u; // the next launch on the stream starts from zero again
             sp.host_words[1] = sp.tc_error ? (uint32_t)*sp.tc_error : 0u;

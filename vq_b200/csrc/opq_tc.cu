@@ -43,7 +43,11 @@ constexpr int NST = 3;                     // stage ring depth
 constexpr int NTHREADS = 320;
 constexpr uint32_t TILE_BYTES = 128 * 128; // one 128 x 32-float operand tile
 constexpr int XC_ROWS = 32;                // rows (K) per cross_cov stage
-constexpr int XC_FLUSH_STAGES = 128;       // cross_cov: the f32 accumulator is added to the f64 result every 4096 rows
+constexpr int XC_NST = 2;                  // cross_cov stage ring depth (a stage is 64 KiB)
+// The tensor core adds into its f32 accumulator with truncation, not round-to-nearest: over 1536 accumulator updates (4096 rows)
+// the sums came out 1.5e-5 low.  So the accumulator is drained every 4 stages (128 rows, 48 updates, bias below 1.5e-6) into an
+// f32 partial sum in shared memory with ordinary rounded additions, and that sum joins the f64 result once per CTA.
+constexpr int XC_FLUSH_STAGES = 4;
 
 struct alignas(8) OpqBarriers {
     unsigned long long afull[NST], aempty[NST], bfull, tfull[2], tempty[2];
@@ -297,7 +301,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) opq_cross_cov_kernel(const CrossP
     constexpr uint32_t OPER_BYTES = 4 * XC_ROWS * 128; // 16 KiB
     constexpr uint32_t STAGE_BYTES = 4 * OPER_BYTES;   // 64 KiB
     unsigned char *s_smem = base;
-    OpqBarriers *bars = reinterpret_cast<OpqBarriers *>(s_smem + (size_t)NST * STAGE_BYTES);
+    float *part = reinterpret_cast<float *>(s_smem + (size_t)XC_NST * STAGE_BYTES); // [128 columns j][128 rows i]: this CTA's partial A
+    OpqBarriers *bars = reinterpret_cast<OpqBarriers *>(part + 128 * 128);
     volatile int *abort_flag = &bars->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int dim = P.dim, kchunks = P.kchunks;
@@ -307,7 +312,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) opq_cross_cov_kernel(const CrossP
     const unsigned long long blk_end = min(n_blocks, blk_begin + per_cta);
     const unsigned long long my_blocks = blk_end - blk_begin;
 
-    for (uint32_t t = threadIdx.x; t < NST * STAGE_BYTES / 16; t += NTHREADS) reinterpret_cast<uint4 *>(s_smem)[t] = make_uint4(0, 0, 0, 0);
+    for (uint32_t t = threadIdx.x; t < (XC_NST * STAGE_BYTES + 128 * 128 * 4) / 16; t += NTHREADS) reinterpret_cast<uint4 *>(s_smem)[t] = make_uint4(0, 0, 0, 0);
     common_setup(bars, warp, 256u);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // the zero fill is visible to the MMA's reads
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -328,8 +333,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) opq_cross_cov_kernel(const CrossP
                     if (!mbar_wait(&bars->tempty[b], (buse & 1u) ^ 1u, abort_flag, P.error, 31)) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 }
-                const int st = it % NST;
-                if (!mbar_wait(&bars->afull[st], (it / NST) & 1u, abort_flag, P.error, 32)) break;
+                const int st = it % XC_NST;
+                if (!mbar_wait(&bars->afull[st], (it / XC_NST) & 1u, abort_flag, P.error, 32)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + b * 128u;
                 const uint32_t sbase = smem_u32(s_smem + (size_t)st * STAGE_BYTES);
@@ -370,8 +375,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) opq_cross_cov_kernel(const CrossP
 #pragma unroll
             for (int i = 0; i < 8; ++i) cy[i] = ny[i], cx[i] = nx[i];
             fetch(ny, nx, blk_begin + j + 1);
-            const int st = it % NST;
-            if (!mbar_wait(&bars->aempty[st], ((it / NST) & 1u) ^ 1u, abort_flag, P.error, 33)) break;
+            const int st = it % XC_NST;
+            if (!mbar_wait(&bars->aempty[st], ((it / XC_NST) & 1u) ^ 1u, abort_flag, P.error, 33)) break;
             unsigned char *sb = s_smem + (size_t)st * STAGE_BYTES;
             if (lane_in) {
 #pragma unroll
@@ -405,15 +410,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) opq_cross_cov_kernel(const CrossP
             for (int cb = 0; cb < kchunks; ++cb) {
                 tmem_ld32_issue(taddr + cb * 32, ra);
                 tmem_wait();
-                if (i < dim) {
 #pragma unroll
-                    for (int t = 0; t < 32; ++t) atomicAdd(P.a + (size_t)i * dim + cb * 32 + t, (double)__uint_as_float(ra[t]));
+                for (int t = 0; t < 32; ++t) { // only this thread ever touches row i of the partial sum
+                    float *pp = part + (size_t)(cb * 32 + t) * 128 + i;
+                    *pp = __fadd_rn(*pp, __uint_as_float(ra[t]));
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->tempty[b]);
         }
+        if (i < dim && my_blocks > 0 && !*abort_flag)
+            for (int j = 0; j < dim; ++j) atomicAdd(P.a + (size_t)i * dim + j, (double)part[(size_t)j * 128 + i]);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -482,7 +490,7 @@ void launch_opq_cross_cov(CudaDevice &dev, const float *y, const float *x, size_
     p.kchunks = (int)(dim / CHUNK);
     p.a = a;
     p.error = error_word;
-    const size_t smem = 1024 + (size_t)NST * 4 * 4 * XC_ROWS * 128 + sizeof(OpqBarriers) + 64;
+    const size_t smem = 1024 + (size_t)XC_NST * 4 * 4 * XC_ROWS * 128 + 128 * 128 * sizeof(float) + sizeof(OpqBarriers) + 64;
     static std::atomic<unsigned long long> configured{0};
     set_smem_once(opq_cross_cov_kernel, smem, dev.device(), configured);
     const unsigned long long blocks = (n + XC_ROWS - 1) / XC_ROWS;

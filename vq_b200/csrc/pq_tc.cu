@@ -785,7 +785,7 @@ __global__ void __launch_bounds__(BN) pq_update_centroids_kernel(float *sums, ui
         sp.host_moved()[s] = act ? moved[s] : 0u;
         moved[s] = 0u;
     }
-    status_publish(sp);
+    status_publish(sp, (j & 31) == 0);
 }
 
 void launch_pq_update_centroids(CudaDevice &dev, int m, int k, float *sums, uint32_t *counts, uint32_t *moved, bool counts_f32,

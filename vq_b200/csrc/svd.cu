@@ -7,6 +7,7 @@
 // __syncthreads.  The sweeps end when no pair rotated (|g_p . g_q| <= 1e-15 |g_p| |g_q| for all pairs) or after 60 sweeps;
 // singular values, U and the completion of a rank-deficient U are computed by the caller from the converged G.
 #include <algorithm>
+#include <cstring>
 
 #include "cuda_device.hpp"
 
@@ -120,6 +121,138 @@ bool CudaDevice::svd_sweeps(double *gt, double *vt, size_t n)
     download(vt, v_d, bytes);
     release(g_d), release(v_d), release(sw_d);
     return true;
+}
+
+} // namespace vqb
+
+// ------------------------------------------------------------------------------------------------
+// The rotation without the SVD.  src/opq.rs:180-183 takes A = U S V^T and sets R = V U^T.  Since A^T = (V U^T)(U S U^T), that R
+// is the orthogonal polar factor of A^T, which is unique when A has full rank and does not depend on how an SVD orders or signs
+// its vectors.  The Newton-Schulz iteration
+//        X_0 = A^T / |A|_F,      X_{k+1} = X_k (1.5 I - 0.5 X_k^T X_k)
+// drives every singular value of X (all in (0, 1] at the start) to 1 and leaves the singular vectors alone, so it converges to
+// that factor: linearly (x 1.5 per step) while a singular value is small, then quadratically.  All of it is 128 x 128 x 128 f64
+// products on the device: no download of A, no sweeps on one SM.  The residual max|X^T X - I| is kept on the device; once it is
+// below 1e-13 the remaining launches copy X through.  If it has not converged after the fixed number of steps (rank-deficient or
+// extremely ill-conditioned A) the caller falls back to the Jacobi SVD, which also completes a null space.
+// ------------------------------------------------------------------------------------------------
+namespace vqb {
+
+namespace {
+
+constexpr int POLAR_TILE = 16;
+constexpr double POLAR_TOL = 1e-13;
+
+__global__ void polar_fro_kernel(const double *a, int count, double *fro2)
+{
+    __shared__ double red[256];
+    double acc = 0.0;
+    for (int t = threadIdx.x; t < count; t += 256) acc += a[t] * a[t];
+    red[threadIdx.x] = acc;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if ((int)threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *fro2 = red[0];
+}
+
+// x[i][j] = a[j][i] / |a|_F
+__global__ void polar_init_kernel(const double *a, int n, const double *fro2, double *x)
+{
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n * n) return;
+    const int i = t / n, j = t % n;
+    const double f = sqrt(*fro2);
+    x[t] = f > 0.0 ? a[(size_t)j * n + i] / f : 0.0;
+}
+
+// b = x^T x, and *resid = max |b - I| (bits of a non-negative double, so an integer max orders them)
+__global__ void __launch_bounds__(POLAR_TILE *POLAR_TILE) polar_gram_kernel(const double *x, int n, double *b, unsigned long long *resid)
+{
+    __shared__ double xa[POLAR_TILE][POLAR_TILE + 1], xb[POLAR_TILE][POLAR_TILE + 1];
+    const int tx = threadIdx.x % POLAR_TILE, ty = threadIdx.x / POLAR_TILE;
+    const int i = blockIdx.y * POLAR_TILE + ty, j = blockIdx.x * POLAR_TILE + tx; // b[i][j] = sum_r x[r][i] x[r][j]
+    double acc = 0.0;
+    for (int r0 = 0; r0 < n; r0 += POLAR_TILE) {
+        xa[ty][tx] = x[(size_t)(r0 + ty) * n + blockIdx.y * POLAR_TILE + tx]; // rows r0.., columns of the i block
+        xb[ty][tx] = x[(size_t)(r0 + ty) * n + blockIdx.x * POLAR_TILE + tx]; // rows r0.., columns of the j block
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < POLAR_TILE; ++r) acc = fma(xa[r][ty], xb[r][tx], acc);
+        __syncthreads();
+    }
+    b[(size_t)i * n + j] = acc;
+    const double dev = fabs(acc - (i == j ? 1.0 : 0.0));
+    atomicMax(resid, (unsigned long long)__double_as_longlong(dev == dev ? dev : 1e300));
+}
+
+// y = 1.5 x - 0.5 x b    (y = x once the residual of this step's b is below the tolerance)
+__global__ void __launch_bounds__(POLAR_TILE *POLAR_TILE) polar_update_kernel(const double *x, const double *b, int n, const unsigned long long *resid, double *y)
+{
+    __shared__ double xs[POLAR_TILE][POLAR_TILE + 1], bs[POLAR_TILE][POLAR_TILE + 1];
+    const int tx = threadIdx.x % POLAR_TILE, ty = threadIdx.x / POLAR_TILE;
+    const int i = blockIdx.y * POLAR_TILE + ty, j = blockIdx.x * POLAR_TILE + tx;
+    if (__longlong_as_double((long long)*resid) < POLAR_TOL) {
+        y[(size_t)i * n + j] = x[(size_t)i * n + j];
+        return;
+    }
+    double acc = 0.0;
+    for (int r0 = 0; r0 < n; r0 += POLAR_TILE) {
+        xs[ty][tx] = x[(size_t)i * n + r0 + tx];
+        bs[ty][tx] = b[(size_t)(r0 + ty) * n + j];
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < POLAR_TILE; ++r) acc = fma(xs[ty][r], bs[r][tx], acc);
+        __syncthreads();
+    }
+    y[(size_t)i * n + j] = 1.5 * x[(size_t)i * n + j] - 0.5 * acc;
+}
+
+__global__ void polar_finish_kernel(const double *x, int count, float *rot)
+{
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < count) rot[t] = (float)x[t];
+}
+
+} // namespace
+
+bool CudaDevice::polar_rotation(const double *a_dev, size_t n, float *rot_dev)
+{
+    if (n == 0 || n % POLAR_TILE != 0 || n > 512) return false;
+    const size_t bytes = sizeof(double) * n * n;
+    double *x0 = static_cast<double *>(alloc(bytes)), *x1 = static_cast<double *>(alloc(bytes)), *b = static_cast<double *>(alloc(bytes));
+    double *fro2 = static_cast<double *>(alloc(sizeof(double)));
+    unsigned long long *resid = static_cast<unsigned long long *>(alloc(sizeof(unsigned long long) * 2));
+    const int count = (int)(n * n);
+    const dim3 grid((unsigned)(n / POLAR_TILE), (unsigned)(n / POLAR_TILE));
+    const int steps = 80; // x 1.5 per step: singular values down to 1e-13 of the largest still reach 1
+    double *cur = x0, *nxt = x1;
+    {
+        KernelScope ks(*this, "polar_rotation");
+        polar_fro_kernel<<<1, 256, 0, stream_>>>(a_dev, count, fro2);
+        polar_init_kernel<<<(count + 255) / 256, 256, 0, stream_>>>(a_dev, (int)n, fro2, cur);
+        count_launch(2);
+        for (int s = 0; s < steps; ++s) {
+            VQB_CUDA_CHECK(cudaMemsetAsync(resid, 0, sizeof(unsigned long long), stream_));
+            polar_gram_kernel<<<grid, POLAR_TILE * POLAR_TILE, 0, stream_>>>(cur, (int)n, b, resid);
+            polar_update_kernel<<<grid, POLAR_TILE * POLAR_TILE, 0, stream_>>>(cur, b, (int)n, resid, nxt);
+            count_launch(2);
+            std::swap(cur, nxt);
+        }
+        // the residual of the final iterate
+        VQB_CUDA_CHECK(cudaMemsetAsync(resid, 0, sizeof(unsigned long long), stream_));
+        polar_gram_kernel<<<grid, POLAR_TILE * POLAR_TILE, 0, stream_>>>(cur, (int)n, b, resid);
+        polar_finish_kernel<<<(count + 255) / 256, 256, 0, stream_>>>(cur, count, rot_dev);
+        count_launch(2);
+        VQB_CUDA_CHECK(cudaGetLastError());
+    }
+    unsigned long long bits = 0;
+    download(&bits, resid, sizeof bits);
+    double r;
+    std::memcpy(&r, &bits, sizeof r);
+    release(x0), release(x1), release(b), release(fro2), release(resid);
+    return r < 1e-11;
 }
 
 } // namespace vqb

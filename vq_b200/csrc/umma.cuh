@@ -41,6 +41,9 @@ __device__ __forceinline__ bool mbar_wait(void *bar, uint32_t parity, volatile i
                      : "r"(addr), "r"(parity), "r"(VQB_WAIT_HINT_NS)
                      : "memory");
         if (done) return true;
+#ifdef VQB_WAIT_SLEEP_NS
+        __nanosleep(VQB_WAIT_SLEEP_NS);
+#endif
         if ((i & 1023u) == 1023u && *abort_flag) return false;
     }
     *abort_flag = 1;
