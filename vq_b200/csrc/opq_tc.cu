@@ -21,8 +21,9 @@
 // MMA thread.  One persistent CTA per SM:
 //   warp 0      operand B by TMA (rotate only)
 //   warp 1      owns tensor memory (two accumulators) and issues the MMAs
-//   warps 2-5   converters
-//   warps 6-9   epilogue: tcgen05.ld, one accumulator row per lane; rotate writes Y, cross_cov adds its partial sum to the f64 result
+//   warps 2-9   converters (three stages of global loads in flight per thread)
+//   warps 10-13 epilogue: tcgen05.ld, one accumulator row per lane; rotate writes Y through a shared-memory transposition (whole
+//               128-byte row pieces per store), cross_cov adds the accumulator to an f32 partial sum and, at the end, to the f64 result
 // Every wait is bounded; on expiry the CTA records a code, stops issuing, frees tensor memory and the host raises an error.
 #include <algorithm>
 #include <atomic>
@@ -39,11 +40,13 @@ namespace {
 
 constexpr int BM = 128;                    // rows per rotate tile = accumulator lanes
 constexpr int CHUNK = 32;                  // f32 per 128-byte swizzle row
-constexpr int NST = 3;                     // stage ring depth
-constexpr int NTHREADS = 320;
+constexpr int NST = 2;                     // stage ring depth (rotate: hi + lo tile of one K chunk; cross_cov: four operand tiles)
+constexpr int NCONV = 8;                   // converter warps
+constexpr int PF = 3;                      // stages of global loads a converter thread keeps in flight (registers)
+constexpr int NTHREADS = 32 * (2 + NCONV + 4);
+constexpr uint32_t STAGE_ROW_BYTES = 144;  // epilogue staging: 32 floats of a row + 16 bytes, so that rows start in different banks
 constexpr uint32_t TILE_BYTES = 128 * 128; // one 128 x 32-float operand tile
 constexpr int XC_ROWS = 32;                // rows (K) per cross_cov stage
-constexpr int XC_NST = 2;                  // cross_cov stage ring depth (a stage is 64 KiB)
 // The tensor core adds into its f32 accumulator with truncation, not round-to-nearest: over 1536 accumulator updates (4096 rows)
 // the sums came out 1.5e-5 low.  So the accumulator is drained every 4 stages (128 rows, 48 updates, bias below 1.5e-6) into an
 // f32 partial sum in shared memory with ordinary rounded additions, and that sum joins the f64 result once per CTA.
@@ -97,7 +100,7 @@ __device__ __forceinline__ void common_setup(OpqBarriers *bars, int warp, uint32
 {
     if (threadIdx.x == 0) {
         for (int s = 0; s < NST; ++s) {
-            mbar_init(&bars->afull[s], 4);
+            mbar_init(&bars->afull[s], NCONV);
             mbar_init(&bars->aempty[s], 1);
         }
         mbar_init(&bars->bfull, 1);
@@ -136,7 +139,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) opq_rotate_kernel(const __grid_co
     unsigned char *bh_smem = base;                                 // kchunks x b_chunk
     unsigned char *bl_smem = base + (size_t)kchunks * b_chunk;     // kchunks x b_chunk
     unsigned char *a_smem = base + 2 * (size_t)kchunks * b_chunk;  // NST x (hi 16 KiB + lo 16 KiB)
-    OpqBarriers *bars = reinterpret_cast<OpqBarriers *>(a_smem + (size_t)NST * 2 * TILE_BYTES);
+    unsigned char *o_smem = a_smem + (size_t)NST * 2 * TILE_BYTES; // 4 epilogue warps x 32 rows x 144 bytes: output staging
+    OpqBarriers *bars = reinterpret_cast<OpqBarriers *>(o_smem + 4 * 32 * STAGE_ROW_BYTES);
     volatile int *abort_flag = &bars->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const unsigned long long n_tiles = (P.n + BM - 1) / BM;
@@ -189,42 +193,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) opq_rotate_kernel(const __grid_co
                 if (ok) umma_commit(&bars->tfull[b]);
             }
         }
-    } else if (warp < 6) {
-        // converters: 8 lanes per row (16 bytes each), 4 rows per warp instruction, rows cw*32 .. cw*32+31 of the tile per warp
+    } else if (warp < 2 + NCONV) {
+        // converters: 8 lanes per row (16 bytes each), 4 rows per warp instruction, rows cw*16 .. cw*16+15 of the tile per warp.
+        // Stage g of this CTA is K chunk g % kchunks of its tile g / kchunks.  A thread keeps PF stages of loads in flight: with
+        // one stage the kernel ran at the pace of one DRAM round trip per stage.
         const int cw = warp - 2, sub = lane >> 3, e16 = lane & 7;
-        uint32_t it = 0;
-        float4 cur[8], nxt[8];
-        auto fetch = [&](float4(&dst)[8], unsigned long long tile, int kc) {
+        const unsigned long long my_tiles = (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+        const unsigned long long total = my_tiles * (unsigned long long)kchunks;
+        auto fetch = [&](float4(&dst)[4], unsigned long long gidx) {
+            const unsigned long long tile = blockIdx.x + (gidx / kchunks) * gridDim.x;
+            const int kc = (int)(gidx % kchunks);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int r = cw * 32 + i * 4 + sub;
+            for (int i = 0; i < 4; ++i) {
+                const int r = cw * 16 + i * 4 + sub;
                 const unsigned long long row = tile * BM + r;
-                dst[i] = (tile < n_tiles && row < P.n) ? __ldg(reinterpret_cast<const float4 *>(P.x + row * dim + kc * CHUNK) + e16)
-                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+                dst[i] = (gidx < total && row < P.n) ? __ldg(reinterpret_cast<const float4 *>(P.x + row * dim + kc * CHUNK) + e16)
+                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         };
-        unsigned long long tile = blockIdx.x;
-        int kc = 0;
-        if (tile < n_tiles) fetch(nxt, tile, 0);
-        bool ok = true;
-        while (ok && tile < n_tiles && !*abort_flag) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
-            unsigned long long ntile = tile;
-            int nkc = kc + 1;
-            if (nkc == kchunks) {
-                nkc = 0;
-                ntile = tile + gridDim.x;
-            }
-            fetch(nxt, ntile, nkc);
+        auto convert = [&](const float4(&src)[4], unsigned long long gidx) -> bool {
+            const uint32_t it = (uint32_t)gidx;
             const int st = it % NST;
-            if (!mbar_wait(&bars->aempty[st], ((it / NST) & 1u) ^ 1u, abort_flag, P.error, 25)) break;
+            if (!mbar_wait(&bars->aempty[st], ((it / NST) & 1u) ^ 1u, abort_flag, P.error, 25)) return false;
             unsigned char *hi_t = a_smem + (size_t)st * 2 * TILE_BYTES, *lo_t = hi_t + TILE_BYTES;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int r = cw * 32 + i * 4 + sub;
+            for (int i = 0; i < 4; ++i) {
+                const int r = cw * 16 + i * 4 + sub;
                 float4 h, l;
-                split4(cur[i], h, l);
+                split4(src[i], h, l);
                 const uint32_t off = (uint32_t)r * 128u + (uint32_t)((e16 ^ (r & 7)) << 4);
                 *reinterpret_cast<float4 *>(hi_t + off) = h;
                 *reinterpret_cast<float4 *>(lo_t + off) = l;
@@ -232,30 +228,54 @@ __global__ void __launch_bounds__(NTHREADS, 1) opq_rotate_kernel(const __grid_co
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->afull[st]);
-            ++it;
-            tile = ntile;
-            kc = nkc;
+            return true;
+        };
+        float4 p0[4], p1[4], p2[4];
+        static_assert(PF == 3, "the ring below is written out for three stages");
+        fetch(p0, 0);
+        fetch(p1, 1);
+        fetch(p2, 2);
+        for (unsigned long long gidx = 0; gidx < total && !*abort_flag; gidx += PF) {
+            if (!convert(p0, gidx)) break;
+            fetch(p0, gidx + 3);
+            if (gidx + 1 < total) {
+                if (!convert(p1, gidx + 1)) break;
+                fetch(p1, gidx + 4);
+            }
+            if (gidx + 2 < total) {
+                if (!convert(p2, gidx + 2)) break;
+                fetch(p2, gidx + 5);
+            }
         }
     } else {
-        // epilogue: one row per lane, 32 outputs (128 bytes) per tensor-memory load
+        // epilogue: one accumulator row per lane, 32 outputs per tensor-memory load; the 32 x 32 block goes through shared memory
+        // so that a store instruction writes four 128-byte row pieces instead of 32 scattered 16-byte pieces
         const int q = warp & 3;
+        unsigned char *stg = o_smem + (size_t)q * 32 * STAGE_ROW_BYTES;
+        const int rsub = lane >> 3, unit = lane & 7;
         uint32_t local = 0;
         for (unsigned long long tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x, ++local) {
             const uint32_t b = local & 1u, buse = local >> 1;
             if (!mbar_wait(&bars->tfull[b], buse & 1u, abort_flag, P.error, 26)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const unsigned long long row = tile * BM + 32ull * q + lane;
+            const unsigned long long row_base = tile * BM + 32ull * q;
             const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + b * 128u;
             uint32_t ra[32];
             for (int cb = 0; cb < kchunks; ++cb) {
                 tmem_ld32_issue(taddr + cb * 32, ra);
                 tmem_wait();
-                if (row < P.n) {
-                    float4 *o = reinterpret_cast<float4 *>(P.y + row * dim + cb * 32);
+                float4 *mine = reinterpret_cast<float4 *>(stg + (size_t)lane * STAGE_ROW_BYTES);
 #pragma unroll
-                    for (int t = 0; t < 8; ++t)
-                        o[t] = make_float4(__uint_as_float(ra[4 * t]), __uint_as_float(ra[4 * t + 1]), __uint_as_float(ra[4 * t + 2]), __uint_as_float(ra[4 * t + 3]));
+                for (int t = 0; t < 8; ++t)
+                    mine[t] = make_float4(__uint_as_float(ra[4 * t]), __uint_as_float(ra[4 * t + 1]), __uint_as_float(ra[4 * t + 2]), __uint_as_float(ra[4 * t + 3]));
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int r = i * 4 + rsub;
+                    const float4 v = *reinterpret_cast<const float4 *>(stg + (size_t)r * STAGE_ROW_BYTES + unit * 16);
+                    if (row_base + r < P.n) *reinterpret_cast<float4 *>(P.y + (row_base + r) * dim + cb * 32 + unit * 4) = v;
                 }
+                __syncwarp();
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -301,7 +321,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) opq_cross_cov_kernel(const CrossP
     constexpr uint32_t OPER_BYTES = 4 * XC_ROWS * 128; // 16 KiB
     constexpr uint32_t STAGE_BYTES = 4 * OPER_BYTES;   // 64 KiB
     unsigned char *s_smem = base;
-    float *part = reinterpret_cast<float *>(s_smem + (size_t)XC_NST * STAGE_BYTES); // [128 columns j][128 rows i]: this CTA's partial A
+    float *part = reinterpret_cast<float *>(s_smem + (size_t)NST * STAGE_BYTES); // [128 columns j][128 rows i]: this CTA's partial A
     OpqBarriers *bars = reinterpret_cast<OpqBarriers *>(part + 128 * 128);
     volatile int *abort_flag = &bars->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -312,7 +332,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) opq_cross_cov_kernel(const CrossP
     const unsigned long long blk_end = min(n_blocks, blk_begin + per_cta);
     const unsigned long long my_blocks = blk_end - blk_begin;
 
-    for (uint32_t t = threadIdx.x; t < (XC_NST * STAGE_BYTES + 128 * 128 * 4) / 16; t += NTHREADS) reinterpret_cast<uint4 *>(s_smem)[t] = make_uint4(0, 0, 0, 0);
+    for (uint32_t t = threadIdx.x; t < (NST * STAGE_BYTES + 128 * 128 * 4) / 16; t += NTHREADS) reinterpret_cast<uint4 *>(s_smem)[t] = make_uint4(0, 0, 0, 0);
     common_setup(bars, warp, 256u);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // the zero fill is visible to the MMA's reads
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -333,8 +353,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) opq_cross_cov_kernel(const CrossP
                     if (!mbar_wait(&bars->tempty[b], (buse & 1u) ^ 1u, abort_flag, P.error, 31)) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 }
-                const int st = it % XC_NST;
-                if (!mbar_wait(&bars->afull[st], (it / XC_NST) & 1u, abort_flag, P.error, 32)) break;
+                const int st = it % NST;
+                if (!mbar_wait(&bars->afull[st], (it / NST) & 1u, abort_flag, P.error, 32)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + b * 128u;
                 const uint32_t sbase = smem_u32(s_smem + (size_t)st * STAGE_BYTES);
@@ -354,40 +374,38 @@ __global__ void __launch_bounds__(NTHREADS, 1) opq_cross_cov_kernel(const CrossP
                 }
             }
         }
-    } else if (warp >= 2 && warp < 6) {
-        // converters: a warp instruction reads one whole row (lane l = floats 4l .. 4l+3); warp cw takes rows cw, cw+4, ... of the stage
+    } else if (warp >= 2 && warp < 2 + NCONV) {
+        // converters: a warp instruction reads one whole row (lane l = floats 4l .. 4l+3); warp cw takes rows cw, cw+8, ... of the
+        // stage; PF stages of loads in flight per thread
         const int cw = warp - 2;
         const int c = lane >> 3, e16 = lane & 7; // column chunk and 16-byte unit of this lane's float4
         const bool lane_in = lane * 4 < dim;
-        float4 cy[8], cx[8], ny[8], nx[8];
-        auto fetch = [&](float4(&dy)[8], float4(&dx)[8], unsigned long long blk) {
+        constexpr int RPW = XC_ROWS / NCONV; // rows of a stage per warp
+        auto fetch = [&](float4(&dy)[RPW], float4(&dx)[RPW], unsigned long long j) {
+            const unsigned long long blk = blk_begin + j;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const unsigned long long row = blk * XC_ROWS + (unsigned long long)(cw + 4 * i);
+            for (int i = 0; i < RPW; ++i) {
+                const unsigned long long row = blk * XC_ROWS + (unsigned long long)(cw + NCONV * i);
                 const bool in = lane_in && blk < blk_end && row < P.n;
                 dy[i] = in ? __ldg(reinterpret_cast<const float4 *>(P.y + row * dim) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
                 dx[i] = in ? __ldg(reinterpret_cast<const float4 *>(P.x + row * dim) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         };
-        if (my_blocks > 0) fetch(ny, nx, blk_begin);
-        for (unsigned long long j = 0; j < my_blocks && !*abort_flag; ++j) {
+        auto convert = [&](const float4(&sy)[RPW], const float4(&sx)[RPW], unsigned long long j) -> bool {
             const uint32_t it = (uint32_t)j;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) cy[i] = ny[i], cx[i] = nx[i];
-            fetch(ny, nx, blk_begin + j + 1);
-            const int st = it % XC_NST;
-            if (!mbar_wait(&bars->aempty[st], ((it / XC_NST) & 1u) ^ 1u, abort_flag, P.error, 33)) break;
+            const int st = it % NST;
+            if (!mbar_wait(&bars->aempty[st], ((it / NST) & 1u) ^ 1u, abort_flag, P.error, 33)) return false;
             unsigned char *sb = s_smem + (size_t)st * STAGE_BYTES;
             if (lane_in) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int r = cw + 4 * i;
+                for (int i = 0; i < RPW; ++i) {
+                    const int r = cw + NCONV * i;
                     const uint32_t off = (uint32_t)c * (XC_ROWS * 128u) + (uint32_t)r * 128u + mn_swizzle_unit(e16, r);
                     float4 h, l;
-                    split4(cy[i], h, l);
+                    split4(sy[i], h, l);
                     *reinterpret_cast<float4 *>(sb + off) = h;
                     *reinterpret_cast<float4 *>(sb + OPER_BYTES + off) = l;
-                    split4(cx[i], h, l);
+                    split4(sx[i], h, l);
                     *reinterpret_cast<float4 *>(sb + 2 * OPER_BYTES + off) = h;
                     *reinterpret_cast<float4 *>(sb + 3 * OPER_BYTES + off) = l;
                 }
@@ -395,8 +413,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) opq_cross_cov_kernel(const CrossP
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->afull[st]);
+            return true;
+        };
+        float4 y0[RPW], x0[RPW], y1[RPW], x1[RPW], y2[RPW], x2[RPW];
+        fetch(y0, x0, 0);
+        fetch(y1, x1, 1);
+        fetch(y2, x2, 2);
+        for (unsigned long long j = 0; j < my_blocks && !*abort_flag; j += PF) {
+            if (!convert(y0, x0, j)) break;
+            fetch(y0, x0, j + 3);
+            if (j + 1 < my_blocks) {
+                if (!convert(y1, x1, j + 1)) break;
+                fetch(y1, x1, j + 4);
+            }
+            if (j + 2 < my_blocks) {
+                if (!convert(y2, x2, j + 2)) break;
+                fetch(y2, x2, j + 5);
+            }
         }
-    } else if (warp >= 6) {
+    } else if (warp >= 2 + NCONV) {
         // epilogue: lane = dimension i of Y, columns = dimensions j of X
         const int q = warp & 3;
         const unsigned long long n_flush = (my_blocks + XC_FLUSH_STAGES - 1) / XC_FLUSH_STAGES;
@@ -469,9 +504,10 @@ void launch_opq_rotate(CudaDevice &dev, const float *rot, size_t dim, const floa
     p.dim = (int)dim;
     p.kchunks = (int)(dim / CHUNK);
     p.error = error_word;
-    const size_t smem = 1024 + 2 * (size_t)p.kchunks * dim * 128 + (size_t)NST * 2 * TILE_BYTES + sizeof(OpqBarriers) + 64;
+    const size_t fixed = (size_t)NST * 2 * TILE_BYTES + 4 * 32 * STAGE_ROW_BYTES + sizeof(OpqBarriers) + 64;
+    const size_t smem = 1024 + 2 * (size_t)p.kchunks * dim * 128 + fixed;
     static std::atomic<unsigned long long> configured{0};
-    set_smem_once(opq_rotate_kernel, 1024 + 2 * (size_t)4 * 128 * 128 + (size_t)NST * 2 * TILE_BYTES + sizeof(OpqBarriers) + 64, dev.device(), configured);
+    set_smem_once(opq_rotate_kernel, 1024 + 2 * (size_t)4 * 128 * 128 + fixed, dev.device(), configured);
     const unsigned long long tiles = (n + BM - 1) / BM;
     const unsigned grid = (unsigned)std::min<unsigned long long>(tiles, (unsigned long long)dev.sm_count());
     KernelScope ks(dev, "rotate_rows");
@@ -490,7 +526,7 @@ void launch_opq_cross_cov(CudaDevice &dev, const float *y, const float *x, size_
     p.kchunks = (int)(dim / CHUNK);
     p.a = a;
     p.error = error_word;
-    const size_t smem = 1024 + (size_t)XC_NST * 4 * 4 * XC_ROWS * 128 + 128 * 128 * sizeof(float) + sizeof(OpqBarriers) + 64;
+    const size_t smem = 1024 + (size_t)NST * 4 * 4 * XC_ROWS * 128 + 128 * 128 * sizeof(float) + sizeof(OpqBarriers) + 64;
     static std::atomic<unsigned long long> configured{0};
     set_smem_once(opq_cross_cov_kernel, smem, dev.device(), configured);
     const unsigned long long blocks = (n + XC_ROWS - 1) / XC_ROWS;

@@ -85,6 +85,17 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
     for (unsigned long long tile = (unsigned long long)blockIdx.x * W + warp; tile < tiles; tile += (unsigned long long)gridDim.x * W) {
         const unsigned long long row0 = tile * 32, row = row0 + lane;
         const bool valid = row < P.n;
+        if (lane == 0) {
+            // A warp has one tile of loads in flight (16 KiB at dim 128), far too little to cover the latency of DRAM at four
+            // warps per SM; the tile it will take two turns from now is asked into the L2 cache here, whole rows, no registers.
+            const unsigned long long nt = tile + 2ull * gridDim.x * W;
+            if (nt < tiles) {
+                const unsigned long long r0 = nt * 32, rows = min(32ull, P.n - r0);
+                const uint32_t bytes = (uint32_t)(rows * dim * sizeof(float));
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(P.x + r0 * dim), "r"(bytes) : "memory");
+                if (MODE == R_RVQ_STAGE) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(P.qsum + r0 * dim), "r"(bytes) : "memory");
+            }
+        }
         bool skip = false;
         if (MODE == R_RVQ_STAGE && valid) skip = P.done[row] != 0;
         // stage the 32 rows: lanes walk along a row (coalesced), stored dimension-major

@@ -129,12 +129,12 @@ bool CudaDevice::svd_sweeps(double *gt, double *vt, size_t n)
 // The rotation without the SVD.  src/opq.rs:180-183 takes A = U S V^T and sets R = V U^T.  Since A^T = (V U^T)(U S U^T), that R
 // is the orthogonal polar factor of A^T, which is unique when A has full rank and does not depend on how an SVD orders or signs
 // its vectors.  The Newton-Schulz iteration
-//        X_0 = A^T / |A|_F,      X_{k+1} = X_k (1.5 I - 0.5 X_k^T X_k)
+//        X_0 = A^T / sqrt(|A|_1 |A|_inf),      X_{k+1} = X_k (1.5 I - 0.5 X_k^T X_k)
 // drives every singular value of X (all in (0, 1] at the start) to 1 and leaves the singular vectors alone, so it converges to
 // that factor: linearly (x 1.5 per step) while a singular value is small, then quadratically.  All of it is 128 x 128 x 128 f64
-// products on the device: no download of A, no sweeps on one SM.  The residual max|X^T X - I| is kept on the device; once it is
-// below 1e-13 the remaining launches copy X through.  If it has not converged after the fixed number of steps (rank-deficient or
-// extremely ill-conditioned A) the caller falls back to the Jacobi SVD, which also completes a null space.
+// products on the device: no download of A, no sweeps on one SM.  The residual max|X^T X - I| is kept on the device and read by the
+// host after every eighth step; within a batch, steps after convergence copy X through.  If it has not converged after 96 steps
+// (rank-deficient or extremely ill-conditioned A) the caller falls back to the Jacobi SVD, which also completes a null space.
 // ------------------------------------------------------------------------------------------------
 namespace vqb {
 
@@ -143,28 +143,46 @@ namespace {
 constexpr int POLAR_TILE = 16;
 constexpr double POLAR_TOL = 1e-13;
 
-__global__ void polar_fro_kernel(const double *a, int count, double *fro2)
+// scale^2 = |a|_1 |a|_inf (largest column sum times largest row sum of |a|), an upper bound of the largest singular value squared
+// that is within a small factor of it
+__global__ void polar_scale_kernel(const double *a, int n, double *scale2)
 {
     __shared__ double red[256];
-    double acc = 0.0;
-    for (int t = threadIdx.x; t < count; t += 256) acc += a[t] * a[t];
-    red[threadIdx.x] = acc;
+    double best_row = 0.0, best_col = 0.0;
+    for (int t = threadIdx.x; t < n; t += 256) {
+        double r = 0.0, c = 0.0;
+        for (int u = 0; u < n; ++u) {
+            r += fabs(a[(size_t)t * n + u]);
+            c += fabs(a[(size_t)u * n + t]);
+        }
+        best_row = fmax(best_row, r);
+        best_col = fmax(best_col, c);
+    }
+    red[threadIdx.x] = best_row;
     __syncthreads();
     for (int o = 128; o > 0; o >>= 1) {
-        if ((int)threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+        if ((int)threadIdx.x < o) red[threadIdx.x] = fmax(red[threadIdx.x], red[threadIdx.x + o]);
         __syncthreads();
     }
-    if (threadIdx.x == 0) *fro2 = red[0];
+    const double rmax = red[0];
+    __syncthreads();
+    red[threadIdx.x] = best_col;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if ((int)threadIdx.x < o) red[threadIdx.x] = fmax(red[threadIdx.x], red[threadIdx.x + o]);
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *scale2 = rmax * red[0];
 }
 
-// x[i][j] = a[j][i] / |a|_F
-__global__ void polar_init_kernel(const double *a, int n, const double *fro2, double *x)
+// x[i][j] = a[j][i] / sqrt(scale2)
+__global__ void polar_init_kernel(const double *a, int n, const double *scale2, double *x)
 {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= n * n) return;
     const int i = t / n, j = t % n;
-    const double f = sqrt(*fro2);
-    x[t] = f > 0.0 ? a[(size_t)j * n + i] / f : 0.0;
+    const double f = sqrt(*scale2);
+    x[t] = (f > 0.0 && f == f) ? a[(size_t)j * n + i] / f : 0.0;
 }
 
 // b = x^T x, and *resid = max |b - I| (bits of a non-negative double, so an integer max orders them)
@@ -226,31 +244,34 @@ bool CudaDevice::polar_rotation(const double *a_dev, size_t n, float *rot_dev)
     unsigned long long *resid = static_cast<unsigned long long *>(alloc(sizeof(unsigned long long) * 2));
     const int count = (int)(n * n);
     const dim3 grid((unsigned)(n / POLAR_TILE), (unsigned)(n / POLAR_TILE));
-    const int steps = 80; // x 1.5 per step: singular values down to 1e-13 of the largest still reach 1
+    const int max_steps = 96, batch = 8; // x 1.5 per step while a singular value is small: down to 1e-16 of the largest
     double *cur = x0, *nxt = x1;
+    double r = 1.0;
     {
         KernelScope ks(*this, "polar_rotation");
-        polar_fro_kernel<<<1, 256, 0, stream_>>>(a_dev, count, fro2);
+        polar_scale_kernel<<<1, 256, 0, stream_>>>(a_dev, (int)n, fro2);
         polar_init_kernel<<<(count + 255) / 256, 256, 0, stream_>>>(a_dev, (int)n, fro2, cur);
         count_launch(2);
-        for (int s = 0; s < steps; ++s) {
+        for (int s0 = 0; s0 < max_steps && !(r < 1e-11); s0 += batch) {
+            for (int s = 0; s < batch; ++s) {
+                VQB_CUDA_CHECK(cudaMemsetAsync(resid, 0, sizeof(unsigned long long), stream_));
+                polar_gram_kernel<<<grid, POLAR_TILE * POLAR_TILE, 0, stream_>>>(cur, (int)n, b, resid);
+                polar_update_kernel<<<grid, POLAR_TILE * POLAR_TILE, 0, stream_>>>(cur, b, (int)n, resid, nxt);
+                count_launch(2);
+                std::swap(cur, nxt);
+            }
+            // the residual of the current iterate; the host looks at it once per batch of steps
             VQB_CUDA_CHECK(cudaMemsetAsync(resid, 0, sizeof(unsigned long long), stream_));
             polar_gram_kernel<<<grid, POLAR_TILE * POLAR_TILE, 0, stream_>>>(cur, (int)n, b, resid);
-            polar_update_kernel<<<grid, POLAR_TILE * POLAR_TILE, 0, stream_>>>(cur, b, (int)n, resid, nxt);
-            count_launch(2);
-            std::swap(cur, nxt);
+            count_launch();
+            unsigned long long bits = 0;
+            download(&bits, resid, sizeof bits);
+            std::memcpy(&r, &bits, sizeof r);
         }
-        // the residual of the final iterate
-        VQB_CUDA_CHECK(cudaMemsetAsync(resid, 0, sizeof(unsigned long long), stream_));
-        polar_gram_kernel<<<grid, POLAR_TILE * POLAR_TILE, 0, stream_>>>(cur, (int)n, b, resid);
         polar_finish_kernel<<<(count + 255) / 256, 256, 0, stream_>>>(cur, count, rot_dev);
-        count_launch(2);
+        count_launch();
         VQB_CUDA_CHECK(cudaGetLastError());
     }
-    unsigned long long bits = 0;
-    download(&bits, resid, sizeof bits);
-    double r;
-    std::memcpy(&r, &bits, sizeof r);
     release(x0), release(x1), release(b), release(fro2), release(resid);
     return r < 1e-11;
 }
