@@ -5,6 +5,7 @@
 
 #include <algorithm>
 #include <chrono>
+#include <cstdio>
 #include <cstring>
 #include <vector>
 
@@ -434,7 +435,15 @@ void CudaDevice::assign_train(const Shape &sh, const float *x, const float *cent
     if (prepared_x_ == x && prepared_n_ == sh.n_local && prepared_dim_ == sh.sd && sh.m == 1 &&
         dense_tc_applicable(sh.n_local, sh.sd, sh.k, M_SQ, x)) {
         // full-width k-means step: tensor-core shortlist, then the exact decision among the candidates
-        dense_shortlist(*this, x, sh.n_local, sh.sd, centroids, sh.k, rownorm_, hn_scratch_, cand_, nullptr, tc_error_, nullptr);
+        static const bool stats_on = std::getenv("VQB_TC_STATS") != nullptr; // diagnostic: shortlist sizes per training pass on stderr
+        if (stats_on) VQB_CUDA_CHECK(cudaMemsetAsync(tc_stats_, 0, 3 * sizeof(unsigned long long), stream_));
+        dense_shortlist(*this, x, sh.n_local, sh.sd, centroids, sh.k, rownorm_, hn_scratch_, cand_, stats_on ? tc_stats_ : nullptr, tc_error_, nullptr);
+        if (stats_on) {
+            unsigned long long st3[3] = {0, 0, 0};
+            download(st3, tc_stats_, sizeof st3);
+            std::fprintf(stderr, "[vqb] shortlist: rows %llu candidates %llu (%.2f per row) full scans %llu\n", st3[0], st3[1],
+                         st3[0] ? (double)st3[1] / (double)st3[0] : 0.0, st3[2]);
+        }
         ResolveParams r = {};
         r.x = x;
         r.n = sh.n_local;

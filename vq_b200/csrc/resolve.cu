@@ -22,14 +22,25 @@ namespace {
 __device__ __forceinline__ void exact_dist4(const float *xcol, const float *c0, const float *c1, const float *c2, const float *c3,
                                             int dim, bool euclid, float (&out)[4])
 {
+    // dim is a multiple of 32 on this path.  Eight dimensions per trip: their 40 shared-memory loads are issued together, so the
+    // serial chains below wait for shared memory once per eight steps instead of once per step (one warp per scheduler cannot
+    // hide that latency any other way).
     float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
-    for (int i = 0; i < dim; ++i) {
-        const float xv = xcol[i * XS_STRIDE];
-        const float d0 = __fsub_rn(xv, c0[i]), d1 = __fsub_rn(xv, c1[i]), d2 = __fsub_rn(xv, c2[i]), d3 = __fsub_rn(xv, c3[i]);
-        a0 = __fadd_rn(a0, __fmul_rn(d0, d0));
-        a1 = __fadd_rn(a1, __fmul_rn(d1, d1));
-        a2 = __fadd_rn(a2, __fmul_rn(d2, d2));
-        a3 = __fadd_rn(a3, __fmul_rn(d3, d3));
+    for (int i0 = 0; i0 < dim; i0 += 8) {
+        float xv[8], v0[8], v1[8], v2[8], v3[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            xv[u] = xcol[(i0 + u) * XS_STRIDE];
+            v0[u] = c0[i0 + u], v1[u] = c1[i0 + u], v2[u] = c2[i0 + u], v3[u] = c3[i0 + u];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float d0 = __fsub_rn(xv[u], v0[u]), d1 = __fsub_rn(xv[u], v1[u]), d2 = __fsub_rn(xv[u], v2[u]), d3 = __fsub_rn(xv[u], v3[u]);
+            a0 = __fadd_rn(a0, __fmul_rn(d0, d0));
+            a1 = __fadd_rn(a1, __fmul_rn(d1, d1));
+            a2 = __fadd_rn(a2, __fmul_rn(d2, d2));
+            a3 = __fadd_rn(a3, __fmul_rn(d3, d3));
+        }
     }
     out[0] = euclid ? __fsqrt_rn(a0) : a0;
     out[1] = euclid ? __fsqrt_rn(a1) : a1;
@@ -82,45 +93,36 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
     bool moved = false;
     double warp_norm = 0.0;
 
+    // A warp's next tile (32 rows, up to 16 KiB) is requested into registers while the current one is worked on: with only the
+    // current tile's loads in flight and four warps per SM the kernel ran at the pace of the memory latency.
+    const int dim4 = dim / 4, total4 = 32 * dim4;
+    float4 pre[32];
+    auto request = [&](unsigned long long tile) {
+        const unsigned long long r0 = tile * 32;
+#pragma unroll
+        for (int u = 0; u < 32; ++u) {
+            const int idx = u * 32 + lane;
+            const unsigned long long rr = r0 + idx / dim4;
+            pre[u] = (tile < tiles && idx < total4 && rr < P.n) ? __ldg(reinterpret_cast<const float4 *>(P.x + rr * dim) + idx % dim4)
+                                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    request((unsigned long long)blockIdx.x * W + warp);
     for (unsigned long long tile = (unsigned long long)blockIdx.x * W + warp; tile < tiles; tile += (unsigned long long)gridDim.x * W) {
         const unsigned long long row0 = tile * 32, row = row0 + lane;
         const bool valid = row < P.n;
-        if (lane == 0) {
-            // A warp has one tile of loads in flight (16 KiB at dim 128), far too little to cover the latency of DRAM at four
-            // warps per SM; the tile it will take two turns from now is asked into the L2 cache here, whole rows, no registers.
-            const unsigned long long nt = tile + 2ull * gridDim.x * W;
-            if (nt < tiles) {
-                const unsigned long long r0 = nt * 32, rows = min(32ull, P.n - r0);
-                const uint32_t bytes = (uint32_t)(rows * dim * sizeof(float));
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(P.x + r0 * dim), "r"(bytes) : "memory");
-                if (MODE == R_RVQ_STAGE) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(P.qsum + r0 * dim), "r"(bytes) : "memory");
-            }
-        }
         bool skip = false;
         if (MODE == R_RVQ_STAGE && valid) skip = P.done[row] != 0;
-        // stage the 32 rows: lanes walk along a row (coalesced), stored dimension-major
-        // (eight independent 128-bit loads per lane are issued before any is stored, to cover the memory latency)
-        {
-            const int dim4 = dim / 4, total4 = 32 * dim4;
-            for (int base = 0; base < total4; base += 8 * 32) {
-                float4 v[8];
+        // stage the 32 rows dimension-major (lanes walked along a row when they were loaded: coalesced), then ask for the next tile
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int idx = base + u * 32 + lane;
-                    const unsigned long long rr = row0 + idx / dim4;
-                    v[u] = (idx < total4 && rr < P.n) ? __ldg(reinterpret_cast<const float4 *>(P.x + rr * dim) + idx % dim4)
-                                                      : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int idx = base + u * 32 + lane;
-                    if (idx < total4) {
-                        float *d = xs + (size_t)(idx % dim4) * 4 * XS_STRIDE + idx / dim4;
-                        d[0] = v[u].x, d[XS_STRIDE] = v[u].y, d[2 * XS_STRIDE] = v[u].z, d[3 * XS_STRIDE] = v[u].w;
-                    }
-                }
+        for (int u = 0; u < 32; ++u) {
+            const int idx = u * 32 + lane;
+            if (idx < total4) {
+                float *d = xs + (size_t)(idx % dim4) * 4 * XS_STRIDE + idx / dim4;
+                d[0] = pre[u].x, d[XS_STRIDE] = pre[u].y, d[2 * XS_STRIDE] = pre[u].z, d[3 * XS_STRIDE] = pre[u].w;
             }
         }
+        request(tile + (unsigned long long)gridDim.x * W);
         __syncwarp();
         const float *xcol = xs + lane;
         int best = 0;
@@ -147,6 +149,7 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
             for (int j = lane; j < k; j += 32) {
                 const float *c = cpad + (size_t)j * cstride;
                 float acc = 0.0f;
+#pragma unroll 8
                 for (int i = 0; i < dim; ++i) {
                     const float d = __fsub_rn(xr[i * XS_STRIDE], c[i]);
                     acc = __fadd_rn(acc, __fmul_rn(d, d));
@@ -209,6 +212,7 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
             } else {
                 const float *cw = cpad + (size_t)best * cstride;
                 float nsq = 0.0f;
+#pragma unroll 8
                 for (int i = 0; i < dim; ++i) {
                     const float r = __fsub_rn(xs[i * XS_STRIDE + lane], cw[i]);
                     xs[i * XS_STRIDE + lane] = r;
@@ -338,29 +342,33 @@ template <typename CodeT> __global__ void __launch_bounds__(128, 1) resolve_trai
             cnt += __popc(bal);
         }
         __syncwarp();
-        // ---- pass B: 32 listed rows at a time
+        // ---- pass B: 32 listed rows at a time; the next group's rows are requested into registers while this one is evaluated
+        const int dim4 = dim / 4;
+        float4 pre[32];
+        auto request = [&](int i0) {
+            const int nb = min(32, cnt - i0), total4 = nb * dim4;
+#pragma unroll
+            for (int u = 0; u < 32; ++u) {
+                const int idx = u * 32 + lane;
+                pre[u] = (i0 < cnt && idx < total4) ? __ldg(reinterpret_cast<const float4 *>(P.x + (base + list[i0 + idx / dim4]) * dim) + idx % dim4)
+                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        };
+        if (cnt > 0) request(0);
         for (int i0 = 0; i0 < cnt; i0 += 32) {
             const int nb = min(32, cnt - i0);
             {
-                const int dim4 = dim / 4, total4 = nb * dim4;
-                for (int b0 = 0; b0 < total4; b0 += 8 * 32) {
-                    float4 v[8];
+                const int total4 = nb * dim4;
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const int idx = b0 + u * 32 + lane;
-                        v[u] = (idx < total4) ? __ldg(reinterpret_cast<const float4 *>(P.x + (base + list[i0 + idx / dim4]) * dim) + idx % dim4)
-                                              : make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const int idx = b0 + u * 32 + lane;
-                        if (idx < total4) {
-                            float *d = xs + (size_t)(idx % dim4) * 4 * XS_STRIDE + idx / dim4;
-                            d[0] = v[u].x, d[XS_STRIDE] = v[u].y, d[2 * XS_STRIDE] = v[u].z, d[3 * XS_STRIDE] = v[u].w;
-                        }
+                for (int u = 0; u < 32; ++u) {
+                    const int idx = u * 32 + lane;
+                    if (idx < total4) {
+                        float *d = xs + (size_t)(idx % dim4) * 4 * XS_STRIDE + idx / dim4;
+                        d[0] = pre[u].x, d[XS_STRIDE] = pre[u].y, d[2 * XS_STRIDE] = pre[u].z, d[3 * XS_STRIDE] = pre[u].w;
                     }
                 }
             }
+            request(i0 + 32);
             __syncwarp();
             const bool valid = lane < nb;
             const unsigned long long row = valid ? base + list[i0 + lane] : 0ull;
@@ -385,6 +393,7 @@ template <typename CodeT> __global__ void __launch_bounds__(128, 1) resolve_trai
                 for (int j = lane; j < k; j += 32) {
                     const float *c = cpad + (size_t)j * cstride;
                     float acc = 0.0f;
+#pragma unroll 8
                     for (int i = 0; i < dim; ++i) {
                         const float d = __fsub_rn(xr[i * XS_STRIDE], c[i]);
                         acc = __fadd_rn(acc, __fmul_rn(d, d));
