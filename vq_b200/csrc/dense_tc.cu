@@ -16,11 +16,13 @@
 //
 // Kernel layout (one CTA per SM, persistent over 128-row tiles):
 //   warp 0      TMA producer: the codebook once (k x dim, resident in shared memory), then row tiles in 128-byte
-//               column chunks through a 3-stage ring (cp.async.bulk.tensor, 128B swizzle, no multicast)
+//               column chunks through a 5-stage ring (cp.async.bulk.tensor, 128B swizzle, no multicast)
 //   warp 1      allocates tensor memory and issues tcgen05.mma M128 x N256 x K8 (kind::tf32); two 256-column
-//               accumulators so the next tile's MMAs overlap this tile's epilogue
-//   warps 2..5  epilogue: tcgen05.ld the 128 x 256 dots, one row per lane; pass 1 finds the two smallest S, pass 2
-//               collects the shortlist
+//               accumulators so the next tile's MMAs overlap this tile's epilogue.  One more K = 8 step per tile multiplies
+//               a constant (1, 1, 0, ...) row operand with (-hn_h, -hn_l, 0, ...) per centroid, so the accumulator holds
+//               D = x.c - |c|^2/2 = -S and the epilogue never touches the half norms
+//   warps 2..5  epilogue: tcgen05.ld the 128 x 256 values, one row per lane; pass 1 finds the largest D (3-input max), pass 2
+//               shifts the sign of (D - limit) into a 256-bit candidate mask
 // Every wait is bounded; on expiry the kernel records an error code, stops issuing work and frees its tensor memory.
 #include <cuda.h>
 
