@@ -87,7 +87,9 @@ def test_oracle_rejects_empty_and_nan():
 # ---------------------------------------------------------------------------------------------- device
 @pytest.mark.gpu
 @pytest.mark.parametrize("n,dim,depth,seed", [(1, 3, 5, 0), (2, 4, 0, 1), (50, 6, 3, 2), (333, 10, 6, 3), (1000, 10, 3, 4), (257, 5, 12, 5),
-                                              (5000, 128, 10, 6), (70000, 33, 8, 7)])
+                                              (5000, 128, 10, 6), (70000, 33, 8, 7),
+                                              # widths in whole 128-byte pieces take the streaming statistics kernel: stage edges, tails
+                                              (64, 32, 2, 8), (65, 32, 3, 9), (1537, 96, 4, 10), (100000, 64, 9, 11), (200001, 128, 6, 12)])
 def test_device_tree_and_lookup_equal_the_oracle(n, dim, depth, seed):
     import vq_b200 as vq
 

@@ -15,11 +15,13 @@
 #include <cub/device/device_scan.cuh>
 
 #include <algorithm>
+#include <cstdlib>
 #include <vector>
 
 #include "cuda_device.hpp"
 #include "kernels_common.cuh"
 #include "tsvq.hpp"
+#include "umma.cuh"
 
 namespace vqb {
 
@@ -94,6 +96,217 @@ __global__ void __launch_bounds__(32) node_stats_kernel(const float *x, size_t d
                 var = __fadd_rn(var, __fmul_rn(d, d));
             });
             spread[(size_t)blockIdx.x * dim + t] = var;
+        }
+    }
+}
+
+// Streaming variant of node_stats_kernel for rows whose 32-column pieces are whole 128-byte lines (dim a multiple of 32,
+// 16-byte aligned base).  The sums stay one serial f32 chain per (node, dimension) in data order -- four cycles per row at
+// best -- so the kernel's job is to keep that chain fed: one CTA per (node, 32 dimensions); warp 0 is the consumer (lane =
+// dimension) and does nothing but read stages from shared memory and add; eleven producer warps gather the node's rows
+// (128-bit loads, 64 rows per warp in flight, the next stage's row numbers requested meanwhile) into a ring of 64-row
+// stages.  In the second pass the producers already store (v - c)^2, each term rounded like the reference's
+// (src/tsvq.rs:86-98), so the consumer's work per row is a quarter of a shared-memory load and one addition in both passes.
+//
+// A stage is stored dimension-major, [32 dimensions][64 rows], so that the consumer fetches four consecutive rows of its
+// dimension with one 128-bit load; the 16 four-row groups of a dimension are permuted by ns_swizzle(d), which keeps both
+// the producers' 32-bit stores and the consumer's 128-bit loads free of bank conflicts.
+//
+// Hand-over.  A poll of an mbarrier costs the consumer 230 cycles even when the phase is complete (the instruction that
+// reads the poll's predicate stalls the warp until the answer is back), as much as the 64 additions of a stage.  So the
+// producers announce finished stages with a shared-memory counter per group of four stages, which the consumer reads
+// with an ordinary load one group ahead -- the load is in flight during the additions and is looked at three stages
+// later -- and the consumer hands a group back with one relaxed arrive.  Stage numbers are padded to a multiple of four
+// per pass (padding stages are announced without data) so that every group sees exactly four announcements.
+constexpr int NS_STAGE_ROWS = 64, NS_GROUP = 4, NS_GROUPS = 6, NS_RING = NS_GROUP * NS_GROUPS, NS_PRODUCERS = 11, NS_THREADS = 32 * (1 + NS_PRODUCERS);
+constexpr int NS_STAGE_BYTES = NS_STAGE_ROWS * 128;
+constexpr int NS_SMEM = NS_RING * NS_STAGE_BYTES + 32 * 4 + (NS_GROUPS + 1) * 8 + NS_GROUPS * 4;
+// a producer may wait for the release of a group only when the release before that one has certainly happened (a parity
+// wait cannot tell two phases apart); the same warp filled a stage NS_PRODUCERS stages earlier, so this holds while
+// NS_PRODUCERS <= NS_RING - NS_GROUP
+static_assert(NS_PRODUCERS <= NS_RING - NS_GROUP, "parity waits need the producers' lead to stay inside the ring");
+constexpr int NS_ERR_WAIT = 190;
+constexpr uint32_t NS_SPIN_LIMIT = 1u << 28;
+
+__device__ __forceinline__ int ns_swizzle(int d) { return ((d & 7) ^ (d >> 3)) & 7; }
+
+__global__ void __launch_bounds__(NS_THREADS) node_stats_stream_kernel(const float *__restrict__ x, size_t dim, const uint32_t *__restrict__ perm,
+                                                                       const NodeInfo *nodes, int first, float *centroids, float *spread, int *error)
+{
+    extern __shared__ __align__(128) unsigned char ns_smem[];
+    float *ring = reinterpret_cast<float *>(ns_smem);
+    float *c_sh = reinterpret_cast<float *>(ns_smem + NS_RING * NS_STAGE_BYTES); // read in 16-byte pieces: keep it aligned
+    uint64_t *empty = reinterpret_cast<uint64_t *>(c_sh + 32);
+    uint64_t *cbar = empty + NS_GROUPS;
+    volatile uint32_t *filled = reinterpret_cast<volatile uint32_t *>(cbar + 1);
+    __shared__ int abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int node = first + blockIdx.x;
+    const NodeInfo nd = nodes[node];
+    const size_t col0 = (size_t)blockIdx.y * 32;
+    const unsigned long long count = nd.count;
+    const uint32_t S = (uint32_t)((count + NS_STAGE_ROWS - 1) / NS_STAGE_ROWS);      // stages with rows, per pass
+    const uint32_t S4 = (S + NS_GROUP - 1) / NS_GROUP * NS_GROUP;                      // stage numbers per pass
+    const uint32_t total = nd.split ? 2 * S4 : S4;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NS_GROUPS; ++i) mbar_init(&empty[i], 1), filled[i] = 0;
+        mbar_init(cbar, 1);
+        abort_flag = 0;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        float4 a[16], b[16];
+        float acc = 0.0f;
+        bool ok = true;
+        uint32_t ahead = 0; // filled[] of the group after the current one, as read at the start of the current group
+        const int g = ns_swizzle(lane);
+        auto group_ready = [&](uint32_t grp, uint32_t have) { // all four stages of group `grp` announced?
+            const uint32_t need = NS_GROUP * (grp / NS_GROUPS + 1);
+            if (have < need) {
+                uint32_t i = 0;
+                while (filled[grp % NS_GROUPS] < need) {
+                    if (++i >= NS_SPIN_LIMIT || ((i & 4095u) == 0 && *(volatile int *)&abort_flag)) {
+                        if (i >= NS_SPIN_LIMIT) abort_flag = 1, atomicCAS(error, 0, NS_ERR_WAIT);
+                        ok = false;
+                        return;
+                    }
+                }
+            }
+            __threadfence_block(); // the stages' values are read after their announcement
+        };
+        auto request = [&](uint32_t s, float4(&buf)[16]) {
+            const float *src = ring + (size_t)(s % NS_RING) * (NS_STAGE_BYTES / 4) + lane * NS_STAGE_ROWS;
+#pragma unroll
+            for (int q = 0; q < 16; ++q) buf[q] = *reinterpret_cast<const float4 *>(src + ((q ^ g) << 2));
+        };
+        // cur holds stage s = base + sb (sb < S)
+        auto step = [&](float4(&cur)[16], float4(&nxt)[16], uint32_t base, uint32_t sb) {
+            const uint32_t s = base + sb;
+            if (sb + 1 < S) {
+                if (((s + 1) & (NS_GROUP - 1)) == 0) {
+                    group_ready((s + 1) / NS_GROUP, ahead);
+                    if (!ok) return;
+                }
+                request(s + 1, nxt);
+            }
+            if ((s & (NS_GROUP - 1)) == 0) ahead = filled[(s / NS_GROUP + 1) % NS_GROUPS];
+            const unsigned long long left = count - (unsigned long long)sb * NS_STAGE_ROWS;
+            if (left >= (unsigned long long)NS_STAGE_ROWS) {
+#pragma unroll
+                for (int q = 0; q < 16; ++q) {
+                    acc = __fadd_rn(acc, cur[q].x), acc = __fadd_rn(acc, cur[q].y);
+                    acc = __fadd_rn(acc, cur[q].z), acc = __fadd_rn(acc, cur[q].w);
+                }
+            } else {
+                const int rows_here = (int)left;
+#pragma unroll
+                for (int q = 0; q < 16; ++q) {
+                    if (4 * q + 0 < rows_here) acc = __fadd_rn(acc, cur[q].x);
+                    if (4 * q + 1 < rows_here) acc = __fadd_rn(acc, cur[q].y);
+                    if (4 * q + 2 < rows_here) acc = __fadd_rn(acc, cur[q].z);
+                    if (4 * q + 3 < rows_here) acc = __fadd_rn(acc, cur[q].w);
+                }
+            }
+            if ((s & (NS_GROUP - 1)) == NS_GROUP - 1 || sb + 1 == S) { // the group's last stage with rows: hand the group back
+                __syncwarp();                                           // every lane has used its values
+                if (lane == 0) mbar_arrive_relaxed(&empty[(s / NS_GROUP) % NS_GROUPS]);
+            }
+        };
+        for (uint32_t pass = 0; pass * S4 < total && ok; ++pass) {
+            const uint32_t base = pass * S4;
+            acc = 0.0f;
+            group_ready(base / NS_GROUP, 0);
+            if (!ok) break;
+            request(base, a);
+            for (uint32_t sb = 0; sb < S && ok; sb += 2) {
+                step(a, b, base, sb);
+                if (sb + 1 < S && ok) step(b, a, base, sb + 1);
+            }
+            if (!ok) break;
+            if (pass == 0) {
+                const float c = __fdiv_rn(acc, __ull2float_rn(count)); // sum / (len as f32)
+                centroids[(size_t)node * dim + col0 + lane] = c;
+                if (nd.split) {
+                    c_sh[lane] = c;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(cbar);
+                }
+            } else {
+                spread[(size_t)blockIdx.x * dim + col0 + lane] = acc;
+            }
+        }
+    } else {
+        const uint32_t *rows = perm + nd.start;
+        const int sub = lane >> 3, piece = lane & 7;
+        const float *xcol = x + col0 + piece * 4;
+        // this lane's four dimensions 4 * piece + j: offset of (dimension, four-row group 0, position sub) in a stage
+        int off[4], gj[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) gj[j] = ns_swizzle(4 * piece + j), off[j] = (4 * piece + j) * NS_STAGE_ROWS + sub;
+        uint32_t idx[16];
+        auto load_idx = [&](uint32_t s) { // stage numbers past the pass's rows give no rows at all
+            const unsigned long long r0 = (unsigned long long)(s % S4) * NS_STAGE_ROWS + sub;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const unsigned long long r = r0 + 4 * i;
+                idx[i] = r < count ? rows[r] : DEAD;
+            }
+        };
+        uint32_t s = warp - 1;
+        if (s < total) load_idx(s);
+        bool have_c = false;
+        float4 cc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (; s < total; s += NS_PRODUCERS) {
+            const bool padding = s % S4 >= S;
+            float4 v[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                v[i] = idx[i] != DEAD ? __ldg(reinterpret_cast<const float4 *>(xcol + (size_t)idx[i] * dim)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (s + NS_PRODUCERS < total) load_idx(s + NS_PRODUCERS);
+            if (s >= S4 && !padding) {
+                if (!have_c) {
+                    // the first pass over the node ends before this completes: the bound grows with the node
+                    bool got = false;
+                    for (unsigned long long tries = 0; tries < 4096ull + 4 * count && !got; ++tries) {
+                        got = mbar_try_wait(cbar, 0u, 1000u);
+                        if (!got && (tries & 255u) == 255u && *(volatile int *)&abort_flag) break;
+                    }
+                    if (!got) {
+                        if (!*(volatile int *)&abort_flag) {
+                            abort_flag = 1;
+                            atomicCAS(error, 0, NS_ERR_WAIT);
+                        }
+                        break;
+                    }
+                    cc = *reinterpret_cast<const float4 *>(c_sh + piece * 4);
+                    have_c = true;
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float d;
+                    d = __fsub_rn(v[i].x, cc.x), v[i].x = __fmul_rn(d, d);
+                    d = __fsub_rn(v[i].y, cc.y), v[i].y = __fmul_rn(d, d);
+                    d = __fsub_rn(v[i].z, cc.z), v[i].z = __fmul_rn(d, d);
+                    d = __fsub_rn(v[i].w, cc.w), v[i].w = __fmul_rn(d, d);
+                }
+            }
+            const uint32_t grp = s / NS_GROUP, gslot = grp % NS_GROUPS;
+            if (!mbar_wait(&empty[gslot], ((grp / NS_GROUPS) & 1u) ^ 1u, &abort_flag, error, NS_ERR_WAIT, 100u)) break;
+            if (!padding) {
+                float *dst = ring + (size_t)(s % NS_RING) * (NS_STAGE_BYTES / 4);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) { // row 4 i + sub of the stage: four-row group i, position sub
+                    dst[off[0] + ((i ^ gj[0]) << 2)] = v[i].x;
+                    dst[off[1] + ((i ^ gj[1]) << 2)] = v[i].y;
+                    dst[off[2] + ((i ^ gj[2]) << 2)] = v[i].z;
+                    dst[off[3] + ((i ^ gj[3]) << 2)] = v[i].w;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) {
+                __threadfence_block(); // the stage's values before its announcement
+                atomicAdd(const_cast<uint32_t *>(&filled[gslot]), 1u);
+            }
         }
     }
 }
@@ -234,6 +447,83 @@ __global__ void tsvq_quantize_kernel(const float *x, size_t n, size_t dim, const
     }
 }
 
+// Tile variant of the lookup for rows in whole 16-byte pieces (dim a multiple of 8, aligned pointers): a CTA stages 128
+// rows in shared memory with coalesced 128-bit loads (row stride dim + 4 floats, so the per-thread 128-bit reads of the
+// walk are conflict-free), every thread walks the tree for its own row with the same serial distance chains as above but
+// fetches both children's centroids 16 bytes at a time, and the f16 rows of the leaves are written by the whole CTA in
+// 16-byte pieces.  One thread per row reading its row straight from global memory spends its time on 32 different lines
+// per load instruction and 2-byte stores 2 * dim bytes apart.
+constexpr int TQ_ROWS = 128;
+template <int METRIC>
+__global__ void __launch_bounds__(TQ_ROWS) tsvq_quantize_tile_kernel(const float *__restrict__ x, size_t n, int dim, const float *__restrict__ centroids,
+                                                                     const int32_t *__restrict__ left, const int32_t *__restrict__ right, float pv,
+                                                                     uint16_t *out_f16, uint32_t *leaf_out)
+{
+    extern __shared__ __align__(16) float tq_rows[];
+    __shared__ int leaf_sh[TQ_ROWS];
+    const int stride = dim + 4, chunks = dim / 4, octs = dim / 8;
+    for (size_t tile = blockIdx.x; tile * TQ_ROWS < n; tile += gridDim.x) {
+        const size_t row0 = tile * TQ_ROWS;
+        const int rows = (int)(n - row0 < (size_t)TQ_ROWS ? n - row0 : (size_t)TQ_ROWS);
+        __syncthreads(); // the previous tile's readers are done
+        const float4 *src = reinterpret_cast<const float4 *>(x + row0 * dim);
+        for (int i = threadIdx.x; i < rows * chunks; i += TQ_ROWS) {
+            const int r = i / chunks, c = i - r * chunks;
+            *reinterpret_cast<float4 *>(tq_rows + r * stride + 4 * c) = __ldcs(src + i);
+        }
+        __syncthreads();
+        if ((int)threadIdx.x < rows) {
+            const float *v = tq_rows + threadIdx.x * stride;
+            float norm_a = 0.0f;
+            if (METRIC == M_COSINE) norm_a = norm_chain(v, dim, 1);
+            int node = 0;
+            for (;;) {
+                const int l = left[node], r = right[node];
+                if (l >= 0 && r >= 0) {
+                    const float4 *cl = reinterpret_cast<const float4 *>(centroids + (size_t)l * dim);
+                    const float4 *cr = reinterpret_cast<const float4 *>(centroids + (size_t)r * dim);
+                    DistAcc<METRIC> al, ar;
+                    al.init();
+                    ar.init();
+#pragma unroll 2
+                    for (int c = 0; c < chunks; ++c) {
+                        const float4 xv = *reinterpret_cast<const float4 *>(v + 4 * c);
+                        const float4 a = __ldg(cl + c), b = __ldg(cr + c);
+                        al.step(xv.x, a.x, pv), ar.step(xv.x, b.x, pv);
+                        al.step(xv.y, a.y, pv), ar.step(xv.y, b.y, pv);
+                        al.step(xv.z, a.z, pv), ar.step(xv.z, b.z, pv);
+                        al.step(xv.w, a.w, pv), ar.step(xv.w, b.w, pv);
+                    }
+                    const float dl = al.finish(pv, norm_a), dr = ar.finish(pv, norm_a);
+                    node = (dl <= dr) ? l : r; // src/tsvq.rs:172: the left child on ties; a NaN distance sends the row right
+                } else if (l >= 0) {
+                    node = l;
+                } else if (r >= 0) {
+                    node = r;
+                } else {
+                    break;
+                }
+            }
+            leaf_sh[threadIdx.x] = node;
+            if (leaf_out) leaf_out[row0 + threadIdx.x] = (uint32_t)node;
+        }
+        __syncthreads();
+        if (out_f16) {
+            for (int i = threadIdx.x; i < rows * octs; i += TQ_ROWS) {
+                const int r = i / octs, o = i - r * octs;
+                const float4 *c = reinterpret_cast<const float4 *>(centroids + (size_t)leaf_sh[r] * dim) + 2 * o;
+                const float4 p = __ldg(c), q = __ldg(c + 1);
+                uint4 w;
+                w.x = (uint32_t)f32_to_f16_bits(p.x) | ((uint32_t)f32_to_f16_bits(p.y) << 16);
+                w.y = (uint32_t)f32_to_f16_bits(p.z) | ((uint32_t)f32_to_f16_bits(p.w) << 16);
+                w.z = (uint32_t)f32_to_f16_bits(q.x) | ((uint32_t)f32_to_f16_bits(q.y) << 16);
+                w.w = (uint32_t)f32_to_f16_bits(q.z) | ((uint32_t)f32_to_f16_bits(q.w) << 16);
+                __stcs(reinterpret_cast<uint4 *>(out_f16 + (row0 + r) * dim + 8 * o), w);
+            }
+        }
+    }
+}
+
 inline unsigned grid_for(size_t items, int threads, unsigned cap)
 {
     return (unsigned)std::max<size_t>(1, std::min<size_t>((items + threads - 1) / threads, cap));
@@ -265,6 +555,9 @@ void tsvq_fit(CudaDevice &dev, const float *x, size_t n, size_t dim, size_t max_
     size_t tmp_bytes = std::max(sort_bytes, scan_bytes);
     float *spread = nullptr;
     size_t spread_cap = 0;
+    // rows in whole 128-byte pieces of 32 columns: the streaming kernel; any other shape: one thread per (node, dimension)
+    const bool stream_rows = dim % 32 == 0 && dim / 32 <= 65535 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && getenv("VQB_TSVQ_SERIAL_WALK") == nullptr;
+    if (stream_rows) VQB_CUDA_CHECK(cudaFuncSetAttribute(node_stats_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, NS_SMEM));
     auto cleanup = [&] {
         dev.release(nodes_d), dev.release(perm), dev.release(perm2), dev.release(pos_node), dev.release(flags), dev.release(scan);
         dev.release(keys), dev.release(keys2), dev.release(error), dev.release(tmp), dev.release(spread);
@@ -297,8 +590,13 @@ void tsvq_fit(CudaDevice &dev, const float *x, size_t n, size_t dim, size_t max_
             }
             {
                 KernelScope ks(dev, "tsvq_node_stats");
-                const dim3 grid((unsigned)level_count, (unsigned)std::min<size_t>((dim + 31) / 32, 64));
-                node_stats_kernel<<<grid, 32, 0, st>>>(x, dim, perm, nodes_d, (int)first, cent, spread);
+                if (stream_rows) {
+                    const dim3 grid((unsigned)level_count, (unsigned)(dim / 32));
+                    node_stats_stream_kernel<<<grid, NS_THREADS, NS_SMEM, st>>>(x, dim, perm, nodes_d, (int)first, cent, spread, error);
+                } else {
+                    const dim3 grid((unsigned)level_count, (unsigned)std::min<size_t>((dim + 31) / 32, 64));
+                    node_stats_kernel<<<grid, 32, 0, st>>>(x, dim, perm, nodes_d, (int)first, cent, spread);
+                }
                 VQB_CUDA_CHECK(cudaGetLastError());
                 dev.count_launch();
             }
@@ -321,6 +619,7 @@ void tsvq_fit(CudaDevice &dev, const float *x, size_t n, size_t dim, size_t max_
             std::swap(perm, perm2);
             int herr = 0;
             dev.download(&herr, error, sizeof(int));
+            if (herr == NS_ERR_WAIT) throw Error(100, "tsvq: a wait inside the node statistics kernel ran out");
             if (herr) throw Error(herr, "values are not comparable (NaN in the training data)");
             dev.download(h.data() + first, nodes_d + first, sizeof(NodeInfo) * level_count);
             const size_t level_end = h.size();
@@ -370,6 +669,18 @@ template <int METRIC>
 static void launch_quantize(CudaDevice &dev, const TsvqTree &t, double p, const float *x, size_t n, uint16_t *out_f16, uint32_t *leaf)
 {
     KernelScope ks(dev, "tsvq_quantize");
+    const size_t tile_smem = sizeof(float) * TQ_ROWS * (t.dim + 4);
+    const bool aligned = reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(out_f16) % 16 == 0;
+    if (t.dim % 8 == 0 && tile_smem <= 200 * 1024 && aligned && getenv("VQB_TSVQ_SERIAL_WALK") == nullptr) {
+        VQB_CUDA_CHECK(cudaFuncSetAttribute(tsvq_quantize_tile_kernel<METRIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem));
+        const size_t tiles = (n + TQ_ROWS - 1) / TQ_ROWS;
+        const unsigned per_sm = (unsigned)std::max<size_t>(1, std::min<size_t>(8, (220 * 1024) / (tile_smem + 1024)));
+        const unsigned grid = (unsigned)std::min<size_t>(tiles, (size_t)dev.sm_count() * per_sm);
+        tsvq_quantize_tile_kernel<METRIC><<<grid, TQ_ROWS, tile_smem, dev.stream()>>>(x, n, (int)t.dim, t.centroids, t.left, t.right, (float)p, out_f16, leaf);
+        VQB_CUDA_CHECK(cudaGetLastError());
+        dev.count_launch();
+        return;
+    }
     tsvq_quantize_kernel<METRIC><<<grid_for(n, 128, (unsigned)dev.sm_count() * 16), 128, 0, dev.stream()>>>(x, n, t.dim, t.centroids, t.left, t.right, (float)p,
                                                                                                      out_f16, leaf);
     VQB_CUDA_CHECK(cudaGetLastError());
