@@ -174,30 +174,39 @@ __global__ void __launch_bounds__(NS_THREADS) node_stats_stream_kernel(const flo
             }
             __threadfence_block(); // the stages' values are read after their announcement
         };
+        // shared-memory address of this lane's dimension in stage s; a four-row group q sits at + ((q ^ g) << 4) bytes
+        auto stage_addr = [&](uint32_t s) { return smem_u32(ring + (size_t)(s % NS_RING) * (NS_STAGE_BYTES / 4) + lane * NS_STAGE_ROWS); };
+        // volatile, so that the loads stay where they are written: between the additions, whose issue slots they fill
+        auto load4 = [&](uint32_t addr, int q) {
+            float4 r;
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "r"(addr + ((q ^ g) << 4)));
+            return r;
+        };
         auto request = [&](uint32_t s, float4(&buf)[16]) {
-            const float *src = ring + (size_t)(s % NS_RING) * (NS_STAGE_BYTES / 4) + lane * NS_STAGE_ROWS;
+            const uint32_t addr = stage_addr(s);
 #pragma unroll
-            for (int q = 0; q < 16; ++q) buf[q] = *reinterpret_cast<const float4 *>(src + ((q ^ g) << 2));
+            for (int q = 0; q < 16; ++q) buf[q] = load4(addr, q);
         };
         // cur holds stage s = base + sb (sb < S)
         auto step = [&](float4(&cur)[16], float4(&nxt)[16], uint32_t base, uint32_t sb) {
             const uint32_t s = base + sb;
-            if (sb + 1 < S) {
-                if (((s + 1) & (NS_GROUP - 1)) == 0) {
-                    group_ready((s + 1) / NS_GROUP, ahead);
-                    if (!ok) return;
-                }
-                request(s + 1, nxt);
+            const bool has_next = sb + 1 < S;
+            if (has_next && ((s + 1) & (NS_GROUP - 1)) == 0) {
+                group_ready((s + 1) / NS_GROUP, ahead);
+                if (!ok) return;
             }
             if ((s & (NS_GROUP - 1)) == 0) ahead = filled[(s / NS_GROUP + 1) % NS_GROUPS];
             const unsigned long long left = count - (unsigned long long)sb * NS_STAGE_ROWS;
-            if (left >= (unsigned long long)NS_STAGE_ROWS) {
+            if (left >= (unsigned long long)NS_STAGE_ROWS && has_next) {
+                const uint32_t addr = stage_addr(s + 1);
 #pragma unroll
-                for (int q = 0; q < 16; ++q) {
+                for (int q = 0; q < 16; ++q) { // one load of the next stage per four additions of this one
+                    nxt[q] = load4(addr, q);
                     acc = __fadd_rn(acc, cur[q].x), acc = __fadd_rn(acc, cur[q].y);
                     acc = __fadd_rn(acc, cur[q].z), acc = __fadd_rn(acc, cur[q].w);
                 }
             } else {
+                if (has_next) request(s + 1, nxt);
                 const int rows_here = (int)left;
 #pragma unroll
                 for (int q = 0; q < 16; ++q) {
