@@ -108,13 +108,17 @@ int vqb_ctx_alloc_count(const vqb_ctx *ctx, uint64_t *out);
 int vqb_ctx_timing(vqb_ctx *ctx, int enable);
 int vqb_ctx_timing_report(vqb_ctx *ctx, char *buf, size_t cap);
 
-/* ---- multi-GPU (one process per GPU; NCCL all-reduce of the centroid sums
- * and counts once per LBG iteration; the reference has no counterpart, it is
- * a single-process rayon program) ---------------------------------------- */
+/* ---- multi-GPU (one process per GPU; the reference has no counterpart, it is a single-process rayon program).
+ * Once per LBG iteration the centroid sums, counts and moved flags of all ranks are added.  Ranks of one node that can
+ * map each other's memory (up to 8; CUDA IPC over NVLink) do this inside the centroid-update kernel, which reads every
+ * rank's part with peer loads and adds them in rank order; otherwise one NCCL all-reduce runs before that kernel.
+ * VQB_PEER_EXCHANGE=0 in the environment selects NCCL.  Either way all ranks end with bit-identical codebooks. */
 #define VQB_UNIQUE_ID_BYTES 128
 int vqb_comm_unique_id(uint8_t *out /* VQB_UNIQUE_ID_BYTES */);
 int vqb_comm_init(vqb_ctx *ctx, const uint8_t *unique_id, int rank, int world);
 int vqb_comm_destroy(vqb_ctx *ctx);
+/* Number of iterations so far whose parts were added by the update kernel itself (0: NCCL did all of them). */
+int vqb_comm_exchange_count(const vqb_ctx *ctx, uint64_t *out);
 
 /* ---- Distance::compute, row-wise on the GPU (src/distances.rs:115-172):
  * out[i] = distance(a[i*d .. ), b[i*d .. )) for i < n.  da != db reproduces

@@ -121,7 +121,7 @@ class HostDevice : public Device {
             }
         }
     }
-    void update_centroids(const Shape &sh, const IterBuffers &buf, const uint32_t *active, float *centroids, IterStatus &st) override
+    void update_centroids(const Shape &sh, const IterBuffers &buf, const uint32_t *active, float *centroids, IterStatus &st, const PeerExchange * = nullptr) override
     {
         const size_t wps = (sh.k + 31) / 32;
         st.moved.assign(sh.m, 0);

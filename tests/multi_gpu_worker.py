@@ -33,6 +33,11 @@ def main():
         res[f"it_{name}"] = pq.iterations
         out, codes = pq.quantize(torch.from_numpy(x[begin:end]).cuda(), return_codes=True)
         res[f"codes_{name}"] = codes.cpu().numpy()
+    # 16-wide sub-spaces take the general assignment and update kernels
+    pqw = vq.ProductQuantizer.fit(torch.from_numpy(x_int[begin:end]).cuda(), 2, k, 4, vq.Distance.Euclidean, 9, ctx=ctx, accumulate=vq.ACCUM_FAST)
+    res["cb_wide"] = pqw.codebooks
+    res["it_wide"] = pqw.iterations
+    res["exchanges"] = np.int64(ctx.exchange_count())
     np.savez(f"{out_prefix}.rank{rank}.npz", begin=begin, end=end, **res)
     ctx.destroy_comm()
     dist.destroy_process_group()

@@ -1,4 +1,6 @@
-"""Two GPUs, one process each: rows sharded, centroid sums/counts all-reduced by NCCL inside the library."""
+"""Two GPUs, one process each: rows sharded; per iteration the ranks' centroid sums, counts and moved flags are added either
+inside the centroid-update kernel over peer memory (the default where the ranks can map each other's memory) or by one NCCL
+all-reduce (VQB_PEER_EXCHANGE=0)."""
 import os
 import socket
 import subprocess
@@ -14,7 +16,8 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def test_two_gpu_fit_matches_the_oracle(oracle, tmp_path):
+@pytest.mark.parametrize("exchange", ["peer", "nccl"])
+def test_two_gpu_fit_matches_the_oracle(oracle, tmp_path, exchange):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -23,7 +26,8 @@ def test_two_gpu_fit_matches_the_oracle(oracle, tmp_path):
     port = s.getsockname()[1]
     s.close()
     prefix = os.path.join(str(tmp_path), "out")
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE="2", NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE="2", NCCL_NVLS_ENABLE="0",
+               VQB_PEER_EXCHANGE="1" if exchange == "peer" else "0")
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "multi_gpu_worker.py"), prefix],
                               env=dict(env, RANK=str(r), LOCAL_RANK=str(r)), stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
              for r in range(2)]
@@ -45,6 +49,17 @@ def test_two_gpu_fit_matches_the_oracle(oracle, tmp_path):
         rel = np.linalg.norm(r["cb_flt"] - cb_flt, axis=2) / np.linalg.norm(cb_flt, axis=2)
         assert rel.max() <= 1e-3
     assert np.array_equal(res[0]["cb_flt"], res[1]["cb_flt"])
+    so3 = RecordingSeeder(9)
+    cb_wide, it_wide = oracle.pq_fit(x_int, 2, k, 4, so3.init_pq(n, 2, k), so3.draw)
+    for r in res:
+        assert np.array_equal(r["cb_wide"], cb_wide) and np.array_equal(r["it_wide"], it_wide)
     codes = np.concatenate([res[0]["codes_int"], res[1]["codes_int"]]).astype(np.uint32)
     _o, codes_o = oracle.pq_quantize(cb_int, x_int, oracle.EUCLIDEAN)
     assert np.array_equal(codes, codes_o)
+    # which path added the parts
+    if exchange == "nccl":
+        assert int(res[0]["exchanges"]) == 0
+    elif int(res[0]["exchanges"]) == 0:
+        pytest.skip("the ranks could not map each other's memory on this machine: NCCL did the exchange (covered by the other case)")
+    else:
+        assert int(res[0]["exchanges"]) == int(res[1]["exchanges"]) >= 3

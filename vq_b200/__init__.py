@@ -188,6 +188,12 @@ class Context:
             _raise(rc, self.handle)
         self.rank, self.world = int(rank), int(world)
 
+    def exchange_count(self) -> int:
+        """Iterations so far whose per-rank parts were added by the centroid-update kernel over peer memory (0: NCCL)."""
+        n = C.c_uint64(0)
+        _lib.load().vqb_comm_exchange_count(self.handle, C.byref(n))
+        return int(n.value)
+
     def destroy_comm(self):
         _lib.load().vqb_comm_destroy(self.handle)
         self.rank, self.world = 0, 1

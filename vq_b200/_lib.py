@@ -37,6 +37,7 @@ SIGNATURES = {
     "vqb_comm_unique_id": (C.c_int, [_P]),
     "vqb_comm_init": (C.c_int, [_P, _P, C.c_int, C.c_int]),
     "vqb_comm_destroy": (C.c_int, [_P]),
+    "vqb_comm_exchange_count": (C.c_int, [_P, C.POINTER(C.c_uint64)]),
     "vqb_distance_rows": (C.c_int, [_P, C.c_int, C.c_double, _P, _SZ, _P, _SZ, _SZ, _P]),
     "vqb_tsvq_fit": (C.c_int, [_P, _P, _SZ, _SZ, _SZ, C.c_int, C.c_double, C.POINTER(_P)]),
     "vqb_tsvq_quantize": (C.c_int, [_P, _P, _SZ, _SZ, _P, _P]),

@@ -347,6 +347,13 @@ int vqb_comm_init(vqb_ctx *ctx, const uint8_t *unique_id, int rank, int world)
     });
 }
 
+int vqb_comm_exchange_count(const vqb_ctx *ctx, uint64_t *out)
+{
+    if (!ctx || !out) return set_err(nullptr, VQB_ERR_BAD_ARGUMENT, "NULL argument");
+    *out = ctx->comm ? ctx->comm->peer_exchanges() : 0;
+    return VQB_OK;
+}
+
 int vqb_comm_destroy(vqb_ctx *ctx)
 {
     if (!ctx) return VQB_OK;

@@ -54,6 +54,17 @@ struct IterStatus {
     std::vector<uint32_t> empty_bits;    // [m][ceil(k / 32)], bit j of subspace s = cluster j is empty
 };
 
+// One direct exchange of iteration buffers between the GPUs of a node (peer_exchange.cuh has the protocol): where every
+// rank's buffer of this exchange and every rank's arrival flags are mapped in this process.
+constexpr int MAX_PEERS = 8;
+struct PeerExchange {
+    int world = 0, rank = 0;
+    uint32_t epoch = 0;
+    const uint32_t *words[MAX_PEERS] = {};
+    uint32_t *flags[MAX_PEERS] = {};
+    uint32_t *stale = nullptr; // this rank's buffer of the previous exchange
+};
+
 class Comm {
   public:
     virtual ~Comm() {}
@@ -65,6 +76,23 @@ class Comm {
     virtual void allreduce_sum_u32(uint32_t *buf, size_t n) = 0;
     virtual void allreduce_max_u32(uint32_t *buf, size_t n) = 0;
     virtual void allreduce_sum_u64(uint64_t *buf, size_t n) = 0;
+    // Optional: iteration buffers that every GPU of the node can read, so that the centroid-update kernel does the
+    // all-reduce itself.  peer_window (collective; every rank passes the same size) returns two zero-filled buffers of
+    // `words` 32-bit words in this rank's window, or false when the ranks cannot map each other's memory.
+    // peer_exchange(which) (same call order on every rank) numbers the next exchange, whose data every rank gathered in
+    // its buffer `which`.
+    virtual bool peer_window(size_t words, uint32_t *local[2])
+    {
+        (void)words;
+        (void)local;
+        return false;
+    }
+    virtual PeerExchange peer_exchange(int which)
+    {
+        (void)which;
+        return PeerExchange();
+    }
+    virtual uint64_t peer_exchanges() const { return 0; } // direct exchanges numbered so far
     // Collectives issued between group_begin() and group_end() may be fused into one launch.
     virtual void group_begin() {}
     virtual void group_end() {}
@@ -125,8 +153,10 @@ class Device {
                             bool ordered, const IterBuffers &buf) = 0;
     // centroids = sums / (counts as f32) where counts > 0 (src/vector.rs:315-316), active subspaces only; reports
     // the iteration's flags to the host (complete on return) and clears the buffer for the next iteration.
+    // With `px` the buffer holds this rank's part only (u32 counts) and the kernel adds the parts of all ranks itself; it
+    // then clears px->stale instead of `buf`.
     virtual void update_centroids(const Shape &sh, const IterBuffers &buf, const uint32_t *active, float *centroids,
-                                  IterStatus &status) = 0;
+                                  IterStatus &status, const PeerExchange *px = nullptr) = 0;
     // Residual update of one RVQ stage (src/rvq.rs:111-138): argmin with `metric`, res -= centroid in place,
     // *norm_sum += sum over rows of sqrt(sum res^2) (f64, device scalar, not cleared here).
     virtual void rvq_update(float *res, size_t n, size_t dim, const float *centroids, size_t k, int metric,

@@ -84,7 +84,6 @@ CudaDevice::~CudaDevice()
         cudaFree(cand_);
         cudaFree(tc_stats_);
         cudaFree(tc_error_);
-        cudaFree(status_counter_);
         if (status_host_) cudaFreeHost(status_host_);
         for (auto &sp : spans_) {
             event_pool_.push_back(sp.a);
@@ -896,13 +895,15 @@ void CudaDevice::accumulate(const Shape &sh, const float *x, const void *codes, 
 // One CTA of 8 warps per (sub-space, 32 clusters): a warp takes four clusters, its lanes the dimensions.
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) update_centroids_kernel(float *sums, uint32_t *counts, uint32_t *moved, int counts_f32, const uint32_t *active,
-                                                               int k, int sd, float *centroids, StatusPage sp)
+                                                               int k, int sd, float *centroids, StatusPage sp, const PeerView pv)
 {
     __shared__ uint32_t s_bits;
     const int s = blockIdx.x, word = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool act = !active || active[s] != 0;
+    const bool direct = pv.world > 1; // the parts of all ranks are added here, in rank order (peer_exchange.cuh)
     if (threadIdx.x == 0) s_bits = 0u;
+    peer_arrive_and_wait(pv);
     __syncthreads();
     if (act) {
 #pragma unroll
@@ -910,32 +911,79 @@ __global__ void __launch_bounds__(256) update_centroids_kernel(float *sums, uint
             const int j = word * 32 + warp * 4 + q;
             if (j >= k) break;
             const size_t cj = (size_t)s * k + j;
-            const uint32_t cw = counts[cj];
-            const float cf = counts_f32 ? __uint_as_float(cw) : __uint2float_rn(cw);
-            if (cf != 0.0f) {
-                for (int d = lane; d < sd; d += 32) {
-                    centroids[cj * sd + d] = __fdiv_rn(sums[cj * sd + d], cf);
-                    sums[cj * sd + d] = 0.0f;
-                }
-            } else if (lane == 0) {
-                atomicOr(&s_bits, 1u << (warp * 4 + q));
+            float cf;
+            if (direct) {
+                uint32_t cnt = 0;
+                for (int r = 0; r < pv.world; ++r) cnt += peer_ld(pv.words[r] + pv.off_counts + cj);
+                cf = __uint2float_rn(cnt);
+            } else {
+                const uint32_t cw = counts[cj];
+                cf = counts_f32 ? __uint_as_float(cw) : __uint2float_rn(cw);
             }
-            __syncwarp();
-            if (lane == 0) counts[cj] = 0u;
+            if (direct) {
+                for (int d = lane; d < sd; d += 32) {
+                    float part[VQB_MAX_PEERS];
+#pragma unroll
+                    for (int r = 0; r < VQB_MAX_PEERS; ++r) part[r] = r < pv.world ? __uint_as_float(peer_ld(pv.words[r] + cj * sd + d)) : 0.0f;
+                    float v = part[0];
+#pragma unroll
+                    for (int r = 1; r < VQB_MAX_PEERS; ++r)
+                        if (r < pv.world) v = __fadd_rn(v, part[r]);
+                    if (cf != 0.0f) centroids[cj * sd + d] = __fdiv_rn(v, cf);
+                    pv.stale[cj * sd + d] = 0u;
+                }
+                if (cf == 0.0f && lane == 0) atomicOr(&s_bits, 1u << (warp * 4 + q));
+                if (lane == 0) pv.stale[pv.off_counts + cj] = 0u;
+            } else {
+                if (cf != 0.0f) {
+                    for (int d = lane; d < sd; d += 32) {
+                        centroids[cj * sd + d] = __fdiv_rn(sums[cj * sd + d], cf);
+                        sums[cj * sd + d] = 0.0f;
+                    }
+                } else if (lane == 0) {
+                    atomicOr(&s_bits, 1u << (warp * 4 + q));
+                }
+                __syncwarp();
+                if (lane == 0) counts[cj] = 0u;
+            }
         }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        sp.host_bitmap()[(size_t)s * sp.words_per_subspace + word] = s_bits;
+        sp.put(sp.idx_bitmap(s, word), s_bits);
         if (word == 0) {
-            sp.host_moved()[s] = act ? moved[s] : 0u;
-            moved[s] = 0u;
+            uint32_t mv = 0u;
+            if (direct) {
+                for (int r = 0; r < pv.world; ++r) mv |= peer_ld(pv.words[r] + pv.off_moved + s);
+                pv.stale[pv.off_moved + s] = 0u;
+            } else {
+                mv = moved[s];
+                moved[s] = 0u;
+            }
+            sp.put(sp.idx_moved(s), act ? mv : 0u);
+            if (s == 0) sp.put_error();
         }
     }
-    status_publish(sp, threadIdx.x == 0);
 }
 
-StatusPage CudaDevice::status_page(size_t m, size_t k, uint32_t blocks)
+// what the update kernels need to know of a direct exchange
+static PeerView peer_view(const PeerExchange *px, const Shape &sh, int *error)
+{
+    PeerView pv;
+    if (!px || px->world <= 1) return pv;
+    if (px->world > VQB_MAX_PEERS) throw Error(103, "direct exchange between more than 8 ranks is not supported");
+    pv.world = px->world;
+    pv.rank = px->rank;
+    pv.epoch = px->epoch;
+    for (int r = 0; r < px->world; ++r) pv.words[r] = px->words[r], pv.flags[r] = px->flags[r];
+    pv.stale = px->stale;
+    pv.off_counts = (unsigned long long)sh.m * sh.k * sh.sd;
+    pv.off_moved = pv.off_counts + (unsigned long long)sh.m * sh.k;
+    pv.error = error;
+    return pv;
+}
+
+StatusPage CudaDevice::status_page(size_t m, size_t k)
 {
     const size_t need = StatusPage::words(m, k);
     if (need > status_cap_words_) {
@@ -943,44 +991,42 @@ StatusPage CudaDevice::status_page(size_t m, size_t k, uint32_t blocks)
         if (status_host_) cudaFreeHost(status_host_);
         status_host_ = nullptr;
         status_cap_words_ = 0;
-        const size_t cap = std::max<size_t>(need + need / 2, 4096);
+        const size_t cap = std::max<size_t>(need + need / 2, 2048);
         ++device_allocs_;
-        VQB_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void **>(&status_host_), cap * sizeof(uint32_t), cudaHostAllocMapped));
+        VQB_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void **>(&status_host_), cap * sizeof(unsigned long long), cudaHostAllocMapped));
         VQB_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void **>(&status_dev_), status_host_, 0));
-        std::memset(status_host_, 0, cap * sizeof(uint32_t));
+        std::memset(status_host_, 0, cap * sizeof(unsigned long long));
         status_cap_words_ = cap;
         status_seq_ = 0;
     }
-    if (!status_counter_) {
-        ++device_allocs_;
-        VQB_CUDA_CHECK(cudaMalloc(&status_counter_, sizeof(unsigned int)));
-        VQB_CUDA_CHECK(cudaMemsetAsync(status_counter_, 0, sizeof(unsigned int), stream_));
-    }
     StatusPage sp;
     sp.host_words = status_dev_;
-    sp.done_counter = status_counter_;
     sp.tc_error = tc_error_;
     sp.seq = ++status_seq_;
     if (sp.seq == 0) sp.seq = ++status_seq_; // zero is the page's initial value
-    sp.total_blocks = blocks;
     sp.m = (uint32_t)m;
     sp.words_per_subspace = (uint32_t)((k + 31) / 32);
     return sp;
 }
 
-// The host polls the page's sequence word (a read of its own memory) instead of queueing a copy and waiting on an event.
+// The host polls the page (reads of its own memory) instead of queueing a copy and waiting on an event: every entry is
+// valid once it carries this update's number.
 void CudaDevice::wait_status(const StatusPage &sp, size_t m, size_t k, IterStatus &out)
 {
-    volatile uint32_t *page = status_host_;
+    volatile unsigned long long *page = status_host_;
+    const size_t need = StatusPage::words(m, k);
     const auto t0 = std::chrono::steady_clock::now();
-    for (uint64_t spin = 1;; ++spin) {
-        if (page[0] == sp.seq) break;
+    size_t next = 0; // entries below `next` have arrived
+    for (uint64_t spin = 1; next < need; ++spin) {
+        while (next < need && (uint32_t)(page[next] >> 32) == sp.seq) ++next;
+        if (next == need) break;
         if ((spin & 0xFFFFu) == 0) {
             const cudaError_t q = cudaStreamQuery(stream_);
             if (q != cudaSuccess && q != cudaErrorNotReady) VQB_CUDA_CHECK(q);
-            if (q == cudaSuccess && page[0] != sp.seq) {
-                // the stream has drained: the write to the page must have landed by now
-                if (page[0] == sp.seq) break;
+            if (q == cudaSuccess) {
+                // the stream has drained: the writes to the page must have landed by now
+                while (next < need && (uint32_t)(page[next] >> 32) == sp.seq) ++next;
+                if (next == need) break;
                 throw Error(100, "centroid update finished without reporting its status");
             }
             if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(120))
@@ -992,22 +1038,24 @@ void CudaDevice::wait_status(const StatusPage &sp, size_t m, size_t k, IterStatu
     out.moved.assign(m, 0);
     out.has_empty.assign(m, 0);
     out.empty_bits.assign(m * wps, 0u);
-    const uint32_t *mv = status_host_ + 4, *bm = status_host_ + 4 + m;
     for (size_t s = 0; s < m; ++s) {
-        out.moved[s] = mv[s] != 0u;
+        out.moved[s] = (uint32_t)page[sp.idx_moved(s)] != 0u;
         for (size_t w = 0; w < wps; ++w) {
-            out.empty_bits[s * wps + w] = bm[s * wps + w];
-            if (bm[s * wps + w]) out.has_empty[s] = 1;
+            const uint32_t bits = (uint32_t)page[sp.idx_bitmap(s, w)];
+            out.empty_bits[s * wps + w] = bits;
+            if (bits) out.has_empty[s] = 1;
         }
     }
-    const int code = (int)status_host_[1];
+    const int code = (int)(uint32_t)page[sp.idx_error()];
     if (code != 0) {
         cudaMemsetAsync(tc_error_, 0, sizeof(int), stream_);
+        if (code == PEER_ERR_WAIT) throw Error(101, "a rank did not arrive at the exchange of an iteration within four seconds");
         throw Error(100, "tensor-core kernel gave up waiting (stage " + std::to_string(code) + "); set VQB_NO_TENSOR=1 to use the CUDA-core path");
     }
 }
 
-void CudaDevice::update_centroids(const Shape &sh, const IterBuffers &buf, const uint32_t *active, float *centroids, IterStatus &status)
+void CudaDevice::update_centroids(const Shape &sh, const IterBuffers &buf, const uint32_t *active, float *centroids, IterStatus &status,
+                                  const PeerExchange *px)
 {
     const size_t m = sh.m, k = sh.k;
     if (m * k * sh.sd == 0) {
@@ -1019,20 +1067,21 @@ void CudaDevice::update_centroids(const Shape &sh, const IterBuffers &buf, const
     // shapes of the product-quantizer tensor kernel: the same launch writes the operand of the next assignment pass
     const bool pq8 = pq_tensor_enabled_ && sh.sd == 8 && sh.m >= 4 && sh.m <= 64 && sh.m % 4 == 0 && k >= 2 && k <= 256 && pq_scratch_ != nullptr &&
                      (reinterpret_cast<uintptr_t>(centroids) & 15u) == 0 && (reinterpret_cast<uintptr_t>(buf.sums) & 15u) == 0;
+    const PeerView pv = peer_view(px, sh, tc_error_);
     if (pq8) {
-        const StatusPage sp = status_page(m, k, (uint32_t)m);
-        launch_pq_update_centroids(*this, (int)m, (int)k, buf.sums, buf.counts, buf.moved, buf.counts_f32, active, centroids, pq_scratch_, sp);
+        const StatusPage sp = status_page(m, k);
+        launch_pq_update_centroids(*this, (int)m, (int)k, buf.sums, buf.counts, buf.moved, buf.counts_f32, active, centroids, pq_scratch_, sp, pv);
         bop_fresh_ = centroids;
         wait_status(sp, m, k, status);
         return;
     }
     const unsigned wps = (unsigned)((k + 31) / 32);
     if (wps > 65535u) throw Error(103, "more than 2,097,120 clusters per sub-space are not supported");
-    const StatusPage sp = status_page(m, k, (uint32_t)(m * wps));
+    const StatusPage sp = status_page(m, k);
     {
         KernelScope ks(*this, "update_centroids");
         update_centroids_kernel<<<dim3((unsigned)m, wps), 256, 0, stream_>>>(buf.sums, buf.counts, buf.moved, buf.counts_f32 ? 1 : 0, active, (int)k,
-                                                                            (int)sh.sd, centroids, sp);
+                                                                            (int)sh.sd, centroids, sp, pv);
         VQB_CUDA_CHECK(cudaGetLastError());
         count_launch();
     }

@@ -45,7 +45,7 @@ class CudaDevice : public Device {
     void accumulate(const Shape &sh, const float *x, const void *codes, const uint32_t *active, bool ordered,
                     const IterBuffers &buf) override;
     void update_centroids(const Shape &sh, const IterBuffers &buf, const uint32_t *active, float *centroids,
-                          IterStatus &status) override;
+                          IterStatus &status, const PeerExchange *px = nullptr) override;
     void rvq_update(float *res, size_t n, size_t dim, const float *centroids, size_t k, int metric, double p,
                     double *norm_sum) override;
     void pq_encode(const Shape &sh, const float *x, const float *codebooks, int metric, double p, uint16_t *out_f16,
@@ -106,11 +106,10 @@ class CudaDevice : public Device {
     cudaEvent_t stage_event_ = nullptr;
     std::atomic<uint64_t> launches_{0}, device_allocs_{0};
     // page of mapped pinned memory the centroid-update kernels report to (iter_status.cuh)
-    uint32_t *status_host_ = nullptr, *status_dev_ = nullptr;
+    unsigned long long *status_host_ = nullptr, *status_dev_ = nullptr;
     size_t status_cap_words_ = 0;
-    unsigned int *status_counter_ = nullptr;
     uint32_t status_seq_ = 0;
-    StatusPage status_page(size_t m, size_t k, uint32_t blocks);
+    StatusPage status_page(size_t m, size_t k);
     void wait_status(const StatusPage &sp, size_t m, size_t k, IterStatus &out);
     // centroids whose operand B (pq_tc.cu) the scratch currently holds, written by the fused centroid update
     const float *bop_fresh_ = nullptr;

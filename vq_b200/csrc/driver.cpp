@@ -114,14 +114,28 @@ void lbg_fit(Device &dev, Comm *comm, const Shape &sh, const float *x, size_t ma
     // sums | counts | moved flags of one iteration, one allocation, cleared here once and then by every centroid update
     IterBuffers buf;
     const size_t words = buf.words(sh);
-    DevBuf iter(dev, sizeof(float) * words);
-    dev.zero(iter.p, sizeof(float) * words);
-    buf.sums = iter.as<float>();
-    buf.counts = reinterpret_cast<uint32_t *>(buf.sums + m * k * sd);
-    buf.moved = buf.counts + m * k;
+    auto lay_out = [&](IterBuffers &b, uint32_t *base) {
+        b.sums = reinterpret_cast<float *>(base);
+        b.counts = base + m * k * sd;
+        b.moved = b.counts + m * k;
+    };
+    // Ranks that can map each other's memory gather into two alternating buffers of a shared window and the update kernel
+    // adds the parts itself; otherwise one buffer and an all-reduce.  (Every rank comes here after the collective in
+    // global_rows, i.e. after all kernels of an earlier fit on every rank: nobody reads the window's buffers any more.)
+    uint32_t *window[2] = {nullptr, nullptr};
+    const bool direct = multi && comm->peer_window(words, window);
+    IterBuffers pair[2];
+    DevBuf iter(dev, direct ? 0 : sizeof(float) * words);
+    if (direct) {
+        lay_out(pair[0], window[0]);
+        lay_out(pair[1], window[1]);
+    } else {
+        dev.zero(iter.p, sizeof(float) * words);
+        lay_out(buf, iter.as<uint32_t>());
+    }
     // below 2^24 rows every count is exact in f32, and sums, counts and flags then cross the ranks as ONE f32 all-reduce
-    buf.counts_f32 = multi && n_global < (1ull << 24);
-    if (multi && !buf.counts_f32 && comm->world() > 256)
+    buf.counts_f32 = multi && !direct && n_global < (1ull << 24);
+    if (multi && !direct && !buf.counts_f32 && comm->world() > 256)
         throw Error(VQB_ERR_UNSUPPORTED, "more than 256 ranks with 2^24 or more rows are not supported");
     DevBuf act(dev, sizeof(uint32_t) * m);
     std::vector<uint32_t> active(m, 1);
@@ -137,9 +151,13 @@ void lbg_fit(Device &dev, Comm *comm, const Shape &sh, const float *x, size_t ma
             dev.upload(act.p, active.data(), sizeof(uint32_t) * m);
             active_dirty = false;
         }
+        if (direct) buf = pair[it & 1];
         dev.assign_train(sh, x, centroids, codes.p, act.as<uint32_t>(), buf);          // 59-80
         dev.accumulate(sh, x, codes.p, act.as<uint32_t>(), ordered, buf);              // 83-92
-        if (multi) { // the only exchange of an iteration, ~144 KiB
+        PeerExchange px;
+        if (direct) {
+            px = comm->peer_exchange((int)(it & 1));
+        } else if (multi) { // the only exchange of an iteration, ~144 KiB
             if (buf.counts_f32) {
                 comm->allreduce_sum_f32(buf.sums, words);
             } else {
@@ -149,7 +167,7 @@ void lbg_fit(Device &dev, Comm *comm, const Shape &sh, const float *x, size_t ma
                 gg.close();
             }
         }
-        dev.update_centroids(sh, buf, act.as<uint32_t>(), centroids, status); // 95-99; flags on the host when it returns
+        dev.update_centroids(sh, buf, act.as<uint32_t>(), centroids, status, direct ? &px : nullptr); // 95-99; flags on the host when it returns
         patches.clear();
         for (size_t s = 0; s < m; ++s) {
             if (!active[s]) continue;

@@ -1,12 +1,13 @@
 // iter_status.cuh -- how the centroid-update kernels hand one k-means iteration's flags to the host.
 //
 // The host needs, once per iteration, the "some row moved" word of every sub-space and the set of clusters that received
-// no row (src/utils.rs:76-80,95-106).  The update kernels write them straight into a page of mapped pinned host memory and
-// then publish a sequence number; the host polls that word, so no copy is queued and no stream is synchronised:
-//   word 0            sequence number of the last finished update
-//   word 1            the tensor-core kernels' error word at that time (0 = no bounded wait expired)
-//   words 4 .. 4+m    moved[s]
-//   then m x wps      bitmap, bit j of sub-space s = cluster j is empty   (wps = ceil(k / 32))
+// no row (src/utils.rs:76-80,95-106).  The update kernels write them straight into a page of mapped pinned host memory,
+// which the host polls, so no copy is queued and no stream is synchronised.  Every entry of the page is one aligned 64-bit
+// word (sequence number of the update << 32) | value, stored with a single instruction: the host accepts an entry when
+// it carries the number it is waiting for, so the kernels need neither fences nor a "last CTA" count.
+//   entry 0            the tensor-core kernels' error word (0 = no bounded wait expired)
+//   entries 1 .. m     moved[s]
+//   then m x wps       bitmap, bit j of sub-space s = cluster j is empty   (wps = ceil(k / 32))
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -14,35 +15,22 @@
 namespace vqb {
 
 struct StatusPage {
-    uint32_t *host_words;       // device-side address of the mapped page
-    unsigned int *done_counter; // device memory, zero between launches
-    const int *tc_error;        // device memory, may be null
-    uint32_t seq;               // value to publish
-    uint32_t total_blocks;      // CTAs of the publishing launch
+    unsigned long long *host_words; // device-side address of the mapped page
+    const int *tc_error;            // device memory, may be null
+    uint32_t seq;                   // number of this update
     uint32_t m, words_per_subspace;
-    __host__ __device__ uint32_t *host_moved() const { return host_words + 4; }
-    __host__ __device__ uint32_t *host_bitmap() const { return host_words + 4 + m; }
-    static size_t words(size_t m, size_t k) { return 4 + m + m * ((k + 31) / 32); }
-};
-
+    __host__ __device__ size_t idx_error() const { return 0; }
+    __host__ __device__ size_t idx_moved(size_t s) const { return 1 + s; }
+    __host__ __device__ size_t idx_bitmap(size_t s, size_t w) const { return 1 + m + s * words_per_subspace + w; }
+    static size_t words(size_t m, size_t k) { return 1 + m + m * ((k + 31) / 32); }
 #ifdef __CUDACC__
-// Every thread of every CTA calls this at the end of the kernel; `wrote` = this thread stored something into the page.  Only
-// those threads pay for a system-scope fence (the others may have a hundred bytes of ordinary global stores in flight, which
-// the next kernel on the stream sees anyway).  The last CTA to arrive publishes the sequence number.
-__device__ __forceinline__ void status_publish(const StatusPage &sp, bool wrote)
-{
-    if (wrote) __threadfence_system(); // this thread's page writes are visible to the host before anything that follows
-    __syncthreads();
-    if (threadIdx.x == 0 && threadIdx.y == 0) {
-        __threadfence_system(); // orders what the barrier made visible to this thread before the arrival below
-        if (atomicAdd(sp.done_counter, 1u) == sp.total_blocks - 1u) {
-            *sp.done_counter = 0u; // the next launch on the stream starts from zero again
-            sp.host_words[1] = sp.tc_error ? (uint32_t)*sp.tc_error : 0u;
-            __threadfence_system();
-            *reinterpret_cast<volatile uint32_t *>(sp.host_words) = sp.seq;
-        }
+    __device__ __forceinline__ void put(size_t idx, uint32_t value) const
+    {
+        *reinterpret_cast<volatile unsigned long long *>(host_words + idx) = ((unsigned long long)seq << 32) | value;
     }
-}
+    // one thread of the launch, after its own work: the error word as it stands
+    __device__ __forceinline__ void put_error() const { put(idx_error(), tc_error ? (uint32_t)*reinterpret_cast<const volatile int *>(tc_error) : 0u); }
 #endif
+};
 
 } // namespace vqb

@@ -711,11 +711,14 @@ void launch_pq_tc(CudaDevice &dev, const AssignParams &p, int metric, bool train
 // assignment pass needs, the iteration's flags for the host, and the sums / counts / flags cleared for the next iteration.
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(BN) pq_update_centroids_kernel(float *sums, uint32_t *counts, uint32_t *moved, int counts_f32, const uint32_t *active,
-                                                                 int k, float *centroids, float *bop, uint4 *c16, float *hnmax, StatusPage sp)
+                                                                 int k, float *centroids, float *bop, uint4 *c16, float *hnmax, StatusPage sp,
+                                                                 const PeerView pv)
 {
     __shared__ float smax[BN];
     const int s = blockIdx.x, j = threadIdx.x;
     const bool act = !active || active[s] != 0;
+    const bool direct = pv.world > 1; // the parts of all ranks are added here, in rank order (peer_exchange.cuh)
+    peer_arrive_and_wait(pv);
     bool empty = false;
     if (act) {
         float4 out[8];
@@ -727,18 +730,44 @@ __global__ void __launch_bounds__(BN) pq_update_centroids_kernel(float *sums, ui
             const size_t cj = (size_t)s * k + j;
             float4 *cp = reinterpret_cast<float4 *>(centroids + cj * SDW);
             float4 *sp4 = reinterpret_cast<float4 *>(sums + cj * SDW);
-            const uint32_t cw = counts[cj];
-            const float cf = counts_f32 ? __uint_as_float(cw) : __uint2float_rn(cw);
+            float4 a, b;
+            float cf;
+            if (direct) {
+                uint32_t cnt = 0;
+                a = b = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int q = 0; q < VQB_MAX_PEERS; ++q) {
+                    if (q >= pv.world) break;
+                    const uint32_t *w = pv.words[q];
+                    const float4 pa = peer_ld4(w + cj * SDW), pb = peer_ld4(w + cj * SDW + 4);
+                    cnt += peer_ld(w + pv.off_counts + cj);
+                    if (q == 0) {
+                        a = pa, b = pb;
+                    } else {
+                        a.x = __fadd_rn(a.x, pa.x), a.y = __fadd_rn(a.y, pa.y), a.z = __fadd_rn(a.z, pa.z), a.w = __fadd_rn(a.w, pa.w);
+                        b.x = __fadd_rn(b.x, pb.x), b.y = __fadd_rn(b.y, pb.y), b.z = __fadd_rn(b.z, pb.z), b.w = __fadd_rn(b.w, pb.w);
+                    }
+                }
+                cf = __uint2float_rn(cnt);
+                float4 *st4 = reinterpret_cast<float4 *>(pv.stale + cj * SDW);
+                st4[0] = st4[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                pv.stale[pv.off_counts + cj] = 0u;
+            } else {
+                const uint32_t cw = counts[cj];
+                cf = counts_f32 ? __uint_as_float(cw) : __uint2float_rn(cw);
+                a = sp4[0], b = sp4[1];
+            }
             float4 c0, c1;
             if (cf != 0.0f) {
-                const float4 a = sp4[0], b = sp4[1];
                 c0 = make_float4(__fdiv_rn(a.x, cf), __fdiv_rn(a.y, cf), __fdiv_rn(a.z, cf), __fdiv_rn(a.w, cf));
                 c1 = make_float4(__fdiv_rn(b.x, cf), __fdiv_rn(b.y, cf), __fdiv_rn(b.z, cf), __fdiv_rn(b.w, cf));
                 cp[0] = c0;
                 cp[1] = c1;
-                sp4[0] = make_float4(0.f, 0.f, 0.f, 0.f);
-                sp4[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-                counts[cj] = 0u;
+                if (!direct) {
+                    sp4[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    sp4[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    counts[cj] = 0u;
+                }
             } else { // an empty cluster keeps its centroid until the host re-seeds it (src/utils.rs:99-101)
                 empty = true;
                 c0 = cp[0];
@@ -780,20 +809,27 @@ __global__ void __launch_bounds__(BN) pq_update_centroids_kernel(float *sums, ui
     }
     // flags of this sub-space for the host: 8 bitmap words (bit = cluster without rows) and the "some row moved" word
     const uint32_t bits = __ballot_sync(0xffffffffu, empty);
-    if ((j & 31) == 0) sp.host_bitmap()[(size_t)s * sp.words_per_subspace + (j >> 5)] = bits;
+    if ((j & 31) == 0 && (uint32_t)(j >> 5) < sp.words_per_subspace) sp.put(sp.idx_bitmap(s, j >> 5), bits);
     if (j == 0) {
-        sp.host_moved()[s] = act ? moved[s] : 0u;
-        moved[s] = 0u;
+        uint32_t mv = 0u;
+        if (direct) {
+            for (int q = 0; q < pv.world; ++q) mv |= peer_ld(pv.words[q] + pv.off_moved + s);
+            pv.stale[pv.off_moved + s] = 0u;
+        } else {
+            mv = moved[s];
+            moved[s] = 0u;
+        }
+        sp.put(sp.idx_moved(s), act ? mv : 0u);
+        if (s == 0) sp.put_error();
     }
-    status_publish(sp, (j & 31) == 0);
 }
 
 void launch_pq_update_centroids(CudaDevice &dev, int m, int k, float *sums, uint32_t *counts, uint32_t *moved, bool counts_f32,
-                                const uint32_t *active, float *centroids, float *scratch, const StatusPage &sp)
+                                const uint32_t *active, float *centroids, float *scratch, const StatusPage &sp, const PeerView &pv)
 {
     KernelScope ks(dev, "update_centroids");
     pq_update_centroids_kernel<<<m, BN, 0, dev.stream()>>>(sums, counts, moved, counts_f32 ? 1 : 0, active, k, centroids, scratch + OFF_BOP,
-                                                            reinterpret_cast<uint4 *>(scratch + OFF_C16), scratch + OFF_HMAX, sp);
+                                                            reinterpret_cast<uint4 *>(scratch + OFF_C16), scratch + OFF_HMAX, sp, pv);
     VQB_CUDA_CHECK(cudaGetLastError());
     dev.count_launch();
 }

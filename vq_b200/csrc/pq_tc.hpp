@@ -4,6 +4,7 @@
 #include <cstdint>
 
 #include "iter_status.cuh"
+#include "peer_exchange.cuh"
 
 namespace vqb {
 
@@ -29,6 +30,6 @@ void launch_pq_tc(CudaDevice &dev, const AssignParams &p, int metric, bool train
 size_t pq_tc_stats_offset_floats();
 // centroid update + operand B of the next pass + the iteration's flags, one launch (m CTAs)
 void launch_pq_update_centroids(CudaDevice &dev, int m, int k, float *sums, uint32_t *counts, uint32_t *moved, bool counts_f32,
-                                const uint32_t *active, float *centroids, float *scratch, const StatusPage &sp);
+                                const uint32_t *active, float *centroids, float *scratch, const StatusPage &sp, const PeerView &pv);
 
 } // namespace vqb
