@@ -277,18 +277,44 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
     }
 }
 
+// Reference distance of one row (xcol, stride XT_STRIDE) to two centroids at once: two independent serial chains.
+#define XT_STRIDE 17
+__device__ __forceinline__ void exact_dist2(const float *xcol, const float *c0, const float *c1, int dim, bool euclid, float (&out)[2])
+{
+    float a0 = 0.0f, a1 = 0.0f;
+    for (int i0 = 0; i0 < dim; i0 += 8) {
+        float xv[8], v0[8], v1[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            xv[u] = xcol[(i0 + u) * XT_STRIDE];
+            v0[u] = c0[i0 + u], v1[u] = c1[i0 + u];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float d0 = __fsub_rn(xv[u], v0[u]), d1 = __fsub_rn(xv[u], v1[u]);
+            a0 = __fadd_rn(a0, __fmul_rn(d0, d0));
+            a1 = __fadd_rn(a1, __fmul_rn(d1, d1));
+        }
+    }
+    out[0] = euclid ? __fsqrt_rn(a0) : a0;
+    out[1] = euclid ? __fsqrt_rn(a1) : a1;
+}
+
 // Training assignment, two passes per block of 256 rows.  Pass A reads only the shortlists: a row with a single candidate is
 // decided at once (that candidate is the reference's choice), the others are collected in a per-warp list.  Pass B stages
-// just the listed rows and runs the exact arithmetic with every lane busy.  After the first k-means iterations most rows have
-// one candidate, so most of the row matrix is never read here.
-template <typename CodeT> __global__ void __launch_bounds__(128, 1) resolve_train_kernel(const ResolveParams P)
+// the listed rows 16 at a time and gives every row TWO lanes, each of which evaluates two of the row's next four candidates
+// with the exact arithmetic; the pair then goes through the four distances in ascending centroid order like the reference.
+// Sixteen-row groups halve a warp's staging buffer, which is what lets ten warps instead of four sit beside the 132 KB
+// codebook: with one warp per scheduler the serial chains ran at a quarter of the issue rate.
+constexpr int RT_MAX_WARPS = 12;
+template <typename CodeT> __global__ void __launch_bounds__(32 * RT_MAX_WARPS, 1) resolve_train_kernel(const ResolveParams P)
 {
     extern __shared__ __align__(16) float smem[];
     const int dim = P.dim, k = P.k, cstride = dim + 1;
     const int W = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float *cpad = smem;                                                                   // [k][dim + 1]
-    float *xs = smem + (size_t)k * cstride + (size_t)warp * dim * XS_STRIDE;              // [dim][33] per warp
-    uint16_t *list = reinterpret_cast<uint16_t *>(smem + (size_t)k * cstride + (size_t)W * dim * XS_STRIDE) + warp * 256; // [256] per warp
+    float *xs = smem + (size_t)k * cstride + (size_t)warp * dim * XT_STRIDE;              // [dim][17] per warp
+    uint16_t *list = reinterpret_cast<uint16_t *>(smem + (size_t)k * cstride + (size_t)W * dim * XT_STRIDE) + warp * 256; // [256] per warp
     {
         const int total4 = k * dim / 4, dim4 = dim / 4;
         const float4 *src = reinterpret_cast<const float4 *>(P.codebook);
@@ -314,6 +340,7 @@ template <typename CodeT> __global__ void __launch_bounds__(128, 1) resolve_trai
     const unsigned long long blocks = (P.n + 255) / 256;
     bool moved = false;
     CodeT *codes = reinterpret_cast<CodeT *>(P.codes);
+    const int r = lane & 15, half = lane >> 4;
     for (unsigned long long blk = (unsigned long long)blockIdx.x * W + warp; blk < blocks; blk += (unsigned long long)gridDim.x * W) {
         const unsigned long long base = blk * 256;
         // ---- pass A
@@ -342,37 +369,37 @@ template <typename CodeT> __global__ void __launch_bounds__(128, 1) resolve_trai
             cnt += __popc(bal);
         }
         __syncwarp();
-        // ---- pass B: 32 listed rows at a time; the next group's rows are requested into registers while this one is evaluated
+        // ---- pass B: 16 listed rows at a time; the next group's rows are requested into registers while this one is evaluated
         const int dim4 = dim / 4;
-        float4 pre[32];
+        float4 pre[16];
         auto request = [&](int i0) {
-            const int nb = min(32, cnt - i0), total4 = nb * dim4;
+            const int nb = min(16, cnt - i0), total4 = nb * dim4;
 #pragma unroll
-            for (int u = 0; u < 32; ++u) {
+            for (int u = 0; u < 16; ++u) {
                 const int idx = u * 32 + lane;
                 pre[u] = (i0 < cnt && idx < total4) ? __ldg(reinterpret_cast<const float4 *>(P.x + (base + list[i0 + idx / dim4]) * dim) + idx % dim4)
                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         };
         if (cnt > 0) request(0);
-        for (int i0 = 0; i0 < cnt; i0 += 32) {
-            const int nb = min(32, cnt - i0);
+        for (int i0 = 0; i0 < cnt; i0 += 16) {
+            const int nb = min(16, cnt - i0);
             {
                 const int total4 = nb * dim4;
 #pragma unroll
-                for (int u = 0; u < 32; ++u) {
+                for (int u = 0; u < 16; ++u) {
                     const int idx = u * 32 + lane;
                     if (idx < total4) {
-                        float *d = xs + (size_t)(idx % dim4) * 4 * XS_STRIDE + idx / dim4;
-                        d[0] = pre[u].x, d[XS_STRIDE] = pre[u].y, d[2 * XS_STRIDE] = pre[u].z, d[3 * XS_STRIDE] = pre[u].w;
+                        float *d = xs + (size_t)(idx % dim4) * 4 * XT_STRIDE + idx / dim4;
+                        d[0] = pre[u].x, d[XT_STRIDE] = pre[u].y, d[2 * XT_STRIDE] = pre[u].z, d[3 * XT_STRIDE] = pre[u].w;
                     }
                 }
             }
-            request(i0 + 32);
+            request(i0 + 16);
             __syncwarp();
-            const bool valid = lane < nb;
-            const unsigned long long row = valid ? base + list[i0 + lane] : 0ull;
-            const float *xcol = xs + lane;
+            const bool valid = r < nb; // both lanes of a row agree on everything below
+            const unsigned long long row = valid ? base + list[i0 + r] : 0ull;
+            const float *xcol = xs + r;
             int best = 0, ncand = 0;
             uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             if (valid) {
@@ -383,11 +410,11 @@ template <typename CodeT> __global__ void __launch_bounds__(128, 1) resolve_trai
             }
             // rows with many candidates (or marked "examine all"): the whole warp scans all centroids, as in resolve_kernel
             const bool wide = valid && (ncand > 12 || ncand == 0);
-            unsigned wide_rows = __ballot_sync(0xffffffffu, wide);
+            unsigned wide_rows = __ballot_sync(0xffffffffu, wide) & 0xFFFFu;
             while (wide_rows) {
-                const int r = __ffs(wide_rows) - 1;
+                const int wr = __ffs(wide_rows) - 1;
                 wide_rows &= wide_rows - 1;
-                const float *xr = xs + r;
+                const float *xr = xs + wr;
                 float bd = VQB_DENSE_INF, d0 = 0.0f;
                 int bi = 0x7fffffff;
                 for (int j = lane; j < k; j += 32) {
@@ -395,7 +422,7 @@ template <typename CodeT> __global__ void __launch_bounds__(128, 1) resolve_trai
                     float acc = 0.0f;
 #pragma unroll 8
                     for (int i = 0; i < dim; ++i) {
-                        const float d = __fsub_rn(xr[i * XS_STRIDE], c[i]);
+                        const float d = __fsub_rn(xr[i * XT_STRIDE], c[i]);
                         acc = __fadd_rn(acc, __fmul_rn(d, d));
                     }
                     const float d = euclid ? __fsqrt_rn(acc) : acc;
@@ -418,35 +445,36 @@ template <typename CodeT> __global__ void __launch_bounds__(128, 1) resolve_trai
                 int res = (bi == 0x7fffffff) ? 0 : bi;
                 if (!(d0 == d0)) res = 0;
                 if (bd == VQB_DENSE_INF) res = 0;
-                if (lane == r) best = res;
+                if (r == wr) best = res;
             }
-            if (valid) {
-                if (!wide) {
-                    float bd = VQB_DENSE_INF;
-                    int bi = -1;
-                    int j = next_bit(w, 0);
-                    while (j < k) {
-                        int js[4];
-                        js[0] = j;
+            // the other rows: rounds of four candidates, two per lane of the pair
+            float bd = VQB_DENSE_INF;
+            int bi = -1;
+            int j = (valid && !wide) ? next_bit(w, 0) : 256;
+            while (__any_sync(0xffffffffu, j < k)) {
+                int js[4];
+                js[0] = j;
 #pragma unroll
-                        for (int t = 1; t < 4; ++t) js[t] = (js[t - 1] < 256) ? next_bit(w, js[t - 1] + 1) : 256;
-                        float d[4];
-                        exact_dist4(xcol, cpad + (size_t)min(js[0], k - 1) * cstride, cpad + (size_t)min(js[1], k - 1) * cstride,
-                                    cpad + (size_t)min(js[2], k - 1) * cstride, cpad + (size_t)min(js[3], k - 1) * cstride, dim, euclid, d);
+                for (int t = 1; t < 4; ++t) js[t] = (js[t - 1] < 256) ? next_bit(w, js[t - 1] + 1) : 256;
+                const int ja = half ? js[2] : js[0], jb = half ? js[3] : js[1];
+                float mine[2];
+                exact_dist2(xcol, cpad + (size_t)min(ja, k - 1) * cstride, cpad + (size_t)min(jb, k - 1) * cstride, dim, euclid, mine);
+                const float o0 = __shfl_xor_sync(0xffffffffu, mine[0], 16), o1 = __shfl_xor_sync(0xffffffffu, mine[1], 16);
+                const float d[4] = {half ? o0 : mine[0], half ? o1 : mine[1], half ? mine[0] : o0, half ? mine[1] : o1};
 #pragma unroll
-                        for (int t = 0; t < 4; ++t) {
-                            if (js[t] >= k) break;
-                            if (js[t] == 0) {
-                                bd = d[t];
-                                bi = 0;
-                            } else {
-                                argmin_update(d[t], js[t], bd, bi);
-                            }
-                        }
-                        j = (js[3] < 256) ? next_bit(w, js[3] + 1) : 256;
+                for (int t = 0; t < 4; ++t) {
+                    if (js[t] >= k) break;
+                    if (js[t] == 0) {
+                        bd = d[t];
+                        bi = 0;
+                    } else {
+                        argmin_update(d[t], js[t], bd, bi);
                     }
-                    best = bi < 0 ? 0 : bi;
                 }
+                j = (js[3] < 256) ? next_bit(w, js[3] + 1) : 256;
+            }
+            if (valid && half == 0) {
+                if (!wide) best = bi < 0 ? 0 : bi;
                 const CodeT nc = (CodeT)best;
                 if (codes[row] != nc) moved = true;
                 codes[row] = nc;
@@ -473,12 +501,16 @@ template <int MODE, typename CodeT> void launch_t(CudaDevice &dev, const Resolve
 
 template <typename CodeT> void launch_train(CudaDevice &dev, const ResolveParams &p)
 {
-    const int threads = 128;
-    const size_t smem = ((size_t)p.k * (p.dim + 1) + (size_t)(threads / 32) * p.dim * XS_STRIDE) * sizeof(float) + (size_t)(threads / 32) * 256 * sizeof(uint16_t);
+    // as many warps as fit beside the padded codebook (ten at k = 256, dim = 128)
+    const size_t book = (size_t)p.k * (p.dim + 1) * sizeof(float), per_warp = (size_t)p.dim * XT_STRIDE * sizeof(float) + 256 * sizeof(uint16_t);
+    const size_t budget = 226 * 1024;
+    const int warps = (int)std::max<size_t>(1, std::min<size_t>(RT_MAX_WARPS, book < budget ? (budget - book) / per_warp : 1));
+    const int threads = 32 * warps;
+    const size_t smem = book + (size_t)warps * per_warp;
     auto kernel = resolve_train_kernel<CodeT>;
     VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const unsigned long long blocks = (p.n + 255) / 256;
-    const unsigned grid = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((blocks + 3) / 4, (unsigned long long)dev.sm_count()));
+    const unsigned grid = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((blocks + warps - 1) / warps, (unsigned long long)dev.sm_count()));
     KernelScope ks(dev, "resolve_train");
     kernel<<<grid, threads, smem, dev.stream()>>>(p);
     VQB_CUDA_CHECK(cudaGetLastError());
