@@ -15,39 +15,6 @@ namespace vqb {
 
 namespace {
 
-#define XS_STRIDE 33
-
-// Reference distance of this lane's row (xcol, stride 33) to up to four centroids at once: four independent serial
-// chains, each in the reference's order over dimensions.
-__device__ __forceinline__ void exact_dist4(const float *xcol, const float *c0, const float *c1, const float *c2, const float *c3,
-                                            int dim, bool euclid, float (&out)[4])
-{
-    // dim is a multiple of 32 on this path.  Eight dimensions per trip: their 40 shared-memory loads are issued together, so the
-    // serial chains below wait for shared memory once per eight steps instead of once per step (one warp per scheduler cannot
-    // hide that latency any other way).
-    float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
-    for (int i0 = 0; i0 < dim; i0 += 8) {
-        float xv[8], v0[8], v1[8], v2[8], v3[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            xv[u] = xcol[(i0 + u) * XS_STRIDE];
-            v0[u] = c0[i0 + u], v1[u] = c1[i0 + u], v2[u] = c2[i0 + u], v3[u] = c3[i0 + u];
-        }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const float d0 = __fsub_rn(xv[u], v0[u]), d1 = __fsub_rn(xv[u], v1[u]), d2 = __fsub_rn(xv[u], v2[u]), d3 = __fsub_rn(xv[u], v3[u]);
-            a0 = __fadd_rn(a0, __fmul_rn(d0, d0));
-            a1 = __fadd_rn(a1, __fmul_rn(d1, d1));
-            a2 = __fadd_rn(a2, __fmul_rn(d2, d2));
-            a3 = __fadd_rn(a3, __fmul_rn(d3, d3));
-        }
-    }
-    out[0] = euclid ? __fsqrt_rn(a0) : a0;
-    out[1] = euclid ? __fsqrt_rn(a1) : a1;
-    out[2] = euclid ? __fsqrt_rn(a2) : a2;
-    out[3] = euclid ? __fsqrt_rn(a3) : a3;
-}
-
 // Index of the lowest set bit at or above `from` in a 256-bit mask, or 256.
 __device__ __forceinline__ int next_bit(const uint32_t (&w)[8], int from)
 {
@@ -59,13 +26,40 @@ __device__ __forceinline__ int next_bit(const uint32_t (&w)[8], int from)
     return 256;
 }
 
-template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) resolve_kernel(const ResolveParams P)
+// Reference distance of one row (xcol, stride XT_STRIDE) to two centroids at once: two independent serial chains.
+#define XT_STRIDE 17
+__device__ __forceinline__ void exact_dist2(const float *xcol, const float *c0, const float *c1, int dim, bool euclid, float (&out)[2])
+{
+    float a0 = 0.0f, a1 = 0.0f;
+    for (int i0 = 0; i0 < dim; i0 += 8) {
+        float xv[8], v0[8], v1[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            xv[u] = xcol[(i0 + u) * XT_STRIDE];
+            v0[u] = c0[i0 + u], v1[u] = c1[i0 + u];
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float d0 = __fsub_rn(xv[u], v0[u]), d1 = __fsub_rn(xv[u], v1[u]);
+            a0 = __fadd_rn(a0, __fmul_rn(d0, d0));
+            a1 = __fadd_rn(a1, __fmul_rn(d1, d1));
+        }
+    }
+    out[0] = euclid ? __fsqrt_rn(a0) : a0;
+    out[1] = euclid ? __fsqrt_rn(a1) : a1;
+}
+
+// Tiles of 16 rows, two lanes per row (see resolve_train_kernel below for why): both lanes of a row evaluate two of its next
+// four candidates each and walk through the four distances in ascending centroid order; the row's epilogue (residual, norm,
+// flags) is the first lane's.
+constexpr int RT_MAX_WARPS = 12;
+template <int MODE, typename CodeT> __global__ void __launch_bounds__(32 * RT_MAX_WARPS, 1) resolve_kernel(const ResolveParams P)
 {
     extern __shared__ __align__(16) float smem[];
     const int dim = P.dim, k = P.k, cstride = dim + 1; // odd stride: lanes reading different centroids hit different banks
     const int W = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float *cpad = smem;                                   // [k][dim + 1]
-    float *xs = smem + (size_t)k * cstride + (size_t)warp * dim * XS_STRIDE; // [dim][33] per warp
+    float *xs = smem + (size_t)k * cstride + (size_t)warp * dim * XT_STRIDE; // [dim][17] per warp
     {
         // codebook -> shared memory, eight 128-bit loads in flight per thread (dim is a multiple of 4 on this path)
         const int total4 = k * dim / 4, dim4 = dim / 4;
@@ -89,18 +83,18 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
     }
     __syncthreads();
     const bool euclid = P.euclid != 0;
-    const unsigned long long tiles = (P.n + 31) / 32;
+    const unsigned long long tiles = (P.n + 15) / 16;
     bool moved = false;
     double warp_norm = 0.0;
+    const int r = lane & 15, half = lane >> 4;
 
-    // A warp's next tile (32 rows, up to 16 KiB) is requested into registers while the current one is worked on: with only the
-    // current tile's loads in flight and four warps per SM the kernel ran at the pace of the memory latency.
-    const int dim4 = dim / 4, total4 = 32 * dim4;
-    float4 pre[32];
+    // A warp's next tile (16 rows, up to 8 KiB) is requested into registers while the current one is worked on.
+    const int dim4 = dim / 4, total4 = 16 * dim4;
+    float4 pre[16];
     auto request = [&](unsigned long long tile) {
-        const unsigned long long r0 = tile * 32;
+        const unsigned long long r0 = tile * 16;
 #pragma unroll
-        for (int u = 0; u < 32; ++u) {
+        for (int u = 0; u < 16; ++u) {
             const int idx = u * 32 + lane;
             const unsigned long long rr = r0 + idx / dim4;
             pre[u] = (tile < tiles && idx < total4 && rr < P.n) ? __ldg(reinterpret_cast<const float4 *>(P.x + rr * dim) + idx % dim4)
@@ -109,22 +103,22 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
     };
     request((unsigned long long)blockIdx.x * W + warp);
     for (unsigned long long tile = (unsigned long long)blockIdx.x * W + warp; tile < tiles; tile += (unsigned long long)gridDim.x * W) {
-        const unsigned long long row0 = tile * 32, row = row0 + lane;
+        const unsigned long long row0 = tile * 16, row = row0 + r;
         const bool valid = row < P.n;
         bool skip = false;
         if (MODE == R_RVQ_STAGE && valid) skip = P.done[row] != 0;
-        // stage the 32 rows dimension-major (lanes walked along a row when they were loaded: coalesced), then ask for the next tile
+        // stage the 16 rows dimension-major (lanes walked along a row when they were loaded: coalesced), then ask for the next tile
 #pragma unroll
-        for (int u = 0; u < 32; ++u) {
+        for (int u = 0; u < 16; ++u) {
             const int idx = u * 32 + lane;
             if (idx < total4) {
-                float *d = xs + (size_t)(idx % dim4) * 4 * XS_STRIDE + idx / dim4;
-                d[0] = pre[u].x, d[XS_STRIDE] = pre[u].y, d[2 * XS_STRIDE] = pre[u].z, d[3 * XS_STRIDE] = pre[u].w;
+                float *d = xs + (size_t)(idx % dim4) * 4 * XT_STRIDE + idx / dim4;
+                d[0] = pre[u].x, d[XT_STRIDE] = pre[u].y, d[2 * XT_STRIDE] = pre[u].z, d[3 * XT_STRIDE] = pre[u].w;
             }
         }
         request(tile + (unsigned long long)gridDim.x * W);
         __syncwarp();
-        const float *xcol = xs + lane;
+        const float *xcol = xs + r;
         int best = 0;
         uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         int ncand = 0;
@@ -138,11 +132,11 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
         // L, L+32, ... in ascending order, then the warp keeps the smallest distance, lowest index on ties.  A NaN never
         // wins in the reference unless it sits at centroid 0, where the scan starts.
         const bool wide = ncand > 12;
-        unsigned wide_rows = __ballot_sync(0xffffffffu, wide);
+        unsigned wide_rows = __ballot_sync(0xffffffffu, wide) & 0xFFFFu;
         while (wide_rows) {
-            const int r = __ffs(wide_rows) - 1;
+            const int wr = __ffs(wide_rows) - 1;
             wide_rows &= wide_rows - 1;
-            const float *xr = xs + r;
+            const float *xr = xs + wr;
             float bd = VQB_DENSE_INF;
             int bi = 0x7fffffff;
             float d0 = 0.0f;
@@ -151,7 +145,7 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
                 float acc = 0.0f;
 #pragma unroll 8
                 for (int i = 0; i < dim; ++i) {
-                    const float d = __fsub_rn(xr[i * XS_STRIDE], c[i]);
+                    const float d = __fsub_rn(xr[i * XT_STRIDE], c[i]);
                     acc = __fadd_rn(acc, __fmul_rn(d, d));
                 }
                 const float d = euclid ? __fsqrt_rn(acc) : acc;
@@ -174,36 +168,38 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
             int res = (bi == 0x7fffffff) ? 0 : bi; // nothing finite below +inf: the reference keeps centroid 0
             if (!(d0 == d0)) res = 0;               // NaN at centroid 0: nothing ever replaces it (src/utils.rs:62-66)
             if (bd == VQB_DENSE_INF) res = 0;       // all distances +inf (or NaN): strict '<' never fires
-            if (lane == r) best = res;
+            if (r == wr) best = res;
         }
-        if (valid && !skip) {
-            if (!wide) {
-                float bd = VQB_DENSE_INF;
-                int bi = -1;
-                int j = next_bit(w, 0);
-                while (j < k) {
-                    int js[4];
-                    js[0] = j;
+        // the other rows: rounds of four candidates, two per lane of the pair; every lane of the warp takes part in a round
+        {
+            float bd = VQB_DENSE_INF;
+            int bi = -1;
+            int j = (valid && !skip && !wide) ? next_bit(w, 0) : 256;
+            while (__any_sync(0xffffffffu, j < k)) {
+                int js[4];
+                js[0] = j;
 #pragma unroll
-                    for (int t = 1; t < 4; ++t) js[t] = (js[t - 1] < 256) ? next_bit(w, js[t - 1] + 1) : 256;
-                    float d[4];
-                    exact_dist4(xcol, cpad + (size_t)min(js[0], k - 1) * cstride, cpad + (size_t)min(js[1], k - 1) * cstride,
-                                cpad + (size_t)min(js[2], k - 1) * cstride, cpad + (size_t)min(js[3], k - 1) * cstride, dim, euclid, d);
+                for (int t = 1; t < 4; ++t) js[t] = (js[t - 1] < 256) ? next_bit(w, js[t - 1] + 1) : 256;
+                const int ja = half ? js[2] : js[0], jb = half ? js[3] : js[1];
+                float mine[2];
+                exact_dist2(xcol, cpad + (size_t)min(ja, k - 1) * cstride, cpad + (size_t)min(jb, k - 1) * cstride, dim, euclid, mine);
+                const float o0 = __shfl_xor_sync(0xffffffffu, mine[0], 16), o1 = __shfl_xor_sync(0xffffffffu, mine[1], 16);
+                const float d[4] = {half ? o0 : mine[0], half ? o1 : mine[1], half ? mine[0] : o0, half ? mine[1] : o1};
 #pragma unroll
-                    for (int t = 0; t < 4; ++t) {
-                        if (js[t] >= k) break;
-                        if (js[t] == 0) { // the reference's scan starts at centroid 0 whatever its value
-                            bd = d[t];
-                            bi = 0;
-                        } else {
-                            argmin_update(d[t], js[t], bd, bi); // a skipped centroid 0 is provably farther than the winner
-                        }
+                for (int t = 0; t < 4; ++t) {
+                    if (js[t] >= k) break;
+                    if (js[t] == 0) { // the reference's scan starts at centroid 0 whatever its value
+                        bd = d[t];
+                        bi = 0;
+                    } else {
+                        argmin_update(d[t], js[t], bd, bi); // a skipped centroid 0 is provably farther than the winner
                     }
-                    j = (js[3] < 256) ? next_bit(w, js[3] + 1) : 256;
                 }
-                best = bi < 0 ? 0 : bi;
+                j = (js[3] < 256) ? next_bit(w, js[3] + 1) : 256;
             }
-
+            if (valid && !skip && !wide) best = bi < 0 ? 0 : bi;
+        }
+        if (valid && !skip && half == 0) {
             if (MODE == R_TRAIN) {
                 CodeT *cp = reinterpret_cast<CodeT *>(P.codes) + row;
                 const CodeT nc = (CodeT)best;
@@ -214,9 +210,9 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
                 float nsq = 0.0f;
 #pragma unroll 8
                 for (int i = 0; i < dim; ++i) {
-                    const float r = __fsub_rn(xs[i * XS_STRIDE + lane], cw[i]);
-                    xs[i * XS_STRIDE + lane] = r;
-                    nsq = __fadd_rn(nsq, __fmul_rn(r, r));
+                    const float rv = __fsub_rn(xs[i * XT_STRIDE + r], cw[i]);
+                    xs[i * XT_STRIDE + r] = rv;
+                    nsq = __fadd_rn(nsq, __fmul_rn(rv, rv));
                 }
                 const float nrm = __fsqrt_rn(nsq);
                 if (MODE == R_RVQ_UPDATE) warp_norm += (double)nrm;
@@ -231,7 +227,7 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
             const int mybest = (valid && !skip) ? best : -1;
             __syncwarp();
             // four rows per step; the running-sum reads of a step are all issued before any is used
-            for (int r0 = 0; r0 < 32; r0 += 4) {
+            for (int r0 = 0; r0 < 16; r0 += 4) {
                 int b[4];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
@@ -258,7 +254,7 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
                         for (int e = 0; e < 4; ++e) {
                             const int i = i0 + e * 32 + lane;
                             if (i >= dim) continue;
-                            P.res[rr * dim + i] = xs[i * XS_STRIDE + r0 + u];
+                            P.res[rr * dim + i] = xs[i * XT_STRIDE + r0 + u];
                             if (MODE == R_RVQ_STAGE) P.qsum[rr * dim + i] = __fadd_rn(q[u][e], cw[i]);
                         }
                     }
@@ -277,36 +273,12 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(128, 1) re
     }
 }
 
-// Reference distance of one row (xcol, stride XT_STRIDE) to two centroids at once: two independent serial chains.
-#define XT_STRIDE 17
-__device__ __forceinline__ void exact_dist2(const float *xcol, const float *c0, const float *c1, int dim, bool euclid, float (&out)[2])
-{
-    float a0 = 0.0f, a1 = 0.0f;
-    for (int i0 = 0; i0 < dim; i0 += 8) {
-        float xv[8], v0[8], v1[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            xv[u] = xcol[(i0 + u) * XT_STRIDE];
-            v0[u] = c0[i0 + u], v1[u] = c1[i0 + u];
-        }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const float d0 = __fsub_rn(xv[u], v0[u]), d1 = __fsub_rn(xv[u], v1[u]);
-            a0 = __fadd_rn(a0, __fmul_rn(d0, d0));
-            a1 = __fadd_rn(a1, __fmul_rn(d1, d1));
-        }
-    }
-    out[0] = euclid ? __fsqrt_rn(a0) : a0;
-    out[1] = euclid ? __fsqrt_rn(a1) : a1;
-}
-
 // Training assignment, two passes per block of 256 rows.  Pass A reads only the shortlists: a row with a single candidate is
 // decided at once (that candidate is the reference's choice), the others are collected in a per-warp list.  Pass B stages
 // the listed rows 16 at a time and gives every row TWO lanes, each of which evaluates two of the row's next four candidates
 // with the exact arithmetic; the pair then goes through the four distances in ascending centroid order like the reference.
 // Sixteen-row groups halve a warp's staging buffer, which is what lets ten warps instead of four sit beside the 132 KB
 // codebook: with one warp per scheduler the serial chains ran at a quarter of the issue rate.
-constexpr int RT_MAX_WARPS = 12;
 template <typename CodeT> __global__ void __launch_bounds__(32 * RT_MAX_WARPS, 1) resolve_train_kernel(const ResolveParams P)
 {
     extern __shared__ __align__(16) float smem[];
@@ -485,34 +457,40 @@ template <typename CodeT> __global__ void __launch_bounds__(32 * RT_MAX_WARPS, 1
     if (__any_sync(0xffffffffu, moved) && lane == 0) atomicOr(P.changed, VQB_MOVED_BITS);
 }
 
+// as many warps as fit beside the padded codebook (ten at k = 256, dim = 128)
+static int resolve_warps(const ResolveParams &p, size_t extra_per_warp, size_t *smem)
+{
+    const size_t book = (size_t)p.k * (p.dim + 1) * sizeof(float), per_warp = (size_t)p.dim * XT_STRIDE * sizeof(float) + extra_per_warp;
+    const size_t budget = 226 * 1024;
+    const int warps = (int)std::max<size_t>(1, std::min<size_t>(RT_MAX_WARPS, book < budget ? (budget - book) / per_warp : 1));
+    *smem = book + (size_t)warps * per_warp;
+    return warps;
+}
+
 template <int MODE, typename CodeT> void launch_t(CudaDevice &dev, const ResolveParams &p, const char *name)
 {
-    const int threads = 128;
-    const size_t smem = ((size_t)p.k * (p.dim + 1) + (size_t)(threads / 32) * p.dim * XS_STRIDE) * sizeof(float);
+    size_t smem = 0;
+    const int warps = resolve_warps(p, 0, &smem);
     auto kernel = resolve_kernel<MODE, CodeT>;
     VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const unsigned long long tiles = (p.n + 31) / 32;
-    const unsigned grid = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((tiles + 3) / 4, (unsigned long long)dev.sm_count()));
+    const unsigned long long tiles = (p.n + 15) / 16;
+    const unsigned grid = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((tiles + warps - 1) / warps, (unsigned long long)dev.sm_count()));
     KernelScope ks(dev, name);
-    kernel<<<grid, threads, smem, dev.stream()>>>(p);
+    kernel<<<grid, 32 * warps, smem, dev.stream()>>>(p);
     VQB_CUDA_CHECK(cudaGetLastError());
     dev.count_launch();
 }
 
 template <typename CodeT> void launch_train(CudaDevice &dev, const ResolveParams &p)
 {
-    // as many warps as fit beside the padded codebook (ten at k = 256, dim = 128)
-    const size_t book = (size_t)p.k * (p.dim + 1) * sizeof(float), per_warp = (size_t)p.dim * XT_STRIDE * sizeof(float) + 256 * sizeof(uint16_t);
-    const size_t budget = 226 * 1024;
-    const int warps = (int)std::max<size_t>(1, std::min<size_t>(RT_MAX_WARPS, book < budget ? (budget - book) / per_warp : 1));
-    const int threads = 32 * warps;
-    const size_t smem = book + (size_t)warps * per_warp;
+    size_t smem = 0;
+    const int warps = resolve_warps(p, 256 * sizeof(uint16_t), &smem);
     auto kernel = resolve_train_kernel<CodeT>;
     VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const unsigned long long blocks = (p.n + 255) / 256;
     const unsigned grid = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((blocks + warps - 1) / warps, (unsigned long long)dev.sm_count()));
     KernelScope ks(dev, "resolve_train");
-    kernel<<<grid, threads, smem, dev.stream()>>>(p);
+    kernel<<<grid, 32 * warps, smem, dev.stream()>>>(p);
     VQB_CUDA_CHECK(cudaGetLastError());
     dev.count_launch();
 }
