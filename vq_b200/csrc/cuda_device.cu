@@ -781,6 +781,92 @@ __global__ void accum_wide_kernel(const float *x, unsigned long long n, unsigned
     }
 }
 
+// FAST, wide rows in whole 16-byte pieces: the warps of a CTA share out the CLUSTERS (warp w owns the clusters j with
+// j mod W == w), so the per-CTA sums need no atomics at all.  Every warp looks at the codes of a 256-row piece (one byte or
+// word per row), lists the rows of its own clusters, fetches those rows eight at a time (128-bit loads, the lanes along the
+// dimensions) and adds them into shared memory with ordinary 128-bit loads and stores: a lane always touches the same
+// addresses of a cluster, so its own program order keeps repeated clusters right.  The shared-memory atomics of
+// accum_wide_kernel ran at a third of the memory rate (0.22 ms per 1M x 128 rows); what is left here is the row traffic.
+constexpr int AO_PIECE = 256, AO_BATCH = 8, AO_WARPS = 32;
+template <typename CodeT>
+__global__ void __launch_bounds__(32 * AO_WARPS) accum_owner_kernel(const float *__restrict__ x, unsigned long long n, unsigned long long ld, int m, int k,
+                                                                    int sd, const CodeT *__restrict__ codes, const uint32_t *active, float *sums,
+                                                                    uint32_t *counts, int counts_f32)
+{
+    extern __shared__ __align__(16) float smem[];
+    const int s = blockIdx.y;
+    if (active && active[s] == 0) return;
+    float *ssum = smem;                                                    // [k][sd]
+    uint32_t *scnt = reinterpret_cast<uint32_t *>(smem + (size_t)k * sd); // [k]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint32_t *list = scnt + k + warp * AO_PIECE;                           // [AO_PIECE] per warp: row in piece | code << 8
+    float *gsum = sums + (size_t)s * k * sd;
+    uint32_t *gcnt = counts + (size_t)s * k;
+    for (int t = threadIdx.x; t < k * sd; t += blockDim.x) ssum[t] = 0.0f;
+    for (int t = threadIdx.x; t < k; t += blockDim.x) scnt[t] = 0u;
+    __syncthreads();
+    const unsigned long long pieces = (n + AO_PIECE - 1) / AO_PIECE;
+    const float *xs = x + (size_t)s * sd;
+    uint32_t cnext[AO_PIECE / 32];
+    auto fetch_codes = [&](unsigned long long piece) {
+#pragma unroll
+        for (int i = 0; i < AO_PIECE / 32; ++i) {
+            const unsigned long long row = piece * AO_PIECE + i * 32 + lane;
+            cnext[i] = (piece < pieces && row < n) ? (uint32_t)codes[row * m + s] : 0xFFFFFFFFu;
+        }
+    };
+    fetch_codes(blockIdx.x);
+    for (unsigned long long piece = blockIdx.x; piece < pieces; piece += gridDim.x) {
+        const unsigned long long row0 = piece * AO_PIECE;
+        int cnt = 0;
+#pragma unroll
+        for (int i = 0; i < AO_PIECE / 32; ++i) {
+            const uint32_t c = cnext[i];
+            const bool mine = c != 0xFFFFFFFFu && (int)(c % AO_WARPS) == warp;
+            const unsigned bal = __ballot_sync(0xffffffffu, mine);
+            if (mine) list[cnt + __popc(bal & ((1u << lane) - 1u))] = (uint32_t)(i * 32 + lane) | (c << 8);
+            cnt += __popc(bal);
+        }
+        fetch_codes(piece + gridDim.x); // the next piece's codes travel while this piece's rows are added
+        __syncwarp();
+        for (int i0 = 0; i0 < cnt; i0 += AO_BATCH) {
+            for (int d0 = 0; d0 < sd; d0 += 128) {
+                const int d = d0 + 4 * lane;
+                float4 v[AO_BATCH];
+                uint32_t e[AO_BATCH];
+#pragma unroll
+                for (int u = 0; u < AO_BATCH; ++u) {
+                    e[u] = i0 + u < cnt ? list[i0 + u] : 0xFFFFFFFFu;
+                    v[u] = (e[u] != 0xFFFFFFFFu && d < sd) ? __ldg(reinterpret_cast<const float4 *>(xs + (row0 + (e[u] & 0xFFu)) * ld + d))
+                                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int u = 0; u < AO_BATCH; ++u) {
+                    if (e[u] == 0xFFFFFFFFu) continue;
+                    const uint32_t code = e[u] >> 8;
+                    if (d < sd) {
+                        float4 *dst = reinterpret_cast<float4 *>(ssum + (size_t)code * sd + d);
+                        float4 a = *dst;
+                        a.x += v[u].x, a.y += v[u].y, a.z += v[u].z, a.w += v[u].w;
+                        *dst = a;
+                    }
+                    if (d0 == 0 && lane == 0) scnt[code] += 1u;
+                }
+            }
+        }
+        __syncwarp();
+    }
+    __syncthreads();
+    // every CTA starts its flush at another cluster, so that the CTAs that finish together do not queue on the same addresses
+    const int total = k * sd, shift = (int)(((unsigned long long)blockIdx.x * 37u % (unsigned)k) * sd);
+    for (int t0 = threadIdx.x; t0 < total; t0 += blockDim.x) {
+        const int t = t0 + shift < total ? t0 + shift : t0 + shift - total;
+        if (scnt[t / sd] != 0u) atomicAdd(gsum + t, ssum[t]);
+    }
+    for (int t = threadIdx.x; t < k; t += blockDim.x)
+        if (scnt[t] != 0u) add_count(gcnt, (size_t)t, scnt[t], counts_f32);
+}
+
 // ORDERED: one thread per (cluster, dimension) walks all rows in ascending order and adds the members
 // of its cluster, which is exactly the serial branch of mean_vector (src/vector.rs:305-313).
 template <typename CodeT>
@@ -862,6 +948,19 @@ static void accumulate_t(CudaDevice &dev, const Shape &sh, const float *x, const
     }
     const int threads = 512;
     KernelScope ks(dev, "accumulate_fast");
+    const size_t owner_smem = per_sub + (size_t)AO_WARPS * AO_PIECE * sizeof(uint32_t);
+    if (owner_smem <= budget && sd % 4 == 0 && sh.ld % 4 == 0 && sd >= 64 && k >= 2 * AO_WARPS && k <= (1 << 24) &&
+        (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && getenv("VQB_ACCUM_ATOMICS") == nullptr) {
+        auto kernel = accum_owner_kernel<CodeT>;
+        VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)owner_smem));
+        const unsigned long long pieces = (sh.n_local + AO_PIECE - 1) / AO_PIECE;
+        unsigned gx = (unsigned)std::min<unsigned long long>(pieces, (unsigned long long)std::max(1, dev.sm_count() / m));
+        dim3 grid(std::max(1u, gx), m);
+        kernel<<<grid, 32 * AO_WARPS, owner_smem, st>>>(x, sh.n_local, sh.ld, m, k, sd, codes, active, sums, counts, counts_f32);
+        VQB_CUDA_CHECK(cudaGetLastError());
+        dev.count_launch();
+        return;
+    }
     if (per_sub <= budget) {
         auto kernel = accum_wide_kernel<CodeT, true>;
         VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)per_sub));
