@@ -719,111 +719,6 @@ __global__ void accum_small_kernel(const float *x, unsigned long long n, unsigne
         if (scnt[t] != 0u) add_count(counts, (size_t)g0 * k + t, scnt[t], counts_f32);
 }
 
-// FAST, 8-wide sub-spaces (the product quantizer's shape): every THREAD of the CTA owns a few (sub-space, cluster) slots of
-// the per-CTA sums.  A piece of 256 rows is handled in two steps: all threads look at the piece's codes and put each
-// (row, sub-space) pair into its owner's queue (one shared-memory atomic per pair instead of nine); then every thread fetches
-// the 32-byte row slices of its queue and adds them into its own slots with ordinary 128-bit loads and stores.  A pair
-// that finds its owner's queue full is added with atomics right away (the two steps are separated by barriers, so the
-// owner is not touching the slot at that time).
-constexpr int AQ_THREADS = 512, AQ_PIECE = 256, AQ_CAP = 8, AQ_ROUND = 4;
-template <typename CodeT>
-__global__ void __launch_bounds__(AQ_THREADS, 2) accum_queue_kernel(const float *__restrict__ x, unsigned long long n, unsigned long long ld, int m, int k,
-                                                                    int group, const CodeT *__restrict__ codes, const uint32_t *active, float *sums,
-                                                                    uint32_t *counts, int counts_f32)
-{
-    constexpr int SD = 8;
-    extern __shared__ __align__(16) float smem[];
-    const int g0 = blockIdx.y * group;
-    const int gcount = min(group, m - g0);
-    float *ssum = smem;                                                                  // [gcount][k][8]
-    uint32_t *scnt = reinterpret_cast<uint32_t *>(smem + (size_t)group * k * SD);       // [gcount][k]
-    uint32_t *qcount = scnt + (size_t)group * k;                                         // [AQ_THREADS]
-    uint32_t *queue = qcount + AQ_THREADS;                                               // [AQ_THREADS][AQ_CAP]: row in piece | slot << 12
-    const int tid = threadIdx.x;
-    for (int t = tid; t < gcount * k * SD; t += AQ_THREADS) ssum[t] = 0.0f;
-    for (int t = tid; t < gcount * k; t += AQ_THREADS) scnt[t] = 0u;
-    qcount[tid] = 0u;
-    __syncthreads();
-    const unsigned long long pieces = (n + AQ_PIECE - 1) / AQ_PIECE;
-    const int per_thread = (AQ_PIECE * gcount + AQ_THREADS - 1) / AQ_THREADS; // <= 8 for group <= 16
-    uint32_t cnext[8];
-    auto fetch_codes = [&](unsigned long long piece) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int pidx = tid + i * AQ_THREADS;
-            const unsigned long long row = piece * AQ_PIECE + pidx / gcount;
-            const int sl = pidx % gcount;
-            cnext[i] = (i < per_thread && piece < pieces && pidx < AQ_PIECE * gcount && row < n && (!active || active[g0 + sl] != 0))
-                           ? (uint32_t)codes[row * m + g0 + sl]
-                           : 0xFFFFFFFFu;
-        }
-    };
-    fetch_codes(blockIdx.x);
-    for (unsigned long long piece = blockIdx.x; piece < pieces; piece += gridDim.x) {
-        const unsigned long long row0 = piece * AQ_PIECE;
-        // ---- step 1: pairs to their owners
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t code = cnext[i];
-            if (code == 0xFFFFFFFFu) continue;
-            const int pidx = tid + i * AQ_THREADS;
-            const int rip = pidx / gcount, sl = pidx % gcount;
-            const uint32_t slot = (uint32_t)sl * k + code;
-            const uint32_t owner = (code * (uint32_t)gcount + (uint32_t)sl) % AQ_THREADS;
-            const uint32_t pos = atomicAdd(&qcount[owner], 1u);
-            if (pos < (uint32_t)AQ_CAP) {
-                queue[owner * AQ_CAP + pos] = (uint32_t)rip | (slot << 12);
-            } else {
-                const float *xp = x + (row0 + rip) * ld + (size_t)(g0 + sl) * SD;
-                const float4 a = __ldg(reinterpret_cast<const float4 *>(xp)), b = __ldg(reinterpret_cast<const float4 *>(xp) + 1);
-                float *dst = ssum + (size_t)slot * SD;
-                atomicAdd(dst + 0, a.x), atomicAdd(dst + 1, a.y), atomicAdd(dst + 2, a.z), atomicAdd(dst + 3, a.w);
-                atomicAdd(dst + 4, b.x), atomicAdd(dst + 5, b.y), atomicAdd(dst + 6, b.z), atomicAdd(dst + 7, b.w);
-                atomicAdd(scnt + slot, 1u);
-            }
-        }
-        fetch_codes(piece + gridDim.x); // the next piece's codes travel during step 2
-        __syncthreads();
-        // ---- step 2: every thread adds the pairs of its own slots
-        {
-            const int mine = (int)min(qcount[tid], (uint32_t)AQ_CAP);
-            qcount[tid] = 0u;
-            for (int u0 = 0; u0 < mine; u0 += AQ_ROUND) { // four slices in flight per thread
-                uint32_t e[AQ_ROUND];
-                float4 va[AQ_ROUND], vb[AQ_ROUND];
-#pragma unroll
-                for (int u = 0; u < AQ_ROUND; ++u) {
-                    if (u0 + u < mine) {
-                        e[u] = queue[tid * AQ_CAP + u0 + u];
-                        const uint32_t slot = e[u] >> 12;
-                        const int sl = (int)(slot / (uint32_t)k);
-                        const float *xp = x + (row0 + (e[u] & 0xFFFu)) * ld + (size_t)(g0 + sl) * SD;
-                        va[u] = __ldg(reinterpret_cast<const float4 *>(xp));
-                        vb[u] = __ldg(reinterpret_cast<const float4 *>(xp) + 1);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < AQ_ROUND; ++u) {
-                    if (u0 + u < mine) {
-                        const uint32_t slot = e[u] >> 12;
-                        float4 *dst = reinterpret_cast<float4 *>(ssum + (size_t)slot * SD);
-                        float4 a = dst[0], b = dst[1];
-                        a.x += va[u].x, a.y += va[u].y, a.z += va[u].z, a.w += va[u].w;
-                        b.x += vb[u].x, b.y += vb[u].y, b.z += vb[u].z, b.w += vb[u].w;
-                        dst[0] = a, dst[1] = b;
-                        scnt[slot] += 1u;
-                    }
-                }
-            }
-        }
-        __syncthreads();
-    }
-    for (int t = tid; t < gcount * k * SD; t += AQ_THREADS)
-        if (scnt[t / SD] != 0u) atomicAdd(sums + (size_t)g0 * k * SD + t, ssum[t]);
-    for (int t = tid; t < gcount * k; t += AQ_THREADS)
-        if (scnt[t] != 0u) add_count(counts, (size_t)g0 * k + t, scnt[t], counts_f32);
-}
-
 // FAST, wide rows: one warp per (row, subspace), lanes over dimensions; sums laid out [code][d].
 // With shared == false the atomics go straight to global memory (codebook too large for shared memory).
 template <typename CodeT, bool SHARED>
@@ -1037,20 +932,6 @@ static void accumulate_t(CudaDevice &dev, const Shape &sh, const float *x, const
         group = (m + (m + group - 1) / group - 1) / ((m + group - 1) / group); // same number of CTAs, even share of subspaces
         const size_t smem = (size_t)group * per_sub;
         const int ctas_per_sm = (int)std::max<size_t>(1, std::min<size_t>(2, budget / (smem + 1024)));
-        const size_t queue_smem = smem + (size_t)AQ_THREADS * (1 + AQ_CAP) * sizeof(uint32_t);
-        if (sd == 8 && sh.ld % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && group <= 16 && (size_t)group * k < (1u << 20) && k >= 64 &&
-            2 * (queue_smem + 1024) <= budget + 1024 && getenv("VQB_ACCUM_ATOMICS") == nullptr) {
-            auto qk = accum_queue_kernel<CodeT>;
-            VQB_CUDA_CHECK(cudaFuncSetAttribute(qk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)queue_smem));
-            const unsigned long long pieces = (sh.n_local + AQ_PIECE - 1) / AQ_PIECE;
-            const unsigned ny = (unsigned)((m + group - 1) / group);
-            const unsigned gx = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>(pieces, (unsigned long long)dev.sm_count() * 2 / ny));
-            KernelScope ks(dev, "accumulate_fast");
-            qk<<<dim3(gx, ny), AQ_THREADS, queue_smem, st>>>(x, sh.n_local, sh.ld, m, k, group, codes, active, sums, counts, counts_f32);
-            VQB_CUDA_CHECK(cudaGetLastError());
-            dev.count_launch();
-            return;
-        }
         auto kernel = accum_small_kernel<CodeT>;
         VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         const int threads = 1024;
