@@ -479,7 +479,7 @@ def run_secondary(args):
         elif w == "tsvq":
             xh = synth.uniform01(rows, DIM, 1)
             fit = lambda xx: vq.TSVQ(xx, 10, vq.Distance.Euclidean, ctx=ctx)  # noqa: E731  (depth 10: benches/bench_tsvq.rs:11)
-            kname, bytes_per_vec, cfg = "tsvq_node_stats", 2 * 512, "tsvq_1m_x128_depth10_fit_plus_encode"
+            kname, bytes_per_vec, cfg = "tsvq_node_spreads", 512, "tsvq_1m_x128_depth10_fit_plus_encode"
 
             def cpu_run(xs):
                 t0 = time.perf_counter()

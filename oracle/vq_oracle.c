@@ -800,8 +800,11 @@ double vqo_mse_f16(const float *x, const uint16_t *q_f16, size_t n, size_t dim)
 
 /* ------------------------------------------------------------------------ */
 /* Tree-structured VQ -- src/tsvq.rs.                                         */
-/* TSVQNode::fit (71-148): centroid = mean_vector of the node's rows (here    */
-/* always in data order, one admissible order for nodes above 1024 rows);     */
+/* TSVQNode::fit (71-148): centroid = mean_vector of the node's rows: the sum */
+/* of the sums of consecutive 1024-row chunks, each chunk added up in data    */
+/* order from 0.0.  Up to 1024 rows that is exactly the reference's serial    */
+/* branch (src/vector.rs:305-313); above, where the reference reduces in      */
+/* parallel in an unspecified order (298-304), it is one admissible order;    */
 /* leaf when max_depth == 0 or <= 1 row; variance per dimension = serial f32  */
 /* sum of (v - c)^2 in data order (86-98); split dimension = max_by with      */
 /* partial_cmp, i.e. the LAST of equal maxima (101-105); median of the sorted */
@@ -813,6 +816,7 @@ double vqo_mse_f16(const float *x, const uint16_t *q_f16, size_t n, size_t dim)
 /* `partial_cmp(..).unwrap()`; here that is status 105.                       */
 /* ------------------------------------------------------------------------ */
 #define VQO_NOT_COMPARABLE 105
+#define VQO_MEAN_CHUNK 1024
 
 static int cmp_f32(const void *a, const void *b)
 {
@@ -838,8 +842,13 @@ int vqo_tsvq_fit(const float *x, size_t n, size_t dim, size_t max_depth, size_t 
         float *c = centroids + node * dim;
         left[node] = right[node] = -1;
         for (size_t t = 0; t < dim; ++t) c[t] = 0.0f;
-        for (size_t i = 0; i < sg.count; ++i)
-            for (size_t t = 0; t < dim; ++t) c[t] = c[t] + x[(size_t)rows[i] * dim + t];
+        for (size_t i0 = 0; i0 < sg.count; i0 += VQO_MEAN_CHUNK) {
+            const size_t i1 = i0 + VQO_MEAN_CHUNK < sg.count ? i0 + VQO_MEAN_CHUNK : sg.count;
+            for (size_t t = 0; t < dim; ++t) var[t] = 0.0f; /* the chunk's sums (var is free until the spreads below) */
+            for (size_t i = i0; i < i1; ++i)
+                for (size_t t = 0; t < dim; ++t) var[t] = var[t] + x[(size_t)rows[i] * dim + t];
+            for (size_t t = 0; t < dim; ++t) c[t] = c[t] + var[t];
+        }
         const float len = (float)(double)sg.count;
         for (size_t t = 0; t < dim; ++t) c[t] = c[t] / len;
         if (sg.depth == 0 || sg.count <= 1) continue;

@@ -13,8 +13,11 @@ def _recursive_fit(x, max_depth):
     x = np.asarray(x, np.float32)
     dim = x.shape[1]
     c = np.zeros(dim, np.float32)
-    for row in x:
-        c = c + row
+    for i0 in range(0, len(x), 1024):        # sums of consecutive 1024-row chunks; one chunk = the reference's serial sum
+        part = np.zeros(dim, np.float32)
+        for row in x[i0:i0 + 1024]:
+            part = part + row
+        c = c + part
     c = c / np.float32(len(x))
     node = {"c": c, "l": None, "r": None}
     if max_depth == 0 or len(x) <= 1:
@@ -55,7 +58,8 @@ def _bfs(root):
     return np.stack(cents), np.array(left, np.int32), np.array(right, np.int32)
 
 
-@pytest.mark.parametrize("n,dim,depth,seed", [(1, 3, 5, 0), (2, 4, 0, 1), (50, 6, 3, 2), (333, 10, 6, 3), (1000, 10, 3, 4), (257, 5, 12, 5)])
+@pytest.mark.parametrize("n,dim,depth,seed", [(1, 3, 5, 0), (2, 4, 0, 1), (50, 6, 3, 2), (333, 10, 6, 3), (1000, 10, 3, 4), (257, 5, 12, 5),
+                                              (2500, 4, 2, 6)])
 def test_oracle_tree_equals_the_recursive_transcription(n, dim, depth, seed):
     x = synth.normal(n, dim, seed)
     x[::7] = x[0]                                    # duplicates: equal values around the median

@@ -1370,6 +1370,7 @@ void CudaDevice::distance_rows(int metric, double p, const float *a, const float
 // 16 values per thread step (4 x 128-bit loads, one 128-bit store), 5 bytes of traffic per value.
 // ------------------------------------------------------------------------------------------------
 struct SqOp {
+    static constexpr bool TWO_PIECES = false;
     float mn, mx, step, inv; // inv = fl(1 / step)
     unsigned last;
     // The reference's arithmetic, operation by operation (src/sq.rs:117-127).
@@ -1398,6 +1399,7 @@ struct SqOp {
 };
 
 struct BqOp {
+    static constexpr bool TWO_PIECES = true;
     float thr;
     unsigned low, high;
     __device__ __forceinline__ unsigned operator()(float v) const { return (v >= thr) ? high : low; }
@@ -1420,7 +1422,22 @@ __global__ void __launch_bounds__(256) elementwise_u8_kernel(const float *__rest
         const unsigned long long n16 = n / 16;
         const float4 *x4 = reinterpret_cast<const float4 *>(x);
         uint4 *o4 = reinterpret_cast<uint4 *>(out);
-        for (unsigned long long i = tid; i < n16; i += nthreads) {
+        // Op::TWO_PIECES: two 64-byte pieces per trip, eight 128-bit loads in flight per thread.  Measured at 10M x 128: the
+        // threshold test gains (1.20 -> 1.07 ms), the scalar quantizer with its longer arithmetic loses (1.10 -> 1.19 ms).
+        unsigned long long i = tid;
+        for (; Op::TWO_PIECES && i + nthreads < n16; i += 2 * nthreads) {
+            float4 v[8];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) v[t] = ld_stream(x4 + 4 * i + t);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) v[4 + t] = ld_stream(x4 + 4 * (i + nthreads) + t);
+            unsigned w[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) w[t] = op(v[t].x) | (op(v[t].y) << 8) | (op(v[t].z) << 16) | (op(v[t].w) << 24);
+            __stcs(o4 + i, make_uint4(w[0], w[1], w[2], w[3]));
+            __stcs(o4 + i + nthreads, make_uint4(w[4], w[5], w[6], w[7]));
+        }
+        for (; i < n16; i += nthreads) {
             float4 v[4];
 #pragma unroll
             for (int t = 0; t < 4; ++t) v[t] = ld_stream(x4 + 4 * i + t);

@@ -1,14 +1,16 @@
 // tsvq.cu -- tree-structured vector quantizer (src/tsvq.rs) built level by level on the device.
 //
 // The reference recurses; here all nodes of one depth are processed together and numbered breadth-first (left child before
-// right).  What fixes the result bit for bit is kept: the centroid of a node is the f32 sum of its rows in data order divided
-// by `len as f32` (mean_vector, src/vector.rs:282-318; an admissible order for nodes above 1024 rows, where the reference's
-// own order is unspecified); a dimension's spread is the serial f32 sum of (v - c)^2 in data order (src/tsvq.rs:86-98); the
+// right).  What fixes the result bit for bit is kept: the centroid of a node is the f32 sum of its rows divided by
+// `len as f32` (mean_vector, src/vector.rs:282-318), added up as the sum of the sums of consecutive 1024-row chunks -- for
+// up to 1024 rows the reference's serial order, above that one admissible order where the reference's own parallel
+// reduction is unspecified, and one whose chunks can be added side by side; a dimension's spread is the serial f32 sum of
+// (v - c)^2 in data order (src/tsvq.rs:86-98), which no reordering may touch; the
 // split dimension is the last of equal maxima (max_by, 101-105); the median is taken from the sorted values (108-116); the
 // partition is stable (119-122); children exist only when both sides are non-empty (127-141).
 //
-// Per level: node_stats_kernel (one thread per (node, dimension) walks the node's rows in order, 32 loads in flight),
-// pick_split_kernel, a 64-bit radix sort of (node, value) keys (CUB, library code off the hot path) from which the medians
+// Per level: chunk_sums_kernel + node_mean_kernel (centroids), node_spread_stream_kernel or node_spread_kernel (spreads of
+// the nodes that split), pick_split_kernel, a 64-bit radix sort of (node, value) keys (CUB, library code off the hot path) from which the medians
 // are read, a flag + exclusive scan (CUB) + scatter for the stable partition, and one small download of the left counts
 // from which the host numbers the children.  The build is not sharded: every rank of a multi-GPU job builds the same tree.
 #include <cub/device/device_radix_sort.cuh>
@@ -35,6 +37,14 @@ struct NodeInfo {
     unsigned long long sorted_start; // first key of this node in the sorted key array
     unsigned long long nleft;
     int child_left, child_right; // ids given by the host after the partition, -1 = none
+    unsigned long long chunk0;   // first of this node's 1024-row chunks in the level's chunk table
+    unsigned int nchunks;
+};
+
+constexpr unsigned MEAN_CHUNK = 1024;
+struct ChunkInfo {
+    unsigned long long start; // position of the chunk's first row in perm
+    unsigned int rows;
 };
 
 constexpr uint32_t DEAD = 0xFFFFFFFFu;
@@ -50,63 +60,101 @@ __device__ __forceinline__ float key_f32(uint32_t k)
     return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
 }
 
-// Calls f(value) for column t of the node's rows in data order.  The additions behind f form one serial chain, so the loads
-// are what can overlap: 48 rows are in flight while the previous 48 are consumed (one warp per 32 dimensions, so that the
-// 96 buffer registers per thread are affordable and a wide node spreads over several SMs).
-template <typename F> __device__ __forceinline__ void walk_rows(const float *x, size_t dim, const uint32_t *rows, unsigned long long count, size_t t, F f)
+// ---- centroids: one warp per (1024-row chunk, 32 dimensions) adds the chunk's rows in data order (lane = dimension; the
+// row numbers of the next 32 rows are requested while the current 32 rows are in flight), then one thread per (node,
+// dimension) adds the node's chunk sums in order and divides.
+__global__ void __launch_bounds__(128) chunk_sums_kernel(const float *__restrict__ x, size_t dim, const uint32_t *__restrict__ perm,
+                                                         const ChunkInfo *chunks, float *partial)
 {
-    constexpr int B = 48;
-    float cur[B], nxt[B];
-    unsigned long long i = 0;
-    if (count >= (unsigned long long)B) {
+    const ChunkInfo ch = chunks[blockIdx.x];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t d0 = ((size_t)blockIdx.y * 4 + warp) * 32;
+    if (d0 >= dim) return;
+    const size_t d = d0 + lane;
+    const bool live = d < dim;
+    const uint32_t *rows = perm + ch.start;
+    float acc = 0.0f;
+    uint32_t next = lane < (int)ch.rows ? rows[lane] : DEAD;
+    for (unsigned r0 = 0; r0 < ch.rows; r0 += 32) {
+        const uint32_t mine = next;
+        next = r0 + 32 + lane < ch.rows ? rows[r0 + 32 + lane] : DEAD;
+        float v[32];
 #pragma unroll
-        for (int u = 0; u < B; ++u) cur[u] = x[(size_t)rows[u] * dim + t];
-    }
-    for (; i + B <= count; i += B) {
-        const bool more = i + 2 * B <= count;
-        if (more) {
-#pragma unroll
-            for (int u = 0; u < B; ++u) nxt[u] = x[(size_t)rows[i + B + u] * dim + t];
+        for (int u = 0; u < 32; ++u) {
+            const uint32_t idx = __shfl_sync(0xffffffffu, mine, u);
+            v[u] = (idx != DEAD && live) ? x[(size_t)idx * dim + d] : 0.0f;
         }
+        const int nrows = (int)min(32u, ch.rows - r0);
 #pragma unroll
-        for (int u = 0; u < B; ++u) f(cur[u]);
-        if (more) {
-#pragma unroll
-            for (int u = 0; u < B; ++u) cur[u] = nxt[u];
-        }
+        for (int u = 0; u < 32; ++u)
+            if (u < nrows) acc = __fadd_rn(acc, v[u]);
     }
-    for (; i < count; ++i) f(x[(size_t)rows[i] * dim + t]);
+    if (live) partial[(size_t)blockIdx.x * dim + d] = acc;
 }
 
+__global__ void node_mean_kernel(const NodeInfo *nodes, int first, int count, size_t dim, const float *partial, float *centroids)
+{
+    const size_t t = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (t >= (size_t)count * dim) return;
+    const int node = first + (int)(t / dim);
+    const size_t d = t % dim;
+    const NodeInfo nd = nodes[node];
+    float total = 0.0f;
+    const float *p = partial + nd.chunk0 * dim + d;
+#pragma unroll 8
+    for (unsigned c = 0; c < nd.nchunks; ++c) total = __fadd_rn(total, p[(size_t)c * dim]);
+    centroids[(size_t)node * dim + d] = __fdiv_rn(total, __ull2float_rn(nd.count)); // sum / (len as f32)
+}
+
+// ---- spreads, any width: one thread per (node, dimension) walks the node's rows in data order; the additions form one
+// serial chain, so the loads are what can overlap: 48 rows are in flight while the previous 48 are consumed.
 // grid.x = nodes of the level (ids first .. first + gridDim.x), grid.y x 32 threads over dimensions
-__global__ void __launch_bounds__(32) node_stats_kernel(const float *x, size_t dim, const uint32_t *perm, NodeInfo *nodes, int first, float *centroids, float *spread)
+__global__ void __launch_bounds__(32) node_spread_kernel(const float *x, size_t dim, const uint32_t *perm, const NodeInfo *nodes, int first,
+                                                         const float *centroids, float *spread)
 {
     const int node = first + blockIdx.x;
     const NodeInfo nd = nodes[node];
+    if (!nd.split) return;
     const uint32_t *rows = perm + nd.start;
+    constexpr int B = 48;
     for (size_t t = blockIdx.y * 32 + threadIdx.x; t < dim; t += (size_t)gridDim.y * 32) {
-        float sum = 0.0f;
-        walk_rows(x, dim, rows, nd.count, t, [&](float v) { sum = __fadd_rn(sum, v); });
-        const float c = __fdiv_rn(sum, __ull2float_rn(nd.count)); // sum / (len as f32)
-        centroids[(size_t)node * dim + t] = c;
-        if (nd.split) {
-            float var = 0.0f;
-            walk_rows(x, dim, rows, nd.count, t, [&](float v) {
-                const float d = __fsub_rn(v, c);
-                var = __fadd_rn(var, __fmul_rn(d, d));
-            });
-            spread[(size_t)blockIdx.x * dim + t] = var;
+        const float c = centroids[(size_t)node * dim + t];
+        float var = 0.0f;
+        auto add = [&](float v) {
+            const float d = __fsub_rn(v, c);
+            var = __fadd_rn(var, __fmul_rn(d, d));
+        };
+        float cur[B], nxt[B];
+        unsigned long long i = 0;
+        if (nd.count >= (unsigned long long)B) {
+#pragma unroll
+            for (int u = 0; u < B; ++u) cur[u] = x[(size_t)rows[u] * dim + t];
         }
+        for (; i + B <= nd.count; i += B) {
+            const bool more = i + 2 * B <= nd.count;
+            if (more) {
+#pragma unroll
+                for (int u = 0; u < B; ++u) nxt[u] = x[(size_t)rows[i + B + u] * dim + t];
+            }
+#pragma unroll
+            for (int u = 0; u < B; ++u) add(cur[u]);
+            if (more) {
+#pragma unroll
+                for (int u = 0; u < B; ++u) cur[u] = nxt[u];
+            }
+        }
+        for (; i < nd.count; ++i) add(x[(size_t)rows[i] * dim + t]);
+        spread[(size_t)blockIdx.x * dim + t] = var;
     }
 }
 
-// Streaming variant of node_stats_kernel for rows whose 32-column pieces are whole 128-byte lines (dim a multiple of 32,
-// 16-byte aligned base).  The sums stay one serial f32 chain per (node, dimension) in data order -- four cycles per row at
-// best -- so the kernel's job is to keep that chain fed: one CTA per (node, 32 dimensions); warp 0 is the consumer (lane =
-// dimension) and does nothing but read stages from shared memory and add; eleven producer warps gather the node's rows
-// (128-bit loads, 64 rows per warp in flight, the next stage's row numbers requested meanwhile) into a ring of 64-row
-// stages.  In the second pass the producers already store (v - c)^2, each term rounded like the reference's
-// (src/tsvq.rs:86-98), so the consumer's work per row is a quarter of a shared-memory load and one addition in both passes.
+// ---- spreads, rows whose 32-column pieces are whole 128-byte lines (dim a multiple of 32, 16-byte aligned base).  The sum
+// stays one serial f32 chain per (node, dimension) in data order -- a dependent addition every 5.8 cycles at best -- so the
+// kernel's job is to keep that chain fed: one CTA per (node, 32 dimensions); warp 0 is the consumer (lane = dimension) and
+// does nothing but read stages from shared memory and add; eleven producer warps gather the node's rows (128-bit loads, 64
+// rows per warp in flight, the next stage's row numbers requested meanwhile), form (v - c)^2 with each term rounded like the
+// reference's (src/tsvq.rs:86-98) and store that into a ring of 64-row stages, so the consumer's work per row is a
+// quarter of a shared-memory load and one addition.
 //
 // A stage is stored dimension-major, [32 dimensions][64 rows], so that the consumer fetches four consecutive rows of its
 // dimension with one 128-bit load; the 16 four-row groups of a dimension are permuted by ns_swizzle(d), which keeps both
@@ -117,10 +165,10 @@ __global__ void __launch_bounds__(32) node_stats_kernel(const float *x, size_t d
 // producers announce finished stages with a shared-memory counter per group of four stages, which the consumer reads
 // with an ordinary load one group ahead -- the load is in flight during the additions and is looked at three stages
 // later -- and the consumer hands a group back with one relaxed arrive.  Stage numbers are padded to a multiple of four
-// per pass (padding stages are announced without data) so that every group sees exactly four announcements.
+// (padding stages are announced without data) so that every group sees exactly four announcements.
 constexpr int NS_STAGE_ROWS = 64, NS_GROUP = 4, NS_GROUPS = 6, NS_RING = NS_GROUP * NS_GROUPS, NS_PRODUCERS = 11, NS_THREADS = 32 * (1 + NS_PRODUCERS);
 constexpr int NS_STAGE_BYTES = NS_STAGE_ROWS * 128;
-constexpr int NS_SMEM = NS_RING * NS_STAGE_BYTES + 32 * 4 + (NS_GROUPS + 1) * 8 + NS_GROUPS * 4;
+constexpr int NS_SMEM = NS_RING * NS_STAGE_BYTES + NS_GROUPS * 8 + NS_GROUPS * 4;
 // a producer may wait for the release of a group only when the release before that one has certainly happened (a parity
 // wait cannot tell two phases apart); the same warp filled a stage NS_PRODUCERS stages earlier, so this holds while
 // NS_PRODUCERS <= NS_RING - NS_GROUP
@@ -130,27 +178,24 @@ constexpr uint32_t NS_SPIN_LIMIT = 1u << 28;
 
 __device__ __forceinline__ int ns_swizzle(int d) { return ((d & 7) ^ (d >> 3)) & 7; }
 
-__global__ void __launch_bounds__(NS_THREADS) node_stats_stream_kernel(const float *__restrict__ x, size_t dim, const uint32_t *__restrict__ perm,
-                                                                       const NodeInfo *nodes, int first, float *centroids, float *spread, int *error)
+__global__ void __launch_bounds__(NS_THREADS) node_spread_stream_kernel(const float *__restrict__ x, size_t dim, const uint32_t *__restrict__ perm,
+                                                                        const NodeInfo *nodes, int first, const float *centroids, float *spread, int *error)
 {
     extern __shared__ __align__(128) unsigned char ns_smem[];
     float *ring = reinterpret_cast<float *>(ns_smem);
-    float *c_sh = reinterpret_cast<float *>(ns_smem + NS_RING * NS_STAGE_BYTES); // read in 16-byte pieces: keep it aligned
-    uint64_t *empty = reinterpret_cast<uint64_t *>(c_sh + 32);
-    uint64_t *cbar = empty + NS_GROUPS;
-    volatile uint32_t *filled = reinterpret_cast<volatile uint32_t *>(cbar + 1);
+    uint64_t *empty = reinterpret_cast<uint64_t *>(ns_smem + NS_RING * NS_STAGE_BYTES);
+    volatile uint32_t *filled = reinterpret_cast<volatile uint32_t *>(empty + NS_GROUPS);
     __shared__ int abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int node = first + blockIdx.x;
     const NodeInfo nd = nodes[node];
+    if (!nd.split) return;
     const size_t col0 = (size_t)blockIdx.y * 32;
     const unsigned long long count = nd.count;
-    const uint32_t S = (uint32_t)((count + NS_STAGE_ROWS - 1) / NS_STAGE_ROWS);      // stages with rows, per pass
-    const uint32_t S4 = (S + NS_GROUP - 1) / NS_GROUP * NS_GROUP;                      // stage numbers per pass
-    const uint32_t total = nd.split ? 2 * S4 : S4;
+    const uint32_t S = (uint32_t)((count + NS_STAGE_ROWS - 1) / NS_STAGE_ROWS);      // stages with rows
+    const uint32_t total = (S + NS_GROUP - 1) / NS_GROUP * NS_GROUP;                   // stage numbers
     if (threadIdx.x == 0) {
         for (int i = 0; i < NS_GROUPS; ++i) mbar_init(&empty[i], 1), filled[i] = 0;
-        mbar_init(cbar, 1);
         abort_flag = 0;
     }
     __syncthreads();
@@ -187,16 +232,15 @@ __global__ void __launch_bounds__(NS_THREADS) node_stats_stream_kernel(const flo
 #pragma unroll
             for (int q = 0; q < 16; ++q) buf[q] = load4(addr, q);
         };
-        // cur holds stage s = base + sb (sb < S)
-        auto step = [&](float4(&cur)[16], float4(&nxt)[16], uint32_t base, uint32_t sb) {
-            const uint32_t s = base + sb;
-            const bool has_next = sb + 1 < S;
+        // cur holds stage s (s < S)
+        auto step = [&](float4(&cur)[16], float4(&nxt)[16], uint32_t s) {
+            const bool has_next = s + 1 < S;
             if (has_next && ((s + 1) & (NS_GROUP - 1)) == 0) {
                 group_ready((s + 1) / NS_GROUP, ahead);
                 if (!ok) return;
             }
             if ((s & (NS_GROUP - 1)) == 0) ahead = filled[(s / NS_GROUP + 1) % NS_GROUPS];
-            const unsigned long long left = count - (unsigned long long)sb * NS_STAGE_ROWS;
+            const unsigned long long left = count - (unsigned long long)s * NS_STAGE_ROWS;
             if (left >= (unsigned long long)NS_STAGE_ROWS && has_next) {
                 const uint32_t addr = stage_addr(s + 1);
 #pragma unroll
@@ -207,7 +251,7 @@ __global__ void __launch_bounds__(NS_THREADS) node_stats_stream_kernel(const flo
                 }
             } else {
                 if (has_next) request(s + 1, nxt);
-                const int rows_here = (int)left;
+                const int rows_here = left < (unsigned long long)NS_STAGE_ROWS ? (int)left : NS_STAGE_ROWS;
 #pragma unroll
                 for (int q = 0; q < 16; ++q) {
                     if (4 * q + 0 < rows_here) acc = __fadd_rn(acc, cur[q].x);
@@ -216,45 +260,30 @@ __global__ void __launch_bounds__(NS_THREADS) node_stats_stream_kernel(const flo
                     if (4 * q + 3 < rows_here) acc = __fadd_rn(acc, cur[q].w);
                 }
             }
-            if ((s & (NS_GROUP - 1)) == NS_GROUP - 1 || sb + 1 == S) { // the group's last stage with rows: hand the group back
-                __syncwarp();                                           // every lane has used its values
+            if ((s & (NS_GROUP - 1)) == NS_GROUP - 1 || s + 1 == S) { // the group's last stage with rows: hand the group back
+                __syncwarp();                                          // every lane has used its values
                 if (lane == 0) mbar_arrive_relaxed(&empty[(s / NS_GROUP) % NS_GROUPS]);
             }
         };
-        for (uint32_t pass = 0; pass * S4 < total && ok; ++pass) {
-            const uint32_t base = pass * S4;
-            acc = 0.0f;
-            group_ready(base / NS_GROUP, 0);
-            if (!ok) break;
-            request(base, a);
-            for (uint32_t sb = 0; sb < S && ok; sb += 2) {
-                step(a, b, base, sb);
-                if (sb + 1 < S && ok) step(b, a, base, sb + 1);
-            }
-            if (!ok) break;
-            if (pass == 0) {
-                const float c = __fdiv_rn(acc, __ull2float_rn(count)); // sum / (len as f32)
-                centroids[(size_t)node * dim + col0 + lane] = c;
-                if (nd.split) {
-                    c_sh[lane] = c;
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(cbar);
-                }
-            } else {
-                spread[(size_t)blockIdx.x * dim + col0 + lane] = acc;
-            }
+        group_ready(0, 0);
+        if (ok) request(0, a);
+        for (uint32_t s = 0; s < S && ok; s += 2) {
+            step(a, b, s);
+            if (s + 1 < S && ok) step(b, a, s + 1);
         }
+        if (ok) spread[(size_t)blockIdx.x * dim + col0 + lane] = acc;
     } else {
         const uint32_t *rows = perm + nd.start;
         const int sub = lane >> 3, piece = lane & 7;
         const float *xcol = x + col0 + piece * 4;
+        const float4 cc = *reinterpret_cast<const float4 *>(centroids + (size_t)node * dim + col0 + piece * 4);
         // this lane's four dimensions 4 * piece + j: offset of (dimension, four-row group 0, position sub) in a stage
         int off[4], gj[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) gj[j] = ns_swizzle(4 * piece + j), off[j] = (4 * piece + j) * NS_STAGE_ROWS + sub;
         uint32_t idx[16];
-        auto load_idx = [&](uint32_t s) { // stage numbers past the pass's rows give no rows at all
-            const unsigned long long r0 = (unsigned long long)(s % S4) * NS_STAGE_ROWS + sub;
+        auto load_idx = [&](uint32_t s) { // stage numbers past the node's rows give no rows at all
+            const unsigned long long r0 = (unsigned long long)s * NS_STAGE_ROWS + sub;
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const unsigned long long r = r0 + 4 * i;
@@ -263,41 +292,20 @@ __global__ void __launch_bounds__(NS_THREADS) node_stats_stream_kernel(const flo
         };
         uint32_t s = warp - 1;
         if (s < total) load_idx(s);
-        bool have_c = false;
-        float4 cc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (; s < total; s += NS_PRODUCERS) {
-            const bool padding = s % S4 >= S;
+            const bool padding = s >= S;
             float4 v[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i)
                 v[i] = idx[i] != DEAD ? __ldg(reinterpret_cast<const float4 *>(xcol + (size_t)idx[i] * dim)) : make_float4(0.f, 0.f, 0.f, 0.f);
             if (s + NS_PRODUCERS < total) load_idx(s + NS_PRODUCERS);
-            if (s >= S4 && !padding) {
-                if (!have_c) {
-                    // the first pass over the node ends before this completes: the bound grows with the node
-                    bool got = false;
-                    for (unsigned long long tries = 0; tries < 4096ull + 4 * count && !got; ++tries) {
-                        got = mbar_try_wait(cbar, 0u, 1000u);
-                        if (!got && (tries & 255u) == 255u && *(volatile int *)&abort_flag) break;
-                    }
-                    if (!got) {
-                        if (!*(volatile int *)&abort_flag) {
-                            abort_flag = 1;
-                            atomicCAS(error, 0, NS_ERR_WAIT);
-                        }
-                        break;
-                    }
-                    cc = *reinterpret_cast<const float4 *>(c_sh + piece * 4);
-                    have_c = true;
-                }
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    float d;
-                    d = __fsub_rn(v[i].x, cc.x), v[i].x = __fmul_rn(d, d);
-                    d = __fsub_rn(v[i].y, cc.y), v[i].y = __fmul_rn(d, d);
-                    d = __fsub_rn(v[i].z, cc.z), v[i].z = __fmul_rn(d, d);
-                    d = __fsub_rn(v[i].w, cc.w), v[i].w = __fmul_rn(d, d);
-                }
+            for (int i = 0; i < 16; ++i) {
+                float d;
+                d = __fsub_rn(v[i].x, cc.x), v[i].x = __fmul_rn(d, d);
+                d = __fsub_rn(v[i].y, cc.y), v[i].y = __fmul_rn(d, d);
+                d = __fsub_rn(v[i].z, cc.z), v[i].z = __fmul_rn(d, d);
+                d = __fsub_rn(v[i].w, cc.w), v[i].w = __fmul_rn(d, d);
             }
             const uint32_t grp = s / NS_GROUP, gslot = grp % NS_GROUPS;
             if (!mbar_wait(&empty[gslot], ((grp / NS_GROUPS) & 1u) ^ 1u, &abort_flag, error, NS_ERR_WAIT, 100u)) break;
@@ -548,7 +556,7 @@ void tsvq_fit(CudaDevice &dev, const float *x, size_t n, size_t dim, size_t max_
     const size_t cap_nodes = std::min<size_t>(max_depth < 40 ? ((size_t)2 << max_depth) - 1 : 2 * n, 2 * n);
     std::vector<NodeInfo> h(1);
     std::vector<size_t> depth_left(1, max_depth);
-    h[0] = NodeInfo{0, n, 0, 0, 0.0f, 0, 0, -1, -1};
+    h[0] = NodeInfo{0, n, 0, 0, 0.0f, 0, 0, -1, -1, 0, 0};
     float *cent = static_cast<float *>(dev.alloc(sizeof(float) * cap_nodes * dim));
     NodeInfo *nodes_d = static_cast<NodeInfo *>(dev.alloc(sizeof(NodeInfo) * cap_nodes));
     uint32_t *perm = static_cast<uint32_t *>(dev.alloc(sizeof(uint32_t) * n)), *perm2 = static_cast<uint32_t *>(dev.alloc(sizeof(uint32_t) * n));
@@ -562,14 +570,16 @@ void tsvq_fit(CudaDevice &dev, const float *x, size_t n, size_t dim, size_t max_
     cub::DeviceScan::ExclusiveSum(nullptr, scan_bytes, flags, scan, (int)(n + 1), st);
     void *tmp = dev.alloc(std::max(sort_bytes, scan_bytes));
     size_t tmp_bytes = std::max(sort_bytes, scan_bytes);
-    float *spread = nullptr;
-    size_t spread_cap = 0;
+    float *spread = nullptr, *partial = nullptr;
+    ChunkInfo *chunks_d = nullptr;
+    size_t spread_cap = 0, chunk_cap = 0;
+    std::vector<ChunkInfo> chunks;
     // rows in whole 128-byte pieces of 32 columns: the streaming kernel; any other shape: one thread per (node, dimension)
     const bool stream_rows = dim % 32 == 0 && dim / 32 <= 65535 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && getenv("VQB_TSVQ_SERIAL_WALK") == nullptr;
-    if (stream_rows) VQB_CUDA_CHECK(cudaFuncSetAttribute(node_stats_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, NS_SMEM));
+    if (stream_rows) VQB_CUDA_CHECK(cudaFuncSetAttribute(node_spread_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, NS_SMEM));
     auto cleanup = [&] {
         dev.release(nodes_d), dev.release(perm), dev.release(perm2), dev.release(pos_node), dev.release(flags), dev.release(scan);
-        dev.release(keys), dev.release(keys2), dev.release(error), dev.release(tmp), dev.release(spread);
+        dev.release(keys), dev.release(keys2), dev.release(error), dev.release(tmp), dev.release(spread), dev.release(partial), dev.release(chunks_d);
     };
     try {
         dev.zero(error, sizeof(int));
@@ -583,7 +593,12 @@ void tsvq_fit(CudaDevice &dev, const float *x, size_t n, size_t dim, size_t max_
         while (first < h.size()) {
             const size_t level_count = h.size() - first;
             size_t n_split = 0, sorted = 0;
+            chunks.clear();
             for (size_t j = first; j < h.size(); ++j) {
+                h[j].chunk0 = chunks.size();
+                h[j].nchunks = (unsigned)((h[j].count + MEAN_CHUNK - 1) / MEAN_CHUNK);
+                for (unsigned long long r = 0; r < h[j].count; r += MEAN_CHUNK)
+                    chunks.push_back(ChunkInfo{h[j].start + r, (unsigned)std::min<unsigned long long>(MEAN_CHUNK, h[j].count - r)});
                 h[j].split = (depth_left[j] > 0 && h[j].count > 1) ? 1 : 0;
                 h[j].sorted_start = sorted;
                 if (h[j].split) {
@@ -597,14 +612,29 @@ void tsvq_fit(CudaDevice &dev, const float *x, size_t n, size_t dim, size_t max_
                 spread = static_cast<float *>(dev.alloc(sizeof(float) * level_count * dim));
                 spread_cap = level_count;
             }
+            if (chunks.size() > chunk_cap) {
+                dev.release(partial), dev.release(chunks_d);
+                chunk_cap = chunks.size() + chunks.size() / 2;
+                partial = static_cast<float *>(dev.alloc(sizeof(float) * chunk_cap * dim));
+                chunks_d = static_cast<ChunkInfo *>(dev.alloc(sizeof(ChunkInfo) * chunk_cap));
+            }
+            dev.upload(chunks_d, chunks.data(), sizeof(ChunkInfo) * chunks.size());
             {
-                KernelScope ks(dev, "tsvq_node_stats");
+                KernelScope ks(dev, "tsvq_node_means");
+                chunk_sums_kernel<<<dim3((unsigned)chunks.size(), (unsigned)((dim + 127) / 128)), 128, 0, st>>>(x, dim, perm, chunks_d, partial);
+                node_mean_kernel<<<grid_for(level_count * dim, 128, 1u << 30), 128, 0, st>>>(nodes_d, (int)first, (int)level_count, dim, partial, cent);
+                VQB_CUDA_CHECK(cudaGetLastError());
+                dev.count_launch();
+            }
+            if (n_split == 0) break;
+            {
+                KernelScope ks(dev, "tsvq_node_spreads");
                 if (stream_rows) {
                     const dim3 grid((unsigned)level_count, (unsigned)(dim / 32));
-                    node_stats_stream_kernel<<<grid, NS_THREADS, NS_SMEM, st>>>(x, dim, perm, nodes_d, (int)first, cent, spread, error);
+                    node_spread_stream_kernel<<<grid, NS_THREADS, NS_SMEM, st>>>(x, dim, perm, nodes_d, (int)first, cent, spread, error);
                 } else {
                     const dim3 grid((unsigned)level_count, (unsigned)std::min<size_t>((dim + 31) / 32, 64));
-                    node_stats_kernel<<<grid, 32, 0, st>>>(x, dim, perm, nodes_d, (int)first, cent, spread);
+                    node_spread_kernel<<<grid, 32, 0, st>>>(x, dim, perm, nodes_d, (int)first, cent, spread);
                 }
                 VQB_CUDA_CHECK(cudaGetLastError());
                 dev.count_launch();
@@ -637,10 +667,10 @@ void tsvq_fit(CudaDevice &dev, const float *x, size_t n, size_t dim, size_t max_
                 const unsigned long long nl = h[j].nleft, nr = h[j].count - nl;
                 if (nl > 0 && nr > 0) { // otherwise neither side is a proper subset: no children (src/tsvq.rs:127-141)
                     h[j].child_left = (int)h.size();
-                    h.push_back(NodeInfo{h[j].start, nl, 0, 0, 0.0f, 0, 0, -1, -1});
+                    h.push_back(NodeInfo{h[j].start, nl, 0, 0, 0.0f, 0, 0, -1, -1, 0, 0});
                     depth_left.push_back(depth_left[j] - 1);
                     h[j].child_right = (int)h.size();
-                    h.push_back(NodeInfo{h[j].start + nl, nr, 0, 0, 0.0f, 0, 0, -1, -1});
+                    h.push_back(NodeInfo{h[j].start + nl, nr, 0, 0, 0.0f, 0, 0, -1, -1, 0, 0});
                     depth_left.push_back(depth_left[j] - 1);
                 }
             }
