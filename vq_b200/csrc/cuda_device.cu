@@ -82,6 +82,7 @@ CudaDevice::~CudaDevice()
         cudaFree(pq_scratch_);
         cudaFree(pq_marks_);
         cudaFree(cand_);
+        cudaFree(list_);
         cudaFree(tc_stats_);
         cudaFree(tc_error_);
         if (status_host_) cudaFreeHost(status_host_);
@@ -255,12 +256,17 @@ void CudaDevice::ensure_tc_buffers(size_t n)
         VQB_CUDA_CHECK(cudaStreamSynchronize(stream_));
         cudaFree(rownorm_);
         cudaFree(cand_);
+        cudaFree(list_);
         rownorm_ = nullptr;
         cand_ = nullptr;
+        list_ = nullptr;
+        list_count_ = nullptr;
         rows_cap_ = 0;
-        device_allocs_ += 2;
+        device_allocs_ += 3;
         VQB_CUDA_CHECK(cudaMalloc(&rownorm_, n * sizeof(float)));
         VQB_CUDA_CHECK(cudaMalloc(&cand_, n * DENSE_MASK_WORDS * sizeof(uint32_t)));
+        VQB_CUDA_CHECK(cudaMalloc(&list_, (n + 1) * sizeof(uint32_t))); // rows left for the exact kernel, then their count
+        list_count_ = list_ + n;
         rows_cap_ = n;
     }
 }
@@ -436,7 +442,11 @@ void CudaDevice::assign_train(const Shape &sh, const float *x, const float *cent
         // full-width k-means step: tensor-core shortlist, then the exact decision among the candidates
         static const bool stats_on = std::getenv("VQB_TC_STATS") != nullptr; // diagnostic: shortlist sizes per training pass on stderr
         if (stats_on) VQB_CUDA_CHECK(cudaMemsetAsync(tc_stats_, 0, 3 * sizeof(unsigned long long), stream_));
-        dense_shortlist(*this, x, sh.n_local, sh.sd, centroids, sh.k, rownorm_, hn_scratch_, cand_, stats_on ? tc_stats_ : nullptr, tc_error_, nullptr);
+        // the shortlist kernel decides the rows with one candidate itself and lists the others for the exact kernel
+        if (code_bytes(sh.k) != 1) throw Error(103, "full-width tensor path with assignments wider than one byte");
+        VQB_CUDA_CHECK(cudaMemsetAsync(list_count_, 0, sizeof(uint32_t), stream_));
+        ShortlistTrain tr = {static_cast<uint8_t *>(codes), changed, list_, list_count_};
+        dense_shortlist(*this, x, sh.n_local, sh.sd, centroids, sh.k, rownorm_, hn_scratch_, cand_, stats_on ? tc_stats_ : nullptr, tc_error_, nullptr, &tr);
         if (stats_on) {
             unsigned long long st3[3] = {0, 0, 0};
             download(st3, tc_stats_, sizeof st3);
@@ -453,6 +463,8 @@ void CudaDevice::assign_train(const Shape &sh, const float *x, const float *cent
         r.euclid = 0;
         r.codes = codes;
         r.changed = changed;
+        r.list = list_;
+        r.list_count = list_count_;
         launch_resolve(*this, r, R_TRAIN, code_bytes(sh.k));
         return;
     }

@@ -124,6 +124,7 @@ class CudaDevice : public Device {
     size_t pq_marks_cap_ = 0;
     bool pq_tensor_enabled_ = false;
     uint32_t *cand_ = nullptr;
+    uint32_t *list_ = nullptr, *list_count_ = nullptr; // rows the shortlist kernel leaves to the exact kernel (training passes)
     size_t rows_cap_ = 0;
     unsigned long long *tc_stats_ = nullptr;
     int *tc_error_ = nullptr;

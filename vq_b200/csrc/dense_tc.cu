@@ -63,6 +63,12 @@ struct ShortlistParams {
     unsigned long long *stats; // [0] rows, [1] candidates, [2] rows needing a full scan   (may be null)
     float *debug_dots;    // [n][256] raw tensor-core dot products (may be null)
     int *error;           // device error word, 0 = ok
+    // training passes (codes != null): a row with a single candidate gets its assignment here; the others are appended to
+    // `list` (and only they get their mask written)
+    uint8_t *codes;        // [n] previous assignment in, new assignment out
+    uint32_t *changed;     // VQB_MOVED_BITS is OR-ed in when a row moved
+    uint32_t *list;        // [n] rows left for the exact decision
+    uint32_t *list_count;  // [1] zero on entry
 };
 
 __global__ void __launch_bounds__(192, 1) dense_shortlist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_c,
@@ -191,6 +197,7 @@ __global__ void __launch_bounds__(192, 1) dense_shortlist_kernel(const __grid_co
         const int q = warp & 3; // TMEM lane quadrant this warp may read
         const float cmax = *P.cmax;
         unsigned long long cand_total = 0, full_scans = 0, rows_done = 0;
+        bool moved = false;
         uint32_t local = 0;
         for (unsigned long long tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x, ++local) {
             const uint32_t b = local & 1u, buse = local >> 1;
@@ -200,6 +207,7 @@ __global__ void __launch_bounds__(192, 1) dense_shortlist_kernel(const __grid_co
             const bool valid = row < P.n;
             const uint32_t taddr = tmem_base + ((uint32_t)(32 * q) << 16) + b * BN;
             const float xn2 = valid ? P.xnorm2[row] : 0.0f;
+            const int old_code = (P.codes && valid) ? (int)P.codes[row] : 0; // asked for now, needed after the two passes
 
             // pass 1: the largest D = x.c - hn, i.e. the smallest score S = -D (four chains of 3-input max); the next 32 columns
             // are in flight while these are processed
@@ -277,6 +285,7 @@ __global__ void __launch_bounds__(192, 1) dense_shortlist_kernel(const __grid_co
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->tempty[b]); // this accumulator may be overwritten
+            bool listed = false;
             if (valid) {
                 int cnt = 0;
 #pragma unroll
@@ -289,11 +298,34 @@ __global__ void __launch_bounds__(192, 1) dense_shortlist_kernel(const __grid_co
                 if (scan_all) ++full_scans;
                 else cand_total += cnt;
                 ++rows_done;
-                uint4 *o = reinterpret_cast<uint4 *>(P.cand + row * 8);
-                o[0] = make_uint4(words[0], words[1], words[2], words[3]);
-                o[1] = make_uint4(words[4], words[5], words[6], words[7]);
+                if (P.codes && cnt == 1) {
+                    // the only candidate is the reference's choice (an unrankable row comes with all k >= 2 bits set)
+                    int best_j = 0;
+#pragma unroll
+                    for (int wd = 0; wd < BN / 32; ++wd)
+                        if (words[wd]) best_j = wd * 32 + __ffs(words[wd]) - 1;
+                    if (best_j != old_code) {
+                        moved = true;
+                        P.codes[row] = (uint8_t)best_j;
+                    }
+                } else {
+                    uint4 *o = reinterpret_cast<uint4 *>(P.cand + row * 8);
+                    o[0] = make_uint4(words[0], words[1], words[2], words[3]);
+                    o[1] = make_uint4(words[4], words[5], words[6], words[7]);
+                    listed = P.codes != nullptr;
+                }
+            }
+            if (P.codes) { // the rows that need the exact decision, appended in one step per warp
+                const unsigned bal = __ballot_sync(0xffffffffu, listed);
+                if (bal) {
+                    uint32_t base = 0;
+                    if (lane == 0) base = atomicAdd(P.list_count, (uint32_t)__popc(bal));
+                    base = __shfl_sync(0xffffffffu, base, 0);
+                    if (listed) P.list[base + __popc(bal & ((1u << lane) - 1u))] = (uint32_t)row;
+                }
             }
         }
+        if (P.codes && __any_sync(0xffffffffu, moved) && lane == 0) atomicOr(P.changed, VQB_MOVED_BITS);
         if (P.stats) {
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
@@ -382,7 +414,8 @@ void dense_row_norms(CudaDevice &dev, const float *x, size_t n, size_t dim, floa
 }
 
 void dense_shortlist(CudaDevice &dev, const float *x, size_t n, size_t dim, const float *codebook, size_t k, const float *xnorm2,
-                     float *hn_scratch /* 257 floats */, uint32_t *cand, unsigned long long *stats, int *error_word, float *debug_dots)
+                     float *hn_scratch /* 257 floats */, uint32_t *cand, unsigned long long *stats, int *error_word, float *debug_dots,
+                     const ShortlistTrain *train)
 {
     if (n == 0) return;
     {
@@ -405,6 +438,10 @@ void dense_shortlist(CudaDevice &dev, const float *x, size_t n, size_t dim, cons
     p.stats = stats;
     p.debug_dots = debug_dots;
     p.error = error_word;
+    p.codes = train ? train->codes : nullptr;
+    p.changed = train ? train->changed : nullptr;
+    p.list = train ? train->list : nullptr;
+    p.list_count = train ? train->list_count : nullptr;
     const size_t smem = dense_tc_smem_bytes();
     VQB_CUDA_CHECK(cudaFuncSetAttribute(dense_shortlist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const unsigned long long tiles = (n + BM - 1) / BM;

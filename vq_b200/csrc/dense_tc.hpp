@@ -17,8 +17,18 @@ size_t dense_tc_smem_bytes();
 void dense_row_norms(CudaDevice &dev, const float *x, size_t n, size_t dim, float *out);
 // cand[r][0..8): 256-bit mask, bit j set for every centroid that can be the reference's choice for row r; rows that
 // cannot be ranked (NaN / infinity) come back with all k bits set.
+// With `train` (k-means passes; assignments are one byte here, k <= 256) the kernel also decides every row that has a single
+// candidate -- codes[r] is rewritten, train->changed gets VQB_MOVED_BITS when a row moved -- and appends the other rows to
+// train->list (count in *train->list_count, zero on entry); only those rows get their mask written.
+struct ShortlistTrain {
+    uint8_t *codes;
+    uint32_t *changed;
+    uint32_t *list;
+    uint32_t *list_count;
+};
 void dense_shortlist(CudaDevice &dev, const float *x, size_t n, size_t dim, const float *codebook, size_t k, const float *xnorm2,
-                     float *hn_scratch /* 257 floats */, uint32_t *cand, unsigned long long *stats, int *error_word, float *debug_dots);
+                     float *hn_scratch /* 257 floats */, uint32_t *cand, unsigned long long *stats, int *error_word, float *debug_dots,
+                     const ShortlistTrain *train = nullptr);
 
 enum : int { R_TRAIN = 0, R_RVQ_UPDATE = 1, R_RVQ_STAGE = 2 };
 
@@ -29,9 +39,11 @@ struct ResolveParams {
     const float *codebook; // [k][dim]
     const uint32_t *cand;  // [n][DENSE_MASK_WORDS]
     int euclid;            // compare square roots (Distance::Euclidean) instead of squared sums
-    // R_TRAIN
+    // R_TRAIN: only the rows in list[0 .. *list_count) are looked at (the shortlist kernel decided the others)
     void *codes;
     uint32_t *changed;
+    const uint32_t *list;
+    const uint32_t *list_count;
     // R_RVQ_UPDATE, R_RVQ_STAGE
     float *res;
     double *norm_sum;

@@ -273,20 +273,22 @@ template <int MODE, typename CodeT> __global__ void __launch_bounds__(32 * RT_MA
     }
 }
 
-// Training assignment, two passes per block of 256 rows.  Pass A reads only the shortlists: a row with a single candidate is
-// decided at once (that candidate is the reference's choice), the others are collected in a per-warp list.  Pass B stages
-// the listed rows 16 at a time and gives every row TWO lanes, each of which evaluates two of the row's next four candidates
-// with the exact arithmetic; the pair then goes through the four distances in ascending centroid order like the reference.
-// Sixteen-row groups halve a warp's staging buffer, which is what lets ten warps instead of four sit beside the 132 KB
-// codebook: with one warp per scheduler the serial chains ran at a quarter of the issue rate.
+// Training assignment of the rows the shortlist kernel could not decide (more than one candidate, or "examine all"); the
+// rows with a single candidate got their assignment there and are never read here.  A warp takes 16 listed rows at a time and
+// gives every row TWO lanes, each of which evaluates two of the row's next four candidates with the exact arithmetic; the pair
+// then goes through the four distances in ascending centroid order like the reference.  Sixteen-row groups halve a warp's
+// staging buffer, which is what lets ten warps instead of four sit beside the 132 KB codebook: with one warp per scheduler
+// the serial chains ran at a quarter of the issue rate.
 template <typename CodeT> __global__ void __launch_bounds__(32 * RT_MAX_WARPS, 1) resolve_train_kernel(const ResolveParams P)
 {
     extern __shared__ __align__(16) float smem[];
     const int dim = P.dim, k = P.k, cstride = dim + 1;
     const int W = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned long long cnt = *reinterpret_cast<const volatile uint32_t *>(P.list_count);
+    const unsigned long long groups = (cnt + 15) / 16;
+    if ((unsigned long long)blockIdx.x * W >= groups) return; // nothing for this CTA: skip the codebook copy as well
     float *cpad = smem;                                                                   // [k][dim + 1]
     float *xs = smem + (size_t)k * cstride + (size_t)warp * dim * XT_STRIDE;              // [dim][17] per warp
-    uint16_t *list = reinterpret_cast<uint16_t *>(smem + (size_t)k * cstride + (size_t)W * dim * XT_STRIDE) + warp * 256; // [256] per warp
     {
         const int total4 = k * dim / 4, dim4 = dim / 4;
         const float4 *src = reinterpret_cast<const float4 *>(P.codebook);
@@ -309,150 +311,121 @@ template <typename CodeT> __global__ void __launch_bounds__(32 * RT_MAX_WARPS, 1
     }
     __syncthreads();
     const bool euclid = P.euclid != 0;
-    const unsigned long long blocks = (P.n + 255) / 256;
     bool moved = false;
     CodeT *codes = reinterpret_cast<CodeT *>(P.codes);
     const int r = lane & 15, half = lane >> 4;
-    for (unsigned long long blk = (unsigned long long)blockIdx.x * W + warp; blk < blocks; blk += (unsigned long long)gridDim.x * W) {
-        const unsigned long long base = blk * 256;
-        // ---- pass A
-        int cnt = 0;
-#pragma unroll 2
-        for (int t = 0; t < 8; ++t) {
-            const unsigned long long row = base + (unsigned long long)(t * 32 + lane);
-            bool need = false;
-            if (row < P.n) {
-                const uint4 lo = __ldg(reinterpret_cast<const uint4 *>(P.cand + row * 8)), hi = __ldg(reinterpret_cast<const uint4 *>(P.cand + row * 8) + 1);
-                const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-                int ncand = 0;
+    const int dim4 = dim / 4;
+    // the next group's rows are requested into registers while this one is evaluated
+    float4 pre[16];
+    auto request = [&](unsigned long long g) {
+        const int nb = g < groups ? (int)min(16ull, cnt - g * 16) : 0, total4 = nb * dim4;
 #pragma unroll
-                for (int e = 0; e < 8; ++e) ncand += __popc(w[e]);
-                if (ncand == 1) {
-                    const int best = next_bit(w, 0);
-                    const CodeT nc = (CodeT)(best < k ? best : 0);
-                    if (codes[row] != nc) moved = true;
-                    codes[row] = nc;
-                } else {
-                    need = true;
-                }
-            }
-            const unsigned bal = __ballot_sync(0xffffffffu, need);
-            if (need) list[cnt + __popc(bal & ((1u << lane) - 1u))] = (uint16_t)(t * 32 + lane);
-            cnt += __popc(bal);
+        for (int u = 0; u < 16; ++u) {
+            const int idx = u * 32 + lane;
+            pre[u] = idx < total4 ? __ldg(reinterpret_cast<const float4 *>(P.x + (unsigned long long)P.list[g * 16 + idx / dim4] * dim) + idx % dim4)
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        __syncwarp();
-        // ---- pass B: 16 listed rows at a time; the next group's rows are requested into registers while this one is evaluated
-        const int dim4 = dim / 4;
-        float4 pre[16];
-        auto request = [&](int i0) {
-            const int nb = min(16, cnt - i0), total4 = nb * dim4;
+    };
+    const unsigned long long g0 = (unsigned long long)blockIdx.x * W + warp, gstep = (unsigned long long)gridDim.x * W;
+    request(g0);
+    for (unsigned long long g = g0; g < groups; g += gstep) {
+        const int nb = (int)min(16ull, cnt - g * 16);
+        {
+            const int total4 = nb * dim4;
 #pragma unroll
             for (int u = 0; u < 16; ++u) {
                 const int idx = u * 32 + lane;
-                pre[u] = (i0 < cnt && idx < total4) ? __ldg(reinterpret_cast<const float4 *>(P.x + (base + list[i0 + idx / dim4]) * dim) + idx % dim4)
-                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-        };
-        if (cnt > 0) request(0);
-        for (int i0 = 0; i0 < cnt; i0 += 16) {
-            const int nb = min(16, cnt - i0);
-            {
-                const int total4 = nb * dim4;
-#pragma unroll
-                for (int u = 0; u < 16; ++u) {
-                    const int idx = u * 32 + lane;
-                    if (idx < total4) {
-                        float *d = xs + (size_t)(idx % dim4) * 4 * XT_STRIDE + idx / dim4;
-                        d[0] = pre[u].x, d[XT_STRIDE] = pre[u].y, d[2 * XT_STRIDE] = pre[u].z, d[3 * XT_STRIDE] = pre[u].w;
-                    }
+                if (idx < total4) {
+                    float *d = xs + (size_t)(idx % dim4) * 4 * XT_STRIDE + idx / dim4;
+                    d[0] = pre[u].x, d[XT_STRIDE] = pre[u].y, d[2 * XT_STRIDE] = pre[u].z, d[3 * XT_STRIDE] = pre[u].w;
                 }
             }
-            request(i0 + 16);
-            __syncwarp();
-            const bool valid = r < nb; // both lanes of a row agree on everything below
-            const unsigned long long row = valid ? base + list[i0 + r] : 0ull;
-            const float *xcol = xs + r;
-            int best = 0, ncand = 0;
-            uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            if (valid) {
-                const uint4 lo = __ldg(reinterpret_cast<const uint4 *>(P.cand + row * 8)), hi = __ldg(reinterpret_cast<const uint4 *>(P.cand + row * 8) + 1);
-                w[0] = lo.x, w[1] = lo.y, w[2] = lo.z, w[3] = lo.w, w[4] = hi.x, w[5] = hi.y, w[6] = hi.z, w[7] = hi.w;
-#pragma unroll
-                for (int e = 0; e < 8; ++e) ncand += __popc(w[e]);
-            }
-            // rows with many candidates (or marked "examine all"): the whole warp scans all centroids, as in resolve_kernel
-            const bool wide = valid && (ncand > 12 || ncand == 0);
-            unsigned wide_rows = __ballot_sync(0xffffffffu, wide) & 0xFFFFu;
-            while (wide_rows) {
-                const int wr = __ffs(wide_rows) - 1;
-                wide_rows &= wide_rows - 1;
-                const float *xr = xs + wr;
-                float bd = VQB_DENSE_INF, d0 = 0.0f;
-                int bi = 0x7fffffff;
-                for (int j = lane; j < k; j += 32) {
-                    const float *c = cpad + (size_t)j * cstride;
-                    float acc = 0.0f;
-#pragma unroll 8
-                    for (int i = 0; i < dim; ++i) {
-                        const float d = __fsub_rn(xr[i * XT_STRIDE], c[i]);
-                        acc = __fadd_rn(acc, __fmul_rn(d, d));
-                    }
-                    const float d = euclid ? __fsqrt_rn(acc) : acc;
-                    if (j == 0) d0 = d;
-                    if (d < bd) {
-                        bd = d;
-                        bi = j;
-                    }
-                }
-                d0 = __shfl_sync(0xffffffffu, d0, 0);
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    const float od = __shfl_xor_sync(0xffffffffu, bd, o);
-                    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                    if (od < bd || (od == bd && oi < bi)) {
-                        bd = od;
-                        bi = oi;
-                    }
-                }
-                int res = (bi == 0x7fffffff) ? 0 : bi;
-                if (!(d0 == d0)) res = 0;
-                if (bd == VQB_DENSE_INF) res = 0;
-                if (r == wr) best = res;
-            }
-            // the other rows: rounds of four candidates, two per lane of the pair
-            float bd = VQB_DENSE_INF;
-            int bi = -1;
-            int j = (valid && !wide) ? next_bit(w, 0) : 256;
-            while (__any_sync(0xffffffffu, j < k)) {
-                int js[4];
-                js[0] = j;
-#pragma unroll
-                for (int t = 1; t < 4; ++t) js[t] = (js[t - 1] < 256) ? next_bit(w, js[t - 1] + 1) : 256;
-                const int ja = half ? js[2] : js[0], jb = half ? js[3] : js[1];
-                float mine[2];
-                exact_dist2(xcol, cpad + (size_t)min(ja, k - 1) * cstride, cpad + (size_t)min(jb, k - 1) * cstride, dim, euclid, mine);
-                const float o0 = __shfl_xor_sync(0xffffffffu, mine[0], 16), o1 = __shfl_xor_sync(0xffffffffu, mine[1], 16);
-                const float d[4] = {half ? o0 : mine[0], half ? o1 : mine[1], half ? mine[0] : o0, half ? mine[1] : o1};
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    if (js[t] >= k) break;
-                    if (js[t] == 0) {
-                        bd = d[t];
-                        bi = 0;
-                    } else {
-                        argmin_update(d[t], js[t], bd, bi);
-                    }
-                }
-                j = (js[3] < 256) ? next_bit(w, js[3] + 1) : 256;
-            }
-            if (valid && half == 0) {
-                if (!wide) best = bi < 0 ? 0 : bi;
-                const CodeT nc = (CodeT)best;
-                if (codes[row] != nc) moved = true;
-                codes[row] = nc;
-            }
-            __syncwarp();
         }
+        request(g + gstep);
+        __syncwarp();
+        const bool valid = r < nb; // both lanes of a row agree on everything below
+        const unsigned long long row = valid ? P.list[g * 16 + r] : 0ull;
+        const float *xcol = xs + r;
+        int best = 0, ncand = 0;
+        uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (valid) {
+            const uint4 lo = __ldg(reinterpret_cast<const uint4 *>(P.cand + row * 8)), hi = __ldg(reinterpret_cast<const uint4 *>(P.cand + row * 8) + 1);
+            w[0] = lo.x, w[1] = lo.y, w[2] = lo.z, w[3] = lo.w, w[4] = hi.x, w[5] = hi.y, w[6] = hi.z, w[7] = hi.w;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ncand += __popc(w[e]);
+        }
+        // rows with many candidates (or marked "examine all"): the whole warp scans all centroids, as in resolve_kernel
+        const bool wide = valid && (ncand > 12 || ncand == 0);
+        unsigned wide_rows = __ballot_sync(0xffffffffu, wide) & 0xFFFFu;
+        while (wide_rows) {
+            const int wr = __ffs(wide_rows) - 1;
+            wide_rows &= wide_rows - 1;
+            const float *xr = xs + wr;
+            float bd = VQB_DENSE_INF, d0 = 0.0f;
+            int bi = 0x7fffffff;
+            for (int j = lane; j < k; j += 32) {
+                const float *c = cpad + (size_t)j * cstride;
+                float acc = 0.0f;
+#pragma unroll 8
+                for (int i = 0; i < dim; ++i) {
+                    const float d = __fsub_rn(xr[i * XT_STRIDE], c[i]);
+                    acc = __fadd_rn(acc, __fmul_rn(d, d));
+                }
+                const float d = euclid ? __fsqrt_rn(acc) : acc;
+                if (j == 0) d0 = d;
+                if (d < bd) {
+                    bd = d;
+                    bi = j;
+                }
+            }
+            d0 = __shfl_sync(0xffffffffu, d0, 0);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float od = __shfl_xor_sync(0xffffffffu, bd, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (od < bd || (od == bd && oi < bi)) {
+                    bd = od;
+                    bi = oi;
+                }
+            }
+            int res = (bi == 0x7fffffff) ? 0 : bi;
+            if (!(d0 == d0)) res = 0;
+            if (bd == VQB_DENSE_INF) res = 0;
+            if (r == wr) best = res;
+        }
+        // the other rows: rounds of four candidates, two per lane of the pair
+        float bd = VQB_DENSE_INF;
+        int bi = -1;
+        int j = (valid && !wide) ? next_bit(w, 0) : 256;
+        while (__any_sync(0xffffffffu, j < k)) {
+            int js[4];
+            js[0] = j;
+#pragma unroll
+            for (int t = 1; t < 4; ++t) js[t] = (js[t - 1] < 256) ? next_bit(w, js[t - 1] + 1) : 256;
+            const int ja = half ? js[2] : js[0], jb = half ? js[3] : js[1];
+            float mine[2];
+            exact_dist2(xcol, cpad + (size_t)min(ja, k - 1) * cstride, cpad + (size_t)min(jb, k - 1) * cstride, dim, euclid, mine);
+            const float o0 = __shfl_xor_sync(0xffffffffu, mine[0], 16), o1 = __shfl_xor_sync(0xffffffffu, mine[1], 16);
+            const float d[4] = {half ? o0 : mine[0], half ? o1 : mine[1], half ? mine[0] : o0, half ? mine[1] : o1};
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                if (js[t] >= k) break;
+                if (js[t] == 0) {
+                    bd = d[t];
+                    bi = 0;
+                } else {
+                    argmin_update(d[t], js[t], bd, bi);
+                }
+            }
+            j = (js[3] < 256) ? next_bit(w, js[3] + 1) : 256;
+        }
+        if (valid && half == 0) {
+            if (!wide) best = bi < 0 ? 0 : bi;
+            const CodeT nc = (CodeT)best;
+            if (codes[row] != nc) moved = true;
+            codes[row] = nc;
+        }
+        __syncwarp();
     }
     if (__any_sync(0xffffffffu, moved) && lane == 0) atomicOr(P.changed, VQB_MOVED_BITS);
 }
@@ -484,11 +457,12 @@ template <int MODE, typename CodeT> void launch_t(CudaDevice &dev, const Resolve
 template <typename CodeT> void launch_train(CudaDevice &dev, const ResolveParams &p)
 {
     size_t smem = 0;
-    const int warps = resolve_warps(p, 256 * sizeof(uint16_t), &smem);
+    const int warps = resolve_warps(p, 0, &smem);
     auto kernel = resolve_train_kernel<CodeT>;
     VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const unsigned long long blocks = (p.n + 255) / 256;
-    const unsigned grid = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((blocks + warps - 1) / warps, (unsigned long long)dev.sm_count()));
+    // the number of listed rows is only known on the device: CTAs without a group leave at once
+    const unsigned long long groups = (p.n + 15) / 16;
+    const unsigned grid = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((groups + warps - 1) / warps, (unsigned long long)dev.sm_count()));
     KernelScope ks(dev, "resolve_train");
     kernel<<<grid, 32 * warps, smem, dev.stream()>>>(p);
     VQB_CUDA_CHECK(cudaGetLastError());
