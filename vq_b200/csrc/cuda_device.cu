@@ -450,8 +450,10 @@ void CudaDevice::assign_train(const Shape &sh, const float *x, const float *cent
         if (stats_on) {
             unsigned long long st3[3] = {0, 0, 0};
             download(st3, tc_stats_, sizeof st3);
-            std::fprintf(stderr, "[vqb] shortlist: rows %llu candidates %llu (%.2f per row) full scans %llu\n", st3[0], st3[1],
-                         st3[0] ? (double)st3[1] / (double)st3[0] : 0.0, st3[2]);
+            uint32_t listed = 0;
+            download(&listed, list_count_, sizeof listed);
+            std::fprintf(stderr, "[vqb] shortlist: rows %llu candidates %llu (%.2f per row) full scans %llu, %u rows left for the exact kernel\n", st3[0],
+                         st3[1], st3[0] ? (double)st3[1] / (double)st3[0] : 0.0, st3[2], listed);
         }
         ResolveParams r = {};
         r.x = x;
