@@ -7,6 +7,7 @@
 // __syncthreads.  The sweeps end when no pair rotated (|g_p . g_q| <= 1e-15 |g_p| |g_q| for all pairs) or after 60 sweeps;
 // singular values, U and the completion of a rank-deficient U are computed by the caller from the converged G.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 #include "cuda_device.hpp"
@@ -132,9 +133,18 @@ bool CudaDevice::svd_sweeps(double *gt, double *vt, size_t n)
 //        X_0 = A^T / sqrt(|A|_1 |A|_inf),      X_{k+1} = X_k (1.5 I - 0.5 X_k^T X_k)
 // drives every singular value of X (all in (0, 1] at the start) to 1 and leaves the singular vectors alone, so it converges to
 // that factor: linearly (x 1.5 per step) while a singular value is small, then quadratically.  All of it is 128 x 128 x 128 f64
-// products on the device: no download of A, no sweeps on one SM.  The residual max|X^T X - I| is kept on the device and read by the
-// host after every eighth step; within a batch, steps after convergence copy X through.  If it has not converged after 96 steps
-// (rank-deficient or extremely ill-conditioned A) the caller falls back to the Jacobi SVD, which also completes a null space.
+// products on the device: no download of A, no sweeps on one SM.
+//
+// polar_iterate_kernel runs the whole iteration in ONE cooperative launch (one CTA per 16 x 16 tile, all resident; its own
+// bounded barrier between the two products of a step; the residual max|X^T X - I| is looked at on the device after every
+// step).  While the singular values are spread it uses, instead of (1.5, 0.5), the odd cubic a x - b x^3 that maps the current
+// interval [l, 1] of singular values into the narrowest interval [l', 1] (l' is known in closed form, so every CTA follows the
+// same sequence); small singular values then grow by up to 2.6 instead of 1.5 per step.  The interval starts at l = 1e-4, a
+// guess: a smaller true value only means the last steps run with the plain coefficients.  One launch and about 16 steps
+// replace some 25 steps of three stream operations each and a host round trip every eighth step (1.23 -> see DESIGN.md).
+// The step-by-step kernels below remain for matrices whose tiles cannot all be resident.  If the iteration has not converged
+// after 96 steps (rank-deficient or extremely ill-conditioned A) the caller falls back to the Jacobi SVD, which also
+// completes a null space.
 // ------------------------------------------------------------------------------------------------
 namespace vqb {
 
@@ -227,6 +237,134 @@ __global__ void __launch_bounds__(POLAR_TILE *POLAR_TILE) polar_update_kernel(co
     y[(size_t)i * n + j] = 1.5 * x[(size_t)i * n + j] - 0.5 * acc;
 }
 
+// ---- the whole iteration in one cooperative launch ---------------------------------------------
+struct PolarWork {
+    double *x0, *x1, *b;             // n x n each
+    unsigned long long *resid;       // [max_steps + 1] bits of max |X^T X - I| per step, zero on entry
+    unsigned int *arrivals;          // grid barrier counter, zero on entry
+    int *status;                     // [0] 1 = converged, 0 = not, -1 = a barrier wait ran out; [1] steps taken
+};
+
+// All threads of all CTAs call this the same number of times; `round` counts the calls from 1.  Bounded: a CTA that does not
+// see the others arrive gives up, records -1 and every later call returns false at once.
+__device__ __forceinline__ bool polar_grid_barrier(const PolarWork &w, unsigned int round, unsigned int ctas, int *failed_sh)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(w.arrivals, 1u);
+        const unsigned int target = round * ctas;
+        unsigned int i = 0;
+        while ((int)(*reinterpret_cast<volatile unsigned int *>(w.arrivals) - target) < 0) {
+            if (++i > (1u << 26) || *reinterpret_cast<volatile int *>(w.status) < 0) {
+                *reinterpret_cast<volatile int *>(w.status) = -1;
+                *failed_sh = 1;
+                break;
+            }
+        }
+        __threadfence();
+    }
+    __syncthreads();
+    return *failed_sh == 0;
+}
+
+__global__ void __launch_bounds__(POLAR_TILE *POLAR_TILE) polar_iterate_kernel(const double *a, int n, PolarWork w, float *rot, int max_steps, double l0)
+{
+    __shared__ double sa[POLAR_TILE][POLAR_TILE + 1], sb[POLAR_TILE][POLAR_TILE + 1];
+    __shared__ double red[POLAR_TILE * POLAR_TILE];
+    __shared__ int failed_sh;
+    const int tx = threadIdx.x % POLAR_TILE, ty = threadIdx.x / POLAR_TILE;
+    const int i = blockIdx.y * POLAR_TILE + ty, j = blockIdx.x * POLAR_TILE + tx;
+    const unsigned int ctas = gridDim.x * gridDim.y;
+    unsigned int round = 0;
+    if (threadIdx.x == 0) failed_sh = 0;
+    // scale^2 = |a|_1 |a|_inf, computed by every CTA for itself (the same value everywhere)
+    double best_row = 0.0, best_col = 0.0;
+    for (int t = threadIdx.x; t < n; t += POLAR_TILE * POLAR_TILE) {
+        double r = 0.0, c = 0.0;
+        for (int u = 0; u < n; ++u) {
+            r += fabs(__ldcg(a + (size_t)t * n + u));
+            c += fabs(__ldcg(a + (size_t)u * n + t));
+        }
+        best_row = fmax(best_row, r);
+        best_col = fmax(best_col, c);
+    }
+    red[threadIdx.x] = best_row;
+    __syncthreads();
+    for (int o = POLAR_TILE * POLAR_TILE / 2; o > 0; o >>= 1) {
+        if ((int)threadIdx.x < o) red[threadIdx.x] = fmax(red[threadIdx.x], red[threadIdx.x + o]);
+        __syncthreads();
+    }
+    const double rmax = red[0];
+    __syncthreads();
+    red[threadIdx.x] = best_col;
+    __syncthreads();
+    for (int o = POLAR_TILE * POLAR_TILE / 2; o > 0; o >>= 1) {
+        if ((int)threadIdx.x < o) red[threadIdx.x] = fmax(red[threadIdx.x], red[threadIdx.x + o]);
+        __syncthreads();
+    }
+    const double f = sqrt(rmax * red[0]);
+    __syncthreads();
+    double *cur = w.x0, *nxt = w.x1;
+    cur[(size_t)i * n + j] = (f > 0.0 && f == f) ? __ldcg(a + (size_t)j * n + i) / f : 0.0; // X_0 = A^T / f
+    if (!polar_grid_barrier(w, ++round, ctas, &failed_sh)) return;
+    double l = l0, resid = 1.0;
+    int step = 0;
+    for (; step <= max_steps; ++step) {
+        // b = cur^T cur, tile (i-block, j-block), and the step's residual
+        double acc = 0.0;
+        for (int r0 = 0; r0 < n; r0 += POLAR_TILE) {
+            sa[ty][tx] = __ldcg(cur + (size_t)(r0 + ty) * n + blockIdx.y * POLAR_TILE + tx);
+            sb[ty][tx] = __ldcg(cur + (size_t)(r0 + ty) * n + blockIdx.x * POLAR_TILE + tx);
+            __syncthreads();
+#pragma unroll
+            for (int r = 0; r < POLAR_TILE; ++r) acc = fma(sa[r][ty], sb[r][tx], acc);
+            __syncthreads();
+        }
+        w.b[(size_t)i * n + j] = acc;
+        const double dev = fabs(acc - (i == j ? 1.0 : 0.0));
+        red[threadIdx.x] = dev == dev ? dev : 1e300;
+        __syncthreads();
+        for (int o = POLAR_TILE * POLAR_TILE / 2; o > 0; o >>= 1) {
+            if ((int)threadIdx.x < o) red[threadIdx.x] = fmax(red[threadIdx.x], red[threadIdx.x + o]);
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) atomicMax(w.resid + step, (unsigned long long)__double_as_longlong(red[0]));
+        if (!polar_grid_barrier(w, ++round, ctas, &failed_sh)) return;
+        resid = __longlong_as_double((long long)__ldcg(w.resid + step));
+        if (resid < POLAR_TOL || step == max_steps) break; // the same value in every CTA
+        // coefficients: the cubic that maps [l, 1] into the narrowest [l', 1]; (1.5, 0.5) once l has reached 1
+        double ca = 1.5, cb = 0.5;
+        if (l < 0.999) {
+            const double s = 1.0 + l + l * l, xs = sqrt(s / 3.0);
+            const double pa = 2.0 / ((2.0 / 3.0) * xs + 1.0 - 1.0 / s), pe = (2.0 * pa / 3.0) * xs - 1.0;
+            ca = pa / (1.0 + pe);
+            cb = pa / s / (1.0 + pe);
+            l = (1.0 - pe) / (1.0 + pe);
+        }
+        // nxt = ca cur - cb cur b, tile (i-block, j-block)
+        acc = 0.0;
+        for (int r0 = 0; r0 < n; r0 += POLAR_TILE) {
+            sa[ty][tx] = __ldcg(cur + (size_t)i * n + r0 + tx);
+            sb[ty][tx] = __ldcg(w.b + (size_t)(r0 + ty) * n + j);
+            __syncthreads();
+#pragma unroll
+            for (int r = 0; r < POLAR_TILE; ++r) acc = fma(sa[ty][r], sb[r][tx], acc);
+            __syncthreads();
+        }
+        nxt[(size_t)i * n + j] = ca * __ldcg(cur + (size_t)i * n + j) - cb * acc;
+        if (!polar_grid_barrier(w, ++round, ctas, &failed_sh)) return;
+        double *t = cur;
+        cur = nxt;
+        nxt = t;
+    }
+    rot[(size_t)i * n + j] = (float)__ldcg(cur + (size_t)i * n + j);
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
+        w.status[0] = resid < 1e-11 ? 1 : 0;
+        w.status[1] = step;
+    }
+}
+
 __global__ void polar_finish_kernel(const double *x, int count, float *rot)
 {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
@@ -239,12 +377,47 @@ bool CudaDevice::polar_rotation(const double *a_dev, size_t n, float *rot_dev)
 {
     if (n == 0 || n % POLAR_TILE != 0 || n > 512) return false;
     const size_t bytes = sizeof(double) * n * n;
+    const int max_steps = 96;
+    {
+        // one cooperative launch when every tile's CTA can be resident at once
+        int per_sm = 0, coop = 0, dev_id = 0;
+        cudaGetDevice(&dev_id);
+        cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev_id);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, polar_iterate_kernel, POLAR_TILE * POLAR_TILE, 0);
+        const size_t ctas = (n / POLAR_TILE) * (n / POLAR_TILE);
+        if (coop && (size_t)per_sm * (size_t)sm_count() >= ctas && std::getenv("VQB_POLAR_STEPWISE") == nullptr) {
+            const size_t extra = sizeof(unsigned long long) * (max_steps + 2) + 64;
+            unsigned char *blk = static_cast<unsigned char *>(alloc(3 * bytes + extra));
+            PolarWork w;
+            w.x0 = reinterpret_cast<double *>(blk);
+            w.x1 = w.x0 + n * n;
+            w.b = w.x1 + n * n;
+            w.resid = reinterpret_cast<unsigned long long *>(blk + 3 * bytes);
+            w.arrivals = reinterpret_cast<unsigned int *>(w.resid + max_steps + 2);
+            w.status = reinterpret_cast<int *>(w.arrivals + 2);
+            int status[2] = {0, 0};
+            {
+                KernelScope ks(*this, "polar_rotation");
+                VQB_CUDA_CHECK(cudaMemsetAsync(w.resid, 0, extra, stream_));
+                const dim3 grid((unsigned)(n / POLAR_TILE), (unsigned)(n / POLAR_TILE));
+                int n_i = (int)n, steps_i = max_steps;
+                double l0 = 1e-4;
+                void *args[] = {(void *)&a_dev, (void *)&n_i, (void *)&w, (void *)&rot_dev, (void *)&steps_i, (void *)&l0};
+                VQB_CUDA_CHECK(cudaLaunchCooperativeKernel((const void *)polar_iterate_kernel, grid, dim3(POLAR_TILE * POLAR_TILE), args, 0, stream_));
+                count_launch();
+            }
+            download(status, w.status, sizeof status);
+            release(blk);
+            if (status[0] < 0) throw Error(100, "polar rotation: a wait between the steps ran out");
+            return status[0] == 1;
+        }
+    }
     double *x0 = static_cast<double *>(alloc(bytes)), *x1 = static_cast<double *>(alloc(bytes)), *b = static_cast<double *>(alloc(bytes));
     double *fro2 = static_cast<double *>(alloc(sizeof(double)));
     unsigned long long *resid = static_cast<unsigned long long *>(alloc(sizeof(unsigned long long) * 2));
     const int count = (int)(n * n);
     const dim3 grid((unsigned)(n / POLAR_TILE), (unsigned)(n / POLAR_TILE));
-    const int max_steps = 96, batch = 8; // x 1.5 per step while a singular value is small: down to 1e-16 of the largest
+    const int batch = 8; // x 1.5 per step while a singular value is small: down to 1e-16 of the largest
     double *cur = x0, *nxt = x1;
     double r = 1.0;
     {
