@@ -41,6 +41,25 @@ def test_quantize_given_identical_parts_is_bit_exact_after_rotation(oracle):
     assert np.array_equal(out.view(np.uint16)[same], out_o[same])
 
 
+@pytest.mark.parametrize("name", ["SquaredEuclidean", "CosineDistance", "Manhattan", "Chebyshev", "Hamming"])
+def test_quantize_with_every_metric_given_identical_parts(oracle, name):
+    """src/opq.rs:246-261 compares with the quantizer's Distance.  A permutation matrix as rotation keeps the rotated rows
+    exact, so the codes must equal the oracle's bit for bit."""
+    from tests.util import METRICS
+    rng = np.random.default_rng(16)
+    dim, m, k = 24, 3, 13
+    rot = np.eye(dim, dtype=np.float32)[rng.permutation(dim)]
+    cb = rng.normal(size=(m, k, dim // m)).astype(np.float32)
+    x = rng.normal(size=(1200, dim)).astype(np.float32)
+    if name == "Hamming":
+        x, cb = np.round(x), np.round(cb)
+    oq = vq.OptimizedProductQuantizer.from_parts(rot, cb, getattr(vq.Distance, name))
+    out, codes = oq.quantize(x, return_codes=True)
+    out_o, codes_o = oracle.opq_quantize(rot, cb, x, METRICS[name])
+    assert np.array_equal(codes, codes_o)
+    assert np.array_equal(out.view(np.uint16), out_o)
+
+
 def test_one_outer_iteration_matches_the_oracle(oracle):
     """First outer iteration starts from the identity, so codebooks are bit-exact; the rotation agrees to 1e-4."""
     x = synth.correlated(4000, 16, 3)

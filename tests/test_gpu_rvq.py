@@ -46,6 +46,44 @@ def test_fit_and_quantize_bit_exact(oracle, n, dim, stages, k, name):
     assert np.array_equal(out.view(np.uint16), out_o)
 
 
+@pytest.mark.parametrize("name", sorted(METRICS))
+def test_encode_with_every_metric_given_identical_codebooks(oracle, name):
+    """src/rvq.rs:186-199 takes whatever Distance the quantizer was built with (src/distances.rs:115-172)."""
+    rng = np.random.default_rng(21)
+    cb = rng.normal(size=(3, 11, 24)).astype(np.float32)
+    cb[1, 4] = cb[1, 2]                      # duplicate centroid: the lower index wins
+    x = rng.normal(size=(900, 24)).astype(np.float32)
+    x[5] = 0.0
+    if name == "Hamming":
+        x, cb = np.round(x), np.round(cb)
+    rq = vq.ResidualQuantizer.from_codebooks(cb, 0.01, getattr(vq.Distance, name))
+    out, codes = rq.quantize(x, return_codes=True)
+    out_o, codes_o, _ = oracle.rvq_quantize(cb, 0.01, x, METRICS[name])
+    assert np.array_equal(codes, codes_o)
+    assert np.array_equal(out.view(np.uint16), out_o)
+
+
+@pytest.mark.parametrize("name", ["Chebyshev", "Hamming"])
+def test_fit_with_the_rarer_metrics(oracle, name):
+    """The residual update of a stage (src/rvq.rs:111-128) uses the quantizer's metric; the k-means itself is Euclidean."""
+    x = synth.gaussian_mixture(600, 12, 3, components=5)
+    if name == "Hamming":
+        x = np.round(x * 4.0).astype(np.float32)
+    cb_o, so, rq, sg = _fit_both(oracle, x, 3, 7, 4, 0.01, name)
+    assert np.array_equal(rq.codebooks, cb_o) and by_stream(so.draws) == by_stream(sg.draws)
+
+
+def test_minkowski_codes_within_near_ties(oracle):
+    rng = np.random.default_rng(22)
+    cb = rng.normal(size=(2, 9, 16)).astype(np.float32)
+    x = rng.normal(size=(500, 16)).astype(np.float32)
+    rq = vq.ResidualQuantizer.from_codebooks(cb, 0.01, vq.Distance.Minkowski(3.0))
+    _, codes = rq.quantize(x, return_codes=True)
+    _, codes_o, _ = oracle.rvq_quantize(cb, 0.01, x, ka.MINKOWSKI, 3.0)
+    # powf differs in the last place between libm and CUDA: a first-stage near-tie changes the later stages of that row too
+    assert int((codes != codes_o).any(axis=1).sum()) <= 5
+
+
 def test_training_stops_when_the_mean_residual_norm_drops_below_epsilon(oracle):
     """src/rvq.rs:131-148: with every row equal to one of k points the first stage leaves zero residuals, so only one
     codebook is produced although more stages were asked for."""
