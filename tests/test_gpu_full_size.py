@@ -119,3 +119,22 @@ def test_opq_1m_first_outer_iteration_and_final_error(oracle):
     err_g = oracle.mse_f16(oracle.rotate_rows(rot, x), out.view(np.uint16))
     err_o = oracle.mse_f16(oracle.rotate_rows(rot_o, x), out_o)
     assert abs(err_g - err_o) <= 0.01 * err_o, (err_g, err_o)
+
+
+def test_tsvq_1m_tree_equals_the_oracle(oracle):
+    """Depth-10 tree over all 1,000,000 x 128 uniform rows (benches/bench_tsvq.rs:11 uses depth 10): every node's centroid,
+    the tree's shape and the leaves of 100,000 rows equal the oracle's bit for bit.  Nodes of this size are where the node
+    means are sums of 1024-row chunks and the spreads are 1M-term serial sums."""
+    import torch
+    oracle.use_all_host_threads()
+    x = synth.uniform01(N, 128, 7)
+    c, l, r = oracle.tsvq_fit(x, 10)
+    t = vq.TSVQ(torch.from_numpy(x).cuda(), 10, vq.Distance.Euclidean)
+    cg, lg, rg = t.tree()
+    assert np.array_equal(lg, l) and np.array_equal(rg, r)
+    assert np.array_equal(cg, c)
+    rows = slice(400_000, 500_000)
+    out, leaf = t.quantize(x[rows], return_leaf=True)
+    out_o, leaf_o = oracle.tsvq_quantize(c, l, r, x[rows], ka.EUCLID)
+    assert np.array_equal(leaf, leaf_o)
+    assert np.array_equal(np.asarray(out).view(np.uint16), out_o)
