@@ -151,6 +151,18 @@ class Device {
     // src/vector.rs:297-314); the buffer comes in zero-filled.  ordered = ascending row order per cluster.
     virtual void accumulate(const Shape &sh, const float *x, const void *codes, const uint32_t *active,
                             bool ordered, const IterBuffers &buf) = 0;
+    // Optional short cut for all but the first iteration: `local` holds the sums and counts of THIS rank's rows under the
+    // assignment codes_prev; bring it up to date with `codes` by moving only the rows whose code changed (add to the new
+    // cluster, subtract from the old one; counts likewise).  After a few iterations a small part of the rows still moves,
+    // so this touches a fraction of what a full pass adds up.  The order of the additions is as unspecified as in the full
+    // pass (src/vector.rs:298-304 for the clusters this mode is used on).  Returns false when the device does not take the
+    // shape; the caller then clears `local` and accumulates all rows.
+    virtual bool accumulate_moved(const Shape &sh, const float *x, const void *codes_prev, const void *codes, const uint32_t *active,
+                                  const IterBuffers &local)
+    {
+        (void)sh, (void)x, (void)codes_prev, (void)codes, (void)active, (void)local;
+        return false;
+    }
     // centroids = sums / (counts as f32) where counts > 0 (src/vector.rs:315-316), active subspaces only; reports
     // the iteration's flags to the host (complete on return) and clears the buffer for the next iteration.
     // With `px` the buffer holds this rank's part only (u32 counts) and the kernel adds the parts of all ranks itself; it

@@ -795,6 +795,84 @@ __global__ void accum_wide_kernel(const float *x, unsigned long long n, unsigned
     }
 }
 
+// FAST, narrow sub-spaces, from the second iteration on: only the (row, sub-space) pairs whose code changed are touched --
+// their slice is added to the new cluster's sums and subtracted from the old one's, the counts move by one.  Same layout and
+// per-CTA shared-memory sums as accum_small_kernel; the flush adds the CTA's net changes to the running totals.
+template <typename CodeT>
+__global__ void accum_moved_kernel(const float *x, unsigned long long n, unsigned long long ld, int m, int k, int sd, int group,
+                                   const CodeT *codes_prev, const CodeT *codes, const uint32_t *active, float *sums, uint32_t *counts, int counts_f32)
+{
+    const bool vec4 = (sd % 4 == 0) && (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
+    extern __shared__ __align__(16) float smem[];
+    const int g0 = blockIdx.y * group;
+    const int gcount = min(group, m - g0);
+    float *ssum = smem;                                                        // [gcount][sd][k] net change of the sums
+    int *scnt = reinterpret_cast<int *>(smem + (size_t)group * sd * k);        // [gcount][k] net change of the counts
+    uint32_t *touched = reinterpret_cast<uint32_t *>(scnt + (size_t)group * k); // [gcount][k] a row joined or left
+    for (int t = threadIdx.x; t < gcount * sd * k; t += blockDim.x) ssum[t] = 0.0f;
+    for (int t = threadIdx.x; t < gcount * k; t += blockDim.x) scnt[t] = 0, touched[t] = 0u;
+    __syncthreads();
+    auto move_pair = [&](unsigned long long row, int sl, int was, int now) {
+        const float *xp = x + row * ld + (size_t)(g0 + sl) * sd;
+        float *add = ssum + (size_t)sl * sd * k + now, *sub = ssum + (size_t)sl * sd * k + was;
+        if (vec4) {
+            for (int d = 0; d < sd; d += 4) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(xp + d));
+                atomicAdd(add + (size_t)d * k, v.x), atomicAdd(sub + (size_t)d * k, -v.x);
+                atomicAdd(add + (size_t)(d + 1) * k, v.y), atomicAdd(sub + (size_t)(d + 1) * k, -v.y);
+                atomicAdd(add + (size_t)(d + 2) * k, v.z), atomicAdd(sub + (size_t)(d + 2) * k, -v.z);
+                atomicAdd(add + (size_t)(d + 3) * k, v.w), atomicAdd(sub + (size_t)(d + 3) * k, -v.w);
+            }
+        } else {
+            for (int d = 0; d < sd; ++d) {
+                const float v = xp[d];
+                atomicAdd(add + (size_t)d * k, v), atomicAdd(sub + (size_t)d * k, -v);
+            }
+        }
+        atomicAdd(scnt + sl * k + now, 1), atomicAdd(scnt + sl * k + was, -1);
+        touched[sl * k + now] = 1u, touched[sl * k + was] = 1u;
+    };
+    if (sizeof(CodeT) == 1 && gcount == 8 && m % 8 == 0 && g0 % 8 == 0 && (reinterpret_cast<uintptr_t>(codes) & 7u) == 0 &&
+        (reinterpret_cast<uintptr_t>(codes_prev) & 7u) == 0) {
+        // one thread per row: the eight codes of the CTA's sub-spaces are one 64-bit word, and most rows have not moved at all
+        uint32_t act_mask = 0;
+        for (int sl = 0; sl < 8; ++sl) act_mask |= (!active || active[g0 + sl] != 0) ? (1u << sl) : 0u;
+        for (unsigned long long row = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; row < n; row += (unsigned long long)gridDim.x * blockDim.x) {
+            const unsigned long long was8 = *reinterpret_cast<const unsigned long long *>(codes_prev + row * m + g0);
+            const unsigned long long now8 = *reinterpret_cast<const unsigned long long *>(codes + row * m + g0);
+            unsigned long long diff = was8 ^ now8;
+            while (diff) {
+                const int sl = (__ffsll((long long)diff) - 1) >> 3;
+                diff &= ~(0xFFull << (8 * sl));
+                if (act_mask >> sl & 1u) move_pair(row, sl, (int)((was8 >> (8 * sl)) & 0xFFu), (int)((now8 >> (8 * sl)) & 0xFFu));
+            }
+        }
+    } else {
+        const unsigned long long total = n * gcount;
+        for (unsigned long long pidx = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; pidx < total;
+             pidx += (unsigned long long)gridDim.x * blockDim.x) {
+            const unsigned long long row = pidx / gcount;
+            const int sl = (int)(pidx % gcount);
+            const int s = g0 + sl;
+            const int was = (int)codes_prev[row * m + s], now = (int)codes[row * m + s];
+            if (was == now || (active && active[s] == 0)) continue;
+            move_pair(row, sl, was, now);
+        }
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < gcount * k * sd; t += blockDim.x) {
+        const int sl = t / (k * sd), rem = t % (k * sd);
+        const int j = rem / sd, d = rem % sd;
+        if (touched[sl * k + j]) atomicAdd(sums + ((size_t)(g0 + sl) * k + j) * sd + d, ssum[((size_t)sl * sd + d) * k + j]);
+    }
+    for (int t = threadIdx.x; t < gcount * k; t += blockDim.x) {
+        const int dc = scnt[t];
+        if (dc == 0) continue;
+        if (counts_f32) atomicAdd(reinterpret_cast<float *>(counts) + (size_t)g0 * k + t, (float)dc);
+        else atomicAdd(counts + (size_t)g0 * k + t, (uint32_t)dc); // modulo 2^32: the total is the true count
+    }
+}
+
 // FAST, wide rows in whole 16-byte pieces: the warps of a CTA share out the CLUSTERS (warp w owns the clusters j with
 // j mod W == w), so the per-CTA sums need no atomics at all.  Every warp looks at the codes of a 256-row piece (one byte or
 // word per row), lists the rows of its own clusters, fetches those rows eight at a time (128-bit loads, the lanes along the
@@ -988,6 +1066,46 @@ static void accumulate_t(CudaDevice &dev, const Shape &sh, const float *x, const
     }
     VQB_CUDA_CHECK(cudaGetLastError());
     dev.count_launch();
+}
+
+template <typename CodeT>
+static bool accumulate_moved_t(CudaDevice &dev, const Shape &sh, const float *x, const CodeT *codes_prev, const CodeT *codes, const uint32_t *active,
+                               float *sums, uint32_t *counts, int counts_f32)
+{
+    const int m = (int)sh.m, k = (int)sh.k, sd = (int)sh.sd;
+    const size_t budget = dev.smem_limit() - 1024;
+    const size_t per_sub = (size_t)k * (sd + 2) * sizeof(float); // sums, count changes, touched flags
+    if (sd > 32 || per_sub > budget) return false;
+    const size_t half_budget = (budget - 2048) / 2;
+    int group = (int)std::min<size_t>(m, std::max<size_t>(1, (per_sub <= half_budget ? half_budget : budget) / per_sub));
+    group = (m + (m + group - 1) / group - 1) / ((m + group - 1) / group);
+    const size_t smem = (size_t)group * per_sub;
+    const int ctas_per_sm = (int)std::max<size_t>(1, std::min<size_t>(2, budget / (smem + 1024)));
+    auto kernel = accum_moved_kernel<CodeT>;
+    VQB_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int threads = 1024;
+    const unsigned long long pairs = (unsigned long long)sh.n_local * group;
+    const unsigned ny = (unsigned)((m + group - 1) / group);
+    const unsigned gx = (unsigned)std::min<unsigned long long>((pairs + threads - 1) / threads,
+                                                               std::max<unsigned long long>(1, (unsigned long long)dev.sm_count() * ctas_per_sm / ny));
+    KernelScope ks(dev, "accumulate_moved");
+    kernel<<<dim3(std::max(1u, gx), ny), threads, smem, dev.stream()>>>(x, sh.n_local, sh.ld, m, k, sd, group, codes_prev, codes, active, sums, counts,
+                                                                        counts_f32);
+    VQB_CUDA_CHECK(cudaGetLastError());
+    dev.count_launch();
+    return true;
+}
+
+bool CudaDevice::accumulate_moved(const Shape &sh, const float *x, const void *codes_prev, const void *codes, const uint32_t *active,
+                                  const IterBuffers &local)
+{
+    static const bool off = std::getenv("VQB_ACCUM_FULL") != nullptr; // A/B switch: add up all rows in every iteration
+    if (off || sh.n_local == 0) return !off;
+    const size_t cb = code_bytes(sh.k);
+    const int cf = local.counts_f32 ? 1 : 0;
+    if (cb == 1) return accumulate_moved_t<uint8_t>(*this, sh, x, (const uint8_t *)codes_prev, (const uint8_t *)codes, active, local.sums, local.counts, cf);
+    if (cb == 2) return accumulate_moved_t<uint16_t>(*this, sh, x, (const uint16_t *)codes_prev, (const uint16_t *)codes, active, local.sums, local.counts, cf);
+    return accumulate_moved_t<uint32_t>(*this, sh, x, (const uint32_t *)codes_prev, (const uint32_t *)codes, active, local.sums, local.counts, cf);
 }
 
 void CudaDevice::accumulate(const Shape &sh, const float *x, const void *codes, const uint32_t *active, bool ordered,

@@ -44,6 +44,8 @@ class CudaDevice : public Device {
                       const IterBuffers &buf) override;
     void accumulate(const Shape &sh, const float *x, const void *codes, const uint32_t *active, bool ordered,
                     const IterBuffers &buf) override;
+    bool accumulate_moved(const Shape &sh, const float *x, const void *codes_prev, const void *codes, const uint32_t *active,
+                          const IterBuffers &local) override;
     void update_centroids(const Shape &sh, const IterBuffers &buf, const uint32_t *active, float *centroids,
                           IterStatus &status, const PeerExchange *px = nullptr) override;
     void rvq_update(float *res, size_t n, size_t dim, const float *centroids, size_t k, int metric, double p,

@@ -142,6 +142,15 @@ void lbg_fit(Device &dev, Comm *comm, const Shape &sh, const float *x, size_t ma
     bool active_dirty = true;
     IterStatus status;
     const size_t wps = (k + 31) / 32;
+    // Unordered accumulation keeps this rank's sums and counts from one iteration to the next and, from the second
+    // iteration on, only moves the rows whose assignment changed (Device::accumulate_moved); the exchange buffer gets a copy.
+    bool incremental = !ordered;
+    const size_t sum_words = m * k * sd + m * k;
+    DevBuf codes_prev(dev, incremental ? sh.n_local * m * cb : 0), local_mem(dev, incremental ? sizeof(uint32_t) * sum_words : 0);
+    IterBuffers local;
+    lay_out(local, local_mem.as<uint32_t>());
+    local.moved = nullptr;
+    bool local_valid = false;
 
     for (size_t it = 0; it < max_iters; ++it) {
         bool any = false;
@@ -152,8 +161,20 @@ void lbg_fit(Device &dev, Comm *comm, const Shape &sh, const float *x, size_t ma
             active_dirty = false;
         }
         if (direct) buf = pair[it & 1];
+        const bool moved_only = incremental && local_valid;
+        if (moved_only) dev.copy(codes_prev.p, codes.p, sh.n_local * m * cb);
         dev.assign_train(sh, x, centroids, codes.p, act.as<uint32_t>(), buf);          // 59-80
-        dev.accumulate(sh, x, codes.p, act.as<uint32_t>(), ordered, buf);              // 83-92
+        if (incremental) {                                                             // 83-92
+            local.counts_f32 = buf.counts_f32;
+            if (moved_only && !dev.accumulate_moved(sh, x, codes_prev.p, codes.p, act.as<uint32_t>(), local)) incremental = false;
+            if (incremental && !moved_only) {
+                dev.zero(local_mem.p, sizeof(uint32_t) * sum_words);
+                dev.accumulate(sh, x, codes.p, act.as<uint32_t>(), false, local);
+                local_valid = true;
+            }
+            if (incremental) dev.copy(buf.sums, local.sums, sizeof(uint32_t) * sum_words); // the moved flags are already in buf
+        }
+        if (!incremental) dev.accumulate(sh, x, codes.p, act.as<uint32_t>(), ordered, buf);
         PeerExchange px;
         if (direct) {
             px = comm->peer_exchange((int)(it & 1));

@@ -144,11 +144,11 @@ class NcclComm : public Comm {
     // still be reading it.
     bool open_window(size_t words)
     {
-        // Measured on B200s (1M x 128 rows in total, 132 KiB per rank and iteration): with two ranks NCCL's all-reduce costs
-        // less than the kernel's own hand-shake (7.47 against 7.65 ms per fit + encode), with four the direct exchange wins
-        // (4.25 against 4.39 ms).  VQB_PEER_EXCHANGE=1 / 0 forces one or the other.
+        // Measured on B200s (1M x 128 rows in total, 132 KiB per rank and iteration): the direct exchange wins against one NCCL
+        // all-reduce per iteration with two ranks (6.92 against 7.03 ms per fit + encode) and with four (4.25 against 4.39 ms).
+        // VQB_PEER_EXCHANGE=0 selects NCCL.
         const char *env = std::getenv("VQB_PEER_EXCHANGE");
-        const bool wanted = env && env[0] ? env[0] != '0' : world_ >= 3;
+        const bool wanted = !(env && env[0] == '0');
         dev_.make_current();
         Window w;
         w.cap_words = (words + 63) / 64 * 64;
