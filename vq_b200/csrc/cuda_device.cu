@@ -959,6 +959,50 @@ __global__ void __launch_bounds__(32 * AO_WARPS) accum_owner_kernel(const float 
         if (scnt[t] != 0u) add_count(gcnt, (size_t)t, scnt[t], counts_f32);
 }
 
+// Wide rows, iterations after the first: a warp looks at 32 rows' old and new codes; for every row that moved, the lanes
+// fetch the row in 16-byte pieces and add it to the new cluster's running sums and subtract it from the old one's with
+// 128-bit atomics on global memory.  Few rows move, so neither per-CTA sums (whose clearing and flushing would dominate)
+// nor an ownership split are worth their fixed cost here.
+template <typename CodeT>
+__global__ void __launch_bounds__(256) accum_rows_moved_kernel(const float *__restrict__ x, unsigned long long n, unsigned long long ld, int m, int k, int sd,
+                                                               const CodeT *__restrict__ codes_prev, const CodeT *__restrict__ codes,
+                                                               const uint32_t *active, float *sums, uint32_t *counts, int counts_f32)
+{
+    const int s = blockIdx.y;
+    if (active && active[s] == 0) return;
+    const int lane = threadIdx.x & 31;
+    const unsigned long long warps = (unsigned long long)gridDim.x * (blockDim.x >> 5);
+    float *gsum = sums + (size_t)s * k * sd;
+    uint32_t *gcnt = counts + (size_t)s * k;
+    const float *xs = x + (size_t)s * sd;
+    for (unsigned long long r0 = (blockIdx.x * (unsigned long long)(blockDim.x >> 5) + (threadIdx.x >> 5)) * 32; r0 < n; r0 += warps * 32) {
+        const unsigned long long row = r0 + lane;
+        uint32_t was = 0, now = 0;
+        if (row < n) was = (uint32_t)codes_prev[row * m + s], now = (uint32_t)codes[row * m + s];
+        unsigned moved = __ballot_sync(0xffffffffu, was != now);
+        while (moved) {
+            const int src = __ffs(moved) - 1;
+            moved &= moved - 1;
+            const uint32_t cw = __shfl_sync(0xffffffffu, was, src), cn = __shfl_sync(0xffffffffu, now, src);
+            const float *xr = xs + (r0 + src) * ld;
+            for (int d = 4 * lane; d < sd; d += 128) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(xr + d));
+                atomicAdd(reinterpret_cast<float4 *>(gsum + (size_t)cn * sd + d), v);
+                atomicAdd(reinterpret_cast<float4 *>(gsum + (size_t)cw * sd + d), make_float4(-v.x, -v.y, -v.z, -v.w));
+            }
+            if (lane == 0) {
+                if (counts_f32) {
+                    atomicAdd(reinterpret_cast<float *>(gcnt) + cn, 1.0f);
+                    atomicAdd(reinterpret_cast<float *>(gcnt) + cw, -1.0f);
+                } else {
+                    atomicAdd(gcnt + cn, 1u);
+                    atomicAdd(gcnt + cw, 0xFFFFFFFFu); // minus one modulo 2^32
+                }
+            }
+        }
+    }
+}
+
 // ORDERED: one thread per (cluster, dimension) walks all rows in ascending order and adds the members
 // of its cluster, which is exactly the serial branch of mean_vector (src/vector.rs:305-313).
 template <typename CodeT>
@@ -1075,6 +1119,16 @@ static bool accumulate_moved_t(CudaDevice &dev, const Shape &sh, const float *x,
     const int m = (int)sh.m, k = (int)sh.k, sd = (int)sh.sd;
     const size_t budget = dev.smem_limit() - 1024;
     const size_t per_sub = (size_t)k * (sd + 2) * sizeof(float); // sums, count changes, touched flags
+    if (sd >= 64 && sd % 4 == 0 && sh.ld % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(sums) & 15u) == 0) {
+        const unsigned long long groups = (sh.n_local + 31) / 32;
+        const unsigned gx = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((groups + 7) / 8, (unsigned long long)dev.sm_count() * 8 / m + 1));
+        KernelScope ks(dev, "accumulate_moved");
+        accum_rows_moved_kernel<CodeT><<<dim3(gx, m), 256, 0, dev.stream()>>>(x, sh.n_local, sh.ld, m, k, sd, codes_prev, codes, active, sums, counts,
+                                                                              counts_f32);
+        VQB_CUDA_CHECK(cudaGetLastError());
+        dev.count_launch();
+        return true;
+    }
     if (sd > 32 || per_sub > budget) return false;
     const size_t half_budget = (budget - 2048) / 2;
     int group = (int)std::min<size_t>(m, std::max<size_t>(1, (per_sub <= half_budget ? half_budget : budget) / per_sub));
