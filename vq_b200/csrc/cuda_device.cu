@@ -959,6 +959,44 @@ __global__ void __launch_bounds__(32 * AO_WARPS) accum_owner_kernel(const float 
         if (scnt[t] != 0u) add_count(gcnt, (size_t)t, scnt[t], counts_f32);
 }
 
+// 8-wide sub-spaces with one-byte codes (the product quantizer's benchmark shape), iterations after the first: one thread per
+// (row, eight sub-spaces) compares the eight old and new codes as one 64-bit word; a pair that moved adds its 32-byte slice to
+// the new cluster's running sums and subtracts it from the old one's with two 128-bit atomics each, straight on global memory.
+// No per-CTA sums to clear and flush, so the cost follows the number of moved pairs (and shrinks with the shard).
+__global__ void __launch_bounds__(256) accum_pairs_moved_kernel(const float *__restrict__ x, unsigned long long n, unsigned long long ld, int m, int k,
+                                                                const uint8_t *__restrict__ codes_prev, const uint8_t *__restrict__ codes,
+                                                                const uint32_t *active, float *sums, uint32_t *counts, int counts_f32)
+{
+    const int words = m >> 3; // 64-bit code words per row
+    const unsigned long long total = n * words;
+    for (unsigned long long t = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; t < total; t += (unsigned long long)gridDim.x * blockDim.x) {
+        const unsigned long long row = t / words;
+        const int g0 = (int)(t % words) * 8;
+        const unsigned long long was8 = *reinterpret_cast<const unsigned long long *>(codes_prev + row * m + g0);
+        const unsigned long long now8 = *reinterpret_cast<const unsigned long long *>(codes + row * m + g0);
+        unsigned long long diff = was8 ^ now8;
+        while (diff) {
+            const int sl = (__ffsll((long long)diff) - 1) >> 3;
+            diff &= ~(0xFFull << (8 * sl));
+            const int s = g0 + sl;
+            if (active && active[s] == 0) continue;
+            const uint32_t was = (uint32_t)((was8 >> (8 * sl)) & 0xFFu), now = (uint32_t)((now8 >> (8 * sl)) & 0xFFu);
+            const float4 *xp = reinterpret_cast<const float4 *>(x + row * ld + (size_t)s * 8);
+            const float4 a = __ldg(xp), b = __ldg(xp + 1);
+            float4 *add = reinterpret_cast<float4 *>(sums + ((size_t)s * k + now) * 8), *sub = reinterpret_cast<float4 *>(sums + ((size_t)s * k + was) * 8);
+            atomicAdd(add, a), atomicAdd(add + 1, b);
+            atomicAdd(sub, make_float4(-a.x, -a.y, -a.z, -a.w)), atomicAdd(sub + 1, make_float4(-b.x, -b.y, -b.z, -b.w));
+            if (counts_f32) {
+                atomicAdd(reinterpret_cast<float *>(counts) + (size_t)s * k + now, 1.0f);
+                atomicAdd(reinterpret_cast<float *>(counts) + (size_t)s * k + was, -1.0f);
+            } else {
+                atomicAdd(counts + (size_t)s * k + now, 1u);
+                atomicAdd(counts + (size_t)s * k + was, 0xFFFFFFFFu); // minus one modulo 2^32
+            }
+        }
+    }
+}
+
 // Wide rows, iterations after the first: a warp looks at 32 rows' old and new codes; for every row that moved, the lanes
 // fetch the row in 16-byte pieces and add it to the new cluster's running sums and subtract it from the old one's with
 // 128-bit atomics on global memory.  Few rows move, so neither per-CTA sums (whose clearing and flushing would dominate)
@@ -1125,6 +1163,20 @@ static bool accumulate_moved_t(CudaDevice &dev, const Shape &sh, const float *x,
         KernelScope ks(dev, "accumulate_moved");
         accum_rows_moved_kernel<CodeT><<<dim3(gx, m), 256, 0, dev.stream()>>>(x, sh.n_local, sh.ld, m, k, sd, codes_prev, codes, active, sums, counts,
                                                                               counts_f32);
+        VQB_CUDA_CHECK(cudaGetLastError());
+        dev.count_launch();
+        return true;
+    }
+    // measured on a B200: 0.006 ms + 0.148 ms per million rows for the direct kernel, 0.03 ms + 0.097 ms per million rows for the
+    // one with per-CTA sums below, so shards below about 450,000 rows take the direct one
+    if (sh.n_local <= 450000 && sd == 8 && sizeof(CodeT) == 1 && m % 8 == 0 && sh.ld % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
+        (reinterpret_cast<uintptr_t>(sums) & 15u) == 0 && (reinterpret_cast<uintptr_t>(codes) & 7u) == 0 && (reinterpret_cast<uintptr_t>(codes_prev) & 7u) == 0 &&
+        getenv("VQB_ACCUM_ATOMICS") == nullptr) {
+        const unsigned long long total = (unsigned long long)sh.n_local * (m / 8);
+        const unsigned gx = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((total + 255) / 256, (unsigned long long)dev.sm_count() * 32));
+        KernelScope ks(dev, "accumulate_moved");
+        accum_pairs_moved_kernel<<<gx, 256, 0, dev.stream()>>>(x, sh.n_local, sh.ld, m, k, reinterpret_cast<const uint8_t *>(codes_prev),
+                                                               reinterpret_cast<const uint8_t *>(codes), active, sums, counts, counts_f32);
         VQB_CUDA_CHECK(cudaGetLastError());
         dev.count_launch();
         return true;
