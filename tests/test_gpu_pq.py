@@ -277,3 +277,22 @@ def test_large_host_batch_goes_through_the_chunked_pipeline(oracle):
     assert np.array_equal(codes, codes_o) and np.array_equal(out.view(np.uint16), out_o)
     only_f16 = pq.quantize(x)
     assert np.array_equal(only_f16.view(np.uint16), out_o)
+
+
+@pytest.mark.parametrize("n,m,dim", [(70_000, 16, 128), (500_000, 16, 128), (90_000, 4, 32), (80_000, 2, 128)])
+def test_unordered_accumulation_moves_only_changed_rows_and_stays_exact_on_integers(oracle, n, m, dim):
+    """From the second iteration on the unordered accumulation adds and subtracts only the rows whose assignment changed
+    (three kernels: 64-bit code words with 128-bit atomics for small shards, per-CTA sums for large ones, whole rows for wide
+    sub-spaces).  Small integers make every f32 sum exact whatever the order, so the codebooks, the iteration counts and the
+    draws must equal the oracle's bit for bit; any slip in the bookkeeping (a row added twice, a count off by one) shows."""
+    oracle.use_all_host_threads()
+    k, iters = 64, 6
+    x = np.random.default_rng(n + m).integers(0, 16, (n, dim)).astype(np.float32)
+    so, sg = RecordingSeeder(13), RecordingSeeder(13)
+    init = so.init_pq(n, m, k)
+    sg.init_pq(n, m, k)
+    cb_o, it_o = oracle.pq_fit(x, m, k, iters, init, so.draw)
+    pq = vq.ProductQuantizer.fit(x, m, k, iters, vq.Distance.Euclidean, 13, init_idx=init, draw=sg.draw, accumulate=vq.ACCUM_FAST)
+    assert np.array_equal(pq.iterations, it_o)
+    assert np.array_equal(pq.codebooks, cb_o)
+    assert by_stream(so.draws) == by_stream(sg.draws)
