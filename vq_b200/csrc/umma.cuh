@@ -35,47 +35,6 @@ __device__ __forceinline__ void mbar_expect_tx(void *bar, uint32_t bytes)
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 
-// One poll of a phase; may park the thread for up to hint_ns before it answers.
-__device__ __forceinline__ bool mbar_try_wait(void *bar, uint32_t parity, uint32_t hint_ns)
-{
-    uint32_t done;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-                 : "=r"(done)
-                 : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
-                 : "memory");
-    return done != 0;
-}
-
-// One poll that never parks the thread.
-__device__ __forceinline__ bool mbar_test(void *bar, uint32_t parity)
-{
-    uint32_t done;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-                 : "=r"(done)
-                 : "r"(smem_u32(bar)), "r"(parity)
-                 : "memory");
-    return done != 0;
-}
-
-// Bounded wait on polls that never park the thread (test_wait): for hand-overs that are expected within a few hundred
-// cycles, where waking a parked thread would cost more than the wait itself.
-__device__ __forceinline__ bool mbar_spin_wait(void *bar, uint32_t parity, volatile int *abort_flag, int *err, int code)
-{
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t i = 0; i < 16u * UMMA_SPIN_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-                     : "=r"(done)
-                     : "r"(addr), "r"(parity)
-                     : "memory");
-        if (done) return true;
-        if ((i & 4095u) == 4095u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    atomicCAS(err, 0, code);
-    return false;
-}
-
 // Bounded wait: returns false (and raises the CTA's abort flag) if the phase does not complete in time.
 __device__ __forceinline__ bool mbar_wait(void *bar, uint32_t parity, volatile int *abort_flag, int *err, int code, uint32_t hint_ns = VQB_WAIT_HINT_NS)
 {
@@ -88,9 +47,6 @@ __device__ __forceinline__ bool mbar_wait(void *bar, uint32_t parity, volatile i
                      : "r"(addr), "r"(parity), "r"(hint_ns)
                      : "memory");
         if (done) return true;
-#ifdef VQB_WAIT_SLEEP_NS
-        __nanosleep(VQB_WAIT_SLEEP_NS);
-#endif
         if ((i & 1023u) == 1023u && *abort_flag) return false;
     }
     *abort_flag = 1;
