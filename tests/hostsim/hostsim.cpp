@@ -121,6 +121,32 @@ class HostDevice : public Device {
             }
         }
     }
+    // the running totals follow the rows whose code changed (the driver's short cut after the first iteration)
+    bool accumulate_moved(const Shape &sh, const float *x, const void *prev_v, const void *codes_v, const uint32_t *active, const IterBuffers &local) override
+    {
+        const uint32_t *prev = (const uint32_t *)prev_v, *codes = (const uint32_t *)codes_v;
+        ++moved_passes;
+        for (size_t s = 0; s < sh.m; ++s) {
+            if (active && !active[s]) continue;
+            for (size_t i = 0; i < sh.n_local; ++i) {
+                const size_t was = prev[i * sh.m + s], now = codes[i * sh.m + s];
+                if (was == now) continue;
+                const float *v = x + i * sh.ld + s * sh.sd;
+                float *add = local.sums + (s * sh.k + now) * sh.sd, *sub = local.sums + (s * sh.k + was) * sh.sd;
+                for (size_t c = 0; c < sh.sd; ++c) add[c] = add[c] + v[c], sub[c] = sub[c] - v[c];
+                if (local.counts_f32) {
+                    float a, b;
+                    std::memcpy(&a, &local.counts[s * sh.k + now], 4), std::memcpy(&b, &local.counts[s * sh.k + was], 4);
+                    a += 1.0f, b -= 1.0f;
+                    std::memcpy(&local.counts[s * sh.k + now], &a, 4), std::memcpy(&local.counts[s * sh.k + was], &b, 4);
+                } else {
+                    local.counts[s * sh.k + now]++, local.counts[s * sh.k + was]--;
+                }
+            }
+        }
+        return true;
+    }
+    size_t moved_passes = 0;
     void update_centroids(const Shape &sh, const IterBuffers &buf, const uint32_t *active, float *centroids, IterStatus &st, const PeerExchange * = nullptr) override
     {
         const size_t wps = (sh.k + 31) / 32;
@@ -210,11 +236,15 @@ thread_local std::string g_err;
 
 } // namespace
 
+static size_t g_moved_passes = 0;
+
 extern "C" {
 
 const char *hs_last_error(void) { return g_err.c_str(); }
 
 // vqb_pq_fit with a host Device; x = this rank's rows.  Euclidean metric (2 = error code for InvalidParameter etc.).
+size_t hs_moved_passes() { return g_moved_passes; }
+
 int hs_pq_fit(const float *x, size_t n_local, size_t dim, size_t m, size_t k, size_t max_iters, const uint64_t *init_idx,
               DrawFn draw, void *user, hs_allreduce_fn ar, void *ar_user, int rank, int world, float *codebooks, size_t *iterations)
 {
@@ -227,7 +257,10 @@ int hs_pq_fit(const float *x, size_t n_local, size_t dim, size_t m, size_t k, si
         sh.m = m;
         sh.sd = dim / m;
         sh.k = k;
-        lbg_fit(dev, world > 1 ? &comm : nullptr, sh, x, max_iters, init_idx, draw, user, 0, 1, codebooks, iterations);
+        // accumulation mode: ordered (1) unless the test asks for the unordered one (2), whose later iterations only move changed rows
+        const char *mode = std::getenv("HOSTSIM_ACCUM");
+        lbg_fit(dev, world > 1 ? &comm : nullptr, sh, x, max_iters, init_idx, draw, user, 0, mode ? std::atoi(mode) : 1, codebooks, iterations);
+        g_moved_passes = dev.moved_passes;
         return 0;
     } catch (const Error &e) {
         g_err = e.what();

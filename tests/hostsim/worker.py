@@ -76,7 +76,8 @@ def main():
         rc = lib.hs_pq_fit(C.c_void_p(xs.ctypes.data), C.c_size_t(xs.shape[0]), C.c_size_t(dim), C.c_size_t(m), C.c_size_t(k),
                            C.c_size_t(iters), C.c_void_p(init.ctypes.data), dcb, None, ar, None, rank, world,
                            C.c_void_p(cb.ctypes.data), C.c_void_p(its.ctypes.data))
-        result = {"codebooks": cb, "iterations": its}
+        lib.hs_moved_passes.restype = C.c_size_t
+        result = {"codebooks": cb, "iterations": its, "moved_passes": np.array(int(lib.hs_moved_passes()))}
     elif kind == "rvq":
         stages = int(case["stages"])
 

@@ -34,11 +34,12 @@ def _free_port():
     return port
 
 
-def run_ranks(tmp_path, world, **case):
+def run_ranks(tmp_path, world, extra_env=None, **case):
     path = os.path.join(tmp_path, "case.npz")
     np.savez(path, **case)
     prefix = os.path.join(tmp_path, "out")
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()), WORLD_SIZE=str(world), OMP_NUM_THREADS="1")
+    env.update(extra_env or {})
     procs = [subprocess.Popen([sys.executable, os.path.join(SIM, "worker.py"), path, prefix], env=dict(env, RANK=str(r)),
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT) for r in range(world)]
     for p in procs:
@@ -81,6 +82,26 @@ def test_pq_fit_sharded_equals_oracle_on_exact_sums(hostsim, oracle, tmp_path, w
         assert (f32_sizes == m * k * (dim // m) + m * k + m).all()
         assert (calls[:, 0] == 4).sum() == 1 and (calls[:, 0] == 3).sum() >= 1
         assert all(np.array_equal(res[0]["allreduce_calls"], r["allreduce_calls"]) for r in res[1:])
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_unordered_mode_keeps_running_sums_and_moves_only_changed_rows(hostsim, oracle, tmp_path, world):
+    """Unordered accumulation: after the first iteration every rank updates its running sums by the rows whose assignment
+    changed and copies them into the exchange buffer (driver.cpp::lbg_fit).  On integer rows the sums are exact, so the
+    sharded result must equal the oracle's bit for bit, re-seeded clusters included; the exchange stays one f32 all-reduce."""
+    n, dim, m, k, iters, seed = 1501, 8, 2, 24, 12, 7
+    x = _int_rows(n, dim, 4, distinct=70)
+    so = RecordingSeeder(seed)
+    cb_o, it_o = oracle.pq_fit(x, m, k, iters, so.init_pq(n, m, k), so.draw)
+    res = run_ranks(str(tmp_path), world, extra_env={"HOSTSIM_ACCUM": "2"}, kind="pq", x=x, m=m, k=k, iters=iters, seed=seed)
+    for r in res:
+        assert int(r["rc"]) == 0, str(r["error"])
+        assert np.array_equal(r["codebooks"], cb_o) and np.array_equal(r["iterations"], it_o)
+        assert by_stream(_draw_pairs(r)) == by_stream(so.draws)
+        assert int(r["moved_passes"]) >= 2          # the short cut ran (every iteration but the first)
+    if world > 1:
+        calls = res[0]["allreduce_calls"]
+        assert ((calls[calls[:, 0] == 0, 1]) == m * k * (dim // m) + m * k + m).all() and (calls[:, 0] == 2).sum() == 0
 
 
 def test_single_rank_host_loop_equals_oracle_on_float_rows(hostsim, oracle, tmp_path):
