@@ -230,6 +230,31 @@ def test_device_resident_tensors(oracle):
     assert torch.equal(out2, out)
 
 
+@pytest.mark.parametrize("mode", ["ordered", "fast"])
+@pytest.mark.parametrize("n,iters", [(150_000, 4), (70_001, 2), (150_000, 0)])
+def test_fit_from_a_host_buffer_follows_the_copy_and_equals_the_device_resident_fit(mode, n, iters):
+    """A large host buffer is copied in pieces while the first iteration already assigns (and, unordered, adds up) the
+    rows that have arrived, and the initial centroids are taken from the host copy.  Integer data make every sum exact,
+    so the result must equal the fit on device-resident rows bit for bit in both accumulation modes; with no iterations
+    the codebooks are the initial rows."""
+    import torch
+    m, k = 16, 64
+    x = np.random.default_rng(n).integers(0, 16, (n, 128)).astype(np.float32)
+    acc = vq.ACCUM_ORDERED if mode == "ordered" else vq.ACCUM_FAST
+    sh, sd = RecordingSeeder(5), RecordingSeeder(5)
+    init = sh.init_pq(n, m, k)
+    sd.init_pq(n, m, k)
+    pq_h = vq.ProductQuantizer.fit(x, m, k, iters, vq.Distance.Euclidean, 5, init_idx=init, draw=sh.draw, accumulate=acc)
+    pq_d = vq.ProductQuantizer.fit(torch.from_numpy(x).cuda(), m, k, iters, vq.Distance.Euclidean, 5, init_idx=init, draw=sd.draw,
+                                   accumulate=acc)
+    assert np.array_equal(pq_h.iterations, pq_d.iterations)
+    assert np.array_equal(pq_h.codebooks, pq_d.codebooks)
+    assert by_stream(sh.draws) == by_stream(sd.draws)
+    if iters == 0:
+        want = x[init.reshape(-1)].reshape(m, k, m, 8)[np.arange(m), :, np.arange(m), :]
+        assert np.array_equal(pq_h.codebooks.reshape(m, k, 8), want)
+
+
 def test_full_size_properties_1m(oracle):
     """README scale (1,000,000 x 128, m=16, k=256): size-independent properties at full size plus an oracle
     comparison on a row sample."""

@@ -115,6 +115,39 @@ struct In {
     template <typename T> const T *as() const { return static_cast<const T *>(d); }
 };
 
+// The rows of a fit.  A large host buffer is copied in pieces on a helper stream and announced to the device, so that
+// the first iteration can follow the copy (CudaDevice::begin_arrival); everything else behaves like In.
+struct RowsIn {
+    CudaDevice &dev;
+    const float *d = nullptr;
+    void *owned = nullptr;
+    RowsIn(CudaDevice &dv, const float *p, size_t n, size_t ld) : dev(dv)
+    {
+        const size_t bytes = sizeof(float) * n * ld;
+        if (bytes == 0 || dev.is_device_pointer(p)) {
+            d = p;
+            return;
+        }
+        owned = dev.alloc(bytes);
+        d = static_cast<const float *>(owned);
+        try {
+            if (!dev.begin_arrival(static_cast<float *>(owned), p, n, ld))
+                VQB_CUDA_CHECK(cudaMemcpyAsync(owned, p, bytes, cudaMemcpyHostToDevice, dev.stream()));
+        } catch (...) {
+            dev.end_arrival();
+            dev.release(owned);
+            throw;
+        }
+    }
+    ~RowsIn()
+    {
+        dev.end_arrival(); // no copy from the caller's buffer is left running
+        dev.release(owned);
+    }
+    RowsIn(const RowsIn &) = delete;
+    RowsIn &operator=(const RowsIn &) = delete;
+};
+
 // An output that is produced on the device and, when the caller's pointer is host memory, copied back.
 struct Out {
     CudaDevice &dev;
@@ -590,14 +623,14 @@ int vqb_pq_fit(vqb_ctx *ctx, const float *x, size_t n, size_t dim, size_t m, siz
         pq->iters.assign(m, 0);
         pq->codebooks = (float *)dev.alloc(sizeof(float) * m * k * pq->sd);
         try {
-            In ix(dev, x, sizeof(float) * n * dim);
+            RowsIn ix(dev, x, n, dim);
             Shape sh;
             sh.n_local = n;
             sh.ld = dim;
             sh.m = m;
             sh.sd = pq->sd;
             sh.k = k;
-            lbg_fit(dev, ctx->comm.get(), sh, ix.as<float>(), max_iters, init_idx, draw, user, 0, flags, pq->codebooks,
+            lbg_fit(dev, ctx->comm.get(), sh, ix.d, max_iters, init_idx, draw, user, 0, flags, pq->codebooks,
                     pq->iters.data());
             dev.synchronize();
         } catch (...) {

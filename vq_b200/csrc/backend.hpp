@@ -122,6 +122,20 @@ class Device {
         (void)sh;
         (void)x;
     }
+    // Rows that are still being copied in from the caller's host buffer when the fit starts.  arriving_pieces(x) is the
+    // number of pieces in which the rows at `x` arrive (0: they are all there).  await_piece(x, i) makes the device's queue
+    // wait for piece i and returns the row at which that piece ends; the first iteration of lbg_fit then works through the
+    // rows piece by piece behind the copies.  Pieces arrive in order.  Default: nothing is ever in flight.
+    virtual size_t arriving_pieces(const float *x)
+    {
+        (void)x;
+        return 0;
+    }
+    virtual size_t await_piece(const float *x, size_t piece)
+    {
+        (void)x, (void)piece;
+        return 0;
+    }
     // One-sided Jacobi sweeps on the device, until no pair of columns rotates.  gt / vt (host, n x n, f64) hold the
     // working matrix G = A V and V TRANSPOSED (row p = column p), and are updated in place.  Returns false when the
     // device does not take the shape; the caller then runs the sweeps on the host.  Default: host.

@@ -40,11 +40,15 @@ CudaDevice::CudaDevice(int device) : device_(device)
     VQB_CUDA_CHECK(cudaStreamCreateWithFlags(&own_stream_, cudaStreamNonBlocking));
     stream_ = own_stream_;
     ++device_allocs_;
-    if (cudaHostAlloc(reinterpret_cast<void **>(&stage_), STAGE_BYTES, cudaHostAllocDefault) != cudaSuccess) {
+    if (cudaHostAlloc(reinterpret_cast<void **>(&stage_), STAGE_BYTES, cudaHostAllocMapped) != cudaSuccess) {
         stage_ = nullptr; // pinned memory is an optimisation only
         cudaGetLastError();
     } else {
         VQB_CUDA_CHECK(cudaEventCreateWithFlags(&stage_event_, cudaEventDisableTiming));
+        if (cudaHostGetDevicePointer(reinterpret_cast<void **>(&stage_dev_), stage_, 0) != cudaSuccess) {
+            stage_dev_ = nullptr;
+            cudaGetLastError();
+        }
     }
     {
         const char *e = std::getenv("VQB_NO_TENSOR"); // VQB_NO_TENSOR=1: CUDA-core kernels only (A/B comparisons)
@@ -75,6 +79,8 @@ CudaDevice::~CudaDevice()
         for (int i = 0; i < 2; ++i)
             if (aux_[i]) cudaStreamDestroy(aux_[i]);
         if (stage_event_) cudaEventDestroy(stage_event_);
+        for (cudaEvent_t e : arrival_done_) cudaEventDestroy(e);
+        if (arrival_fence_) cudaEventDestroy(arrival_fence_);
         if (stage_) cudaFreeHost(stage_);
         cudaFree(rownorm_);
         cudaFree(hn_scratch_);
@@ -200,11 +206,102 @@ void CudaDevice::release(void *p)
     if (p) cudaFreeAsync(p, stream_);
 }
 
+// Reads mapped host memory over the link; used for small uploads while a large copy occupies the copy engine.
+__global__ void fetch_host_bytes_kernel(unsigned char *dst, const unsigned char *src, unsigned long long bytes)
+{
+    const unsigned long long t = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x;
+    const bool words = ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 3u) == 0;
+    if (words) {
+        if (4 * t + 4 <= bytes) reinterpret_cast<uint32_t *>(dst)[t] = reinterpret_cast<const uint32_t *>(src)[t];
+        else
+            for (unsigned long long b = 4 * t; b < bytes; ++b) dst[b] = src[b];
+    } else {
+        for (unsigned long long b = 4 * t; b < bytes && b < 4 * t + 4; ++b) dst[b] = src[b];
+    }
+}
+
 void CudaDevice::upload(void *dst, const void *src, size_t bytes)
 {
     if (!bytes) return;
+    if (arrival_.dev && arrival_.awaited < arrival_.pieces && stage_dev_ && bytes <= STAGE_BYTES) {
+        // Host-to-device copies run one after the other, so this one would wait for all the rows still arriving
+        // (begin_arrival); a kernel fetches the bytes from the pinned staging buffer instead.
+        std::memcpy(stage_, src, bytes);
+        const unsigned long long threads = (bytes + 3) / 4;
+        fetch_host_bytes_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream_>>>(static_cast<unsigned char *>(dst), stage_dev_, bytes);
+        VQB_CUDA_CHECK(cudaGetLastError());
+        VQB_CUDA_CHECK(cudaStreamSynchronize(stream_));
+        return;
+    }
     VQB_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, stream_));
     VQB_CUDA_CHECK(cudaStreamSynchronize(stream_));
+}
+
+// ------------------------------------------------------------------------------------------------
+// Rows that arrive while the first iteration already works on them.  A fit that is handed a host buffer copies it in
+// pieces on a helper stream; the first assignment pass waits piece by piece (lbg_fit), so that the copy, which takes about
+// as long as nine iterations at PCIe speed, hides one of them.
+// ------------------------------------------------------------------------------------------------
+bool CudaDevice::begin_arrival(float *dst, const float *host, size_t n, size_t ld)
+{
+    end_arrival();
+    static const bool whole = std::getenv("VQB_UPLOAD_WHOLE") != nullptr; // one copy ahead of everything, for comparison
+    if (whole || n == 0 || ld == 0) return false;
+    // at most 16 pieces, none below 8 MiB (a copy of that size still runs at the link's full rate), at least four of them
+    const size_t min_rows = std::max<size_t>(1024, ((size_t(8) << 20) / (ld * sizeof(float)) + 1023) / 1024 * 1024);
+    const size_t piece_rows = std::max(min_rows, ((n + 15) / 16 + 1023) / 1024 * 1024);
+    const size_t pieces = (n + piece_rows - 1) / piece_rows;
+    if (pieces < 4) return false;
+    make_current();
+    if (!arrival_fence_) VQB_CUDA_CHECK(cudaEventCreateWithFlags(&arrival_fence_, cudaEventDisableTiming));
+    while (arrival_done_.size() < pieces) {
+        cudaEvent_t e = nullptr;
+        VQB_CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        arrival_done_.push_back(e);
+    }
+    cudaStream_t up = aux_stream(0);
+    // `dst` may be memory that earlier work of the working stream has just let go of
+    VQB_CUDA_CHECK(cudaEventRecord(arrival_fence_, stream_));
+    VQB_CUDA_CHECK(cudaStreamWaitEvent(up, arrival_fence_, 0));
+    for (size_t i = 0; i < pieces; ++i) {
+        const size_t r0 = i * piece_rows, rows = std::min(piece_rows, n - r0);
+        VQB_CUDA_CHECK(cudaMemcpyAsync(dst + r0 * ld, host + r0 * ld, rows * ld * sizeof(float), cudaMemcpyHostToDevice, up));
+        VQB_CUDA_CHECK(cudaEventRecord(arrival_done_[i], up));
+    }
+    arrival_.dev = dst;
+    arrival_.host = host;
+    arrival_.n = n;
+    arrival_.ld = ld;
+    arrival_.piece_rows = piece_rows;
+    arrival_.pieces = pieces;
+    arrival_.awaited = 0;
+    return true;
+}
+
+void CudaDevice::end_arrival()
+{
+    // Nothing waited for the last pieces (an error, or a fit without iterations): the caller's buffer must not be read after
+    // the call returns, and the working stream must not run ahead of the copies, so the host waits for them here.
+    if (arrival_.dev && arrival_.awaited < arrival_.pieces) cudaStreamSynchronize(aux_[0]);
+    arrival_ = Arrival();
+}
+
+size_t CudaDevice::arriving_pieces(const float *x)
+{
+    if (!arrival_.dev || x != arrival_.dev || arrival_.awaited == arrival_.pieces) return 0;
+    if (arrival_.awaited == 0) return arrival_.pieces;
+    // somebody stopped half way through the pieces: wait for the rest in one go
+    VQB_CUDA_CHECK(cudaStreamWaitEvent(stream_, arrival_done_[arrival_.pieces - 1], 0));
+    arrival_.awaited = arrival_.pieces;
+    return 0;
+}
+
+size_t CudaDevice::await_piece(const float *x, size_t piece)
+{
+    if (!arrival_.dev || x != arrival_.dev || piece >= arrival_.pieces) throw Error(103, "no such piece of arriving rows");
+    VQB_CUDA_CHECK(cudaStreamWaitEvent(stream_, arrival_done_[piece], 0));
+    arrival_.awaited = std::max(arrival_.awaited, piece + 1);
+    return std::min(arrival_.n, (piece + 1) * arrival_.piece_rows);
 }
 
 // Small downloads sit on the critical path of every k-means iteration (counts and "changed" flags): they go through a
@@ -307,6 +404,7 @@ void CudaDevice::prepare_rows(const Shape &sh, const float *x)
     if (!tensor_enabled_ || sh.m != 1 || sh.ld != sh.sd || sh.n_local == 0) return;
     if (!dense_tc_applicable(sh.n_local, sh.sd, sh.k, M_SQ, x)) return;
     ensure_tc_buffers(sh.n_local);
+    if (x == arrival_.dev) end_arrival(); // the norms need all rows: the host waits for the copies
     dense_row_norms(*this, x, sh.n_local, sh.sd, rownorm_);
     prepared_x_ = x;
     prepared_n_ = sh.n_local;
@@ -414,10 +512,21 @@ void CudaDevice::patch_centroids(const Shape &sh, const float *x, uint64_t row_b
     upload(pd, patches, sizeof(RowPatch) * n_patches);
     const size_t total = n_patches * sh.sd;
     KernelScope ks(*this, "patch_centroids");
-    patch_fill_kernel<<<blocks_for(total, 256, 4096), 256, 0, stream_>>>(x, sh.n_local, sh.ld, (int)sh.sd, row_begin, pd,
-                                                                       n_patches, stage);
-    VQB_CUDA_CHECK(cudaGetLastError());
-    count_launch();
+    if (arrival_.dev && x == arrival_.dev && arrival_.awaited < arrival_.pieces) {
+        // the rows are still being copied in: take the wanted ones from the caller's host buffer
+        std::vector<uint32_t> bits(total, 0u);
+        for (size_t i = 0; i < n_patches; ++i) {
+            const RowPatch &pt = patches[i];
+            if (pt.row >= row_begin && pt.row - row_begin < sh.n_local)
+                std::memcpy(&bits[i * sh.sd], arrival_.host + (pt.row - row_begin) * sh.ld + (size_t)pt.subspace * sh.sd, sizeof(float) * sh.sd);
+        }
+        upload(stage, bits.data(), sizeof(uint32_t) * total);
+    } else {
+        patch_fill_kernel<<<blocks_for(total, 256, 4096), 256, 0, stream_>>>(x, sh.n_local, sh.ld, (int)sh.sd, row_begin, pd,
+                                                                           n_patches, stage);
+        VQB_CUDA_CHECK(cudaGetLastError());
+        count_launch();
+    }
     if (comm && comm->world() > 1) comm->allreduce_max_u32(stage, total);
     patch_scatter_kernel<<<blocks_for(total, 256, 4096), 256, 0, stream_>>>(stage, pd, n_patches, (int)sh.k, (int)sh.sd,
                                                                           centroids);

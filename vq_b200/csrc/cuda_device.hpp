@@ -34,6 +34,14 @@ class CudaDevice : public Device {
     size_t code_bytes(size_t k) const override { return k <= 256 ? 1 : (k <= 65536 ? 2 : 4); }
 
     void prepare_rows(const Shape &sh, const float *x) override;
+    size_t arriving_pieces(const float *x) override;
+    size_t await_piece(const float *x, size_t piece) override;
+    // Starts copying n rows of ld floats from the caller's host buffer to `dst` in pieces on a helper stream and remembers
+    // them as arriving (Device::arriving_pieces).  Returns false, having copied nothing, when the rows are too few for pieces
+    // to pay.  end_arrival waits (on the host) for whatever nobody has awaited yet; the owner of `dst` calls it before it
+    // lets go of the memory or returns to the caller.
+    bool begin_arrival(float *dst, const float *host, size_t n, size_t ld);
+    void end_arrival();
     bool svd_sweeps(double *gt, double *vt, size_t n) override;
     bool polar_rotation(const double *a_dev, size_t n, float *rot_dev) override;
     // Zero-filled map of at least `bytes` bytes for the product-quantizer tensor kernel; its users leave it zero-filled.
@@ -104,7 +112,7 @@ class CudaDevice : public Device {
     size_t smem_limit_ = 0;
     cudaStream_t own_stream_ = nullptr, stream_ = nullptr, aux_[2] = {nullptr, nullptr};
     static constexpr size_t STAGE_BYTES = 1u << 20; // pinned staging for small downloads
-    unsigned char *stage_ = nullptr;
+    unsigned char *stage_ = nullptr, *stage_dev_ = nullptr; // stage_dev_: the same bytes as kernels on this GPU address them
     cudaEvent_t stage_event_ = nullptr;
     std::atomic<uint64_t> launches_{0}, device_allocs_{0};
     // page of mapped pinned memory the centroid-update kernels report to (iter_status.cuh)
@@ -135,6 +143,13 @@ class CudaDevice : public Device {
                         uint32_t *out_codes, float *out_f32, bool cuda_cores_only);
 
     void check_tc_error();
+    // rows on their way from a host buffer (begin_arrival): piece i is complete when arrival_done_[i] has fired
+    struct Arrival {
+        const float *dev = nullptr, *host = nullptr;
+        size_t n = 0, ld = 0, piece_rows = 0, pieces = 0, awaited = 0;
+    } arrival_;
+    std::vector<cudaEvent_t> arrival_done_; // created once, re-used
+    cudaEvent_t arrival_fence_ = nullptr;
     bool timing_ = false;
     struct Span {
         const char *name;

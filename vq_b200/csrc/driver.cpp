@@ -162,19 +162,47 @@ void lbg_fit(Device &dev, Comm *comm, const Shape &sh, const float *x, size_t ma
         }
         if (direct) buf = pair[it & 1];
         const bool moved_only = incremental && local_valid;
-        if (moved_only) dev.copy(codes_prev.p, codes.p, sh.n_local * m * cb);
-        dev.assign_train(sh, x, centroids, codes.p, act.as<uint32_t>(), buf);          // 59-80
-        if (incremental) {                                                             // 83-92
-            local.counts_f32 = buf.counts_f32;
-            if (moved_only && !dev.accumulate_moved(sh, x, codes_prev.p, codes.p, act.as<uint32_t>(), local)) incremental = false;
-            if (incremental && !moved_only) {
+        const size_t pieces = it == 0 ? dev.arriving_pieces(x) : 0;
+        if (pieces) {
+            // The rows are still on their way from the host: assignment (59-80) and, where no order is asked for, the sums
+            // (83-92) follow the copies piece by piece, so that all but the last piece's work hides behind the transfer.
+            if (incremental) {
+                local.counts_f32 = buf.counts_f32;
                 dev.zero(local_mem.p, sizeof(uint32_t) * sum_words);
-                dev.accumulate(sh, x, codes.p, act.as<uint32_t>(), false, local);
-                local_valid = true;
             }
-            if (incremental) dev.copy(buf.sums, local.sums, sizeof(uint32_t) * sum_words); // the moved flags are already in buf
+            size_t r0 = 0;
+            for (size_t i = 0; i < pieces; ++i) {
+                const size_t r1 = dev.await_piece(x, i);
+                if (r1 <= r0 || r1 > sh.n_local) throw Error(VQB_ERR_BAD_ARGUMENT, "rows arrive out of order");
+                Shape part = sh;
+                part.n_local = r1 - r0;
+                const float *xp = x + r0 * sh.ld;
+                void *cp = static_cast<char *>(codes.p) + r0 * m * cb;
+                dev.assign_train(part, xp, centroids, cp, act.as<uint32_t>(), buf);
+                if (!ordered) dev.accumulate(part, xp, cp, act.as<uint32_t>(), false, incremental ? local : buf);
+                r0 = r1;
+            }
+            if (r0 != sh.n_local) throw Error(VQB_ERR_BAD_ARGUMENT, "not all rows arrived");
+            if (ordered) dev.accumulate(sh, x, codes.p, act.as<uint32_t>(), true, buf);
+            if (incremental) {
+                local_valid = true;
+                dev.copy(buf.sums, local.sums, sizeof(uint32_t) * sum_words);
+            }
+        } else {
+            if (moved_only) dev.copy(codes_prev.p, codes.p, sh.n_local * m * cb);
+            dev.assign_train(sh, x, centroids, codes.p, act.as<uint32_t>(), buf);          // 59-80
+            if (incremental) {                                                             // 83-92
+                local.counts_f32 = buf.counts_f32;
+                if (moved_only && !dev.accumulate_moved(sh, x, codes_prev.p, codes.p, act.as<uint32_t>(), local)) incremental = false;
+                if (incremental && !moved_only) {
+                    dev.zero(local_mem.p, sizeof(uint32_t) * sum_words);
+                    dev.accumulate(sh, x, codes.p, act.as<uint32_t>(), false, local);
+                    local_valid = true;
+                }
+                if (incremental) dev.copy(buf.sums, local.sums, sizeof(uint32_t) * sum_words); // the moved flags are already in buf
+            }
+            if (!incremental) dev.accumulate(sh, x, codes.p, act.as<uint32_t>(), ordered, buf);
         }
-        if (!incremental) dev.accumulate(sh, x, codes.p, act.as<uint32_t>(), ordered, buf);
         PeerExchange px;
         if (direct) {
             px = comm->peer_exchange((int)(it & 1));
