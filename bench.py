@@ -456,7 +456,8 @@ def run_secondary(args):
         oracle.use_all_host_threads()
         xp = torch.empty((min(rows, 2_000_000), DIM), dtype=torch.float32, pin_memory=True)
         xp.copy_(x[: xp.shape[0]])
-        e2e_fn = lambda: q.quantize(xp.numpy())  # noqa: E731
+        out_pinned = torch.empty(tuple(xp.shape), dtype=torch.uint8, pin_memory=True)
+        e2e_fn = lambda: q.quantize(xp.numpy(), out=out_pinned.numpy())  # noqa: E731  (page-locked buffers in and out)
         e2e_rows, h2d, d2h = xp.shape[0], xp.numel() * 4, xp.numel()
     else:
         import oracle
@@ -510,9 +511,11 @@ def run_secondary(args):
             extra["train_s"], extra["encode_s"] = t_fit, t_enc
             return out
 
-        def e2e_fn():  # host rows in (pinned), host f16 out, through the same public calls
+        out_pinned = torch.empty((rows, DIM), dtype=torch.float16, pin_memory=True)
+
+        def e2e_fn():  # page-locked host rows in, page-locked host f16 out, through the same public calls
             qz = fit(xp.numpy())
-            return qz.quantize(xp.numpy())
+            return qz.quantize(xp.numpy(), out=out_pinned.numpy())
         cpu_fit, cpu_enc = cpu_run(np.ascontiguousarray(xh[:sample_rows]))
         cpu = {"value": sample_rows / (cpu_fit + cpu_enc) / 1e6, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
                "sample": f"{sample_rows} of {rows} rows, full algorithm, scaled per vector",

@@ -255,6 +255,32 @@ def test_fit_from_a_host_buffer_follows_the_copy_and_equals_the_device_resident_
         assert np.array_equal(pq_h.codebooks.reshape(m, k, 8), want)
 
 
+def test_quantize_into_a_callers_buffer():
+    """`out=` takes the result where the caller wants it (page-locked host memory, or a CUDA tensor for device input): same
+    bits as a fresh result, and a buffer of the wrong shape, type or side is refused."""
+    import torch
+    x = synth.uniform01(3000, 32, 3)
+    pq = vq.ProductQuantizer.fit(x, 4, 16, 3, vq.Distance.Euclidean, 1)
+    want = pq.quantize(x)
+    buf = torch.empty((3000, 32), dtype=torch.float16, pin_memory=True)
+    got = pq.quantize(x, out=buf.numpy())
+    assert got is not None and np.array_equal(buf.numpy().view(np.uint16), want.view(np.uint16))
+    dev = torch.empty((3000, 32), dtype=torch.float16, device="cuda")
+    pq.quantize(torch.from_numpy(x).cuda(), out=dev)
+    assert np.array_equal(dev.cpu().numpy().view(np.uint16), want.view(np.uint16))
+    for bad in (np.empty((3000, 31), np.float16), np.empty((3000, 32), np.float32), dev):
+        with pytest.raises(ValueError):
+            pq.quantize(x, out=bad)
+    sq = vq.ScalarQuantizer.fit(0.0, 1.0, 256)
+    b8 = np.empty((3000, 32), np.uint8)
+    sq.quantize(x, out=b8)
+    assert np.array_equal(b8, sq.quantize(x))
+    t = vq.TSVQ(x, 3, vq.Distance.Euclidean)
+    bt = np.empty((3000, 32), np.float16)
+    t.quantize(x, out=bt)
+    assert np.array_equal(bt.view(np.uint16), t.quantize(x).view(np.uint16))
+
+
 def test_full_size_properties_1m(oracle):
     """README scale (1,000,000 x 128, m=16, k=256): size-independent properties at full size plus an oracle
     comparison on a row sample."""

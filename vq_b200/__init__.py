@@ -270,7 +270,25 @@ class _Arr:
                 raise ValueError("expected a vector or a matrix of row vectors")
         self.size = int(np.prod(self.shape)) if len(self.shape) else 1
 
-    def empty(self, shape, np_dtype):
+    def empty(self, shape, np_dtype, out=None):
+        """A fresh result of the input's kind, or the caller's `out`: a C-contiguous array of this shape and dtype that
+        lives where the input lives (numpy or CPU tensor for host input -- page-locked memory makes the copy back run at the
+        link's rate -- CUDA tensor for device input)."""
+        if out is not None:
+            want = tuple(int(v) for v in shape)
+            if _is_torch(out):
+                tdt = {np.float16: "float16", np.uint8: "uint8", np.uint32: "int32", np.float32: "float32"}[np_dtype]
+                on_device = bool(out.is_cuda)
+                ok = tuple(out.shape) == want and str(out.dtype) == "torch." + tdt and out.is_contiguous()
+                ptr = out.data_ptr()
+            else:
+                on_device = False
+                ok = isinstance(out, np.ndarray) and out.shape == want and out.dtype == np.dtype(np_dtype) and out.flags.c_contiguous \
+                    and out.flags.writeable
+                ptr = out.ctypes.data if ok else 0
+            if not ok or on_device != (self.torch is not None):
+                raise ValueError(f"out must be a contiguous {np.dtype(np_dtype).name} array of shape {want} on the input's side")
+            return out, ptr
         if self.torch is not None:
             tdt = {np.float16: self.torch.float16, np.uint8: self.torch.uint8, np.uint32: self.torch.int32,
                    np.float32: self.torch.float32}[np_dtype]
@@ -367,10 +385,11 @@ class ProductQuantizer:
         _lib.load().vqb_pq_iterations(self._h, out.ctypes.data)
         return out
 
-    def quantize(self, vector, return_codes: bool = False):
-        """ProductQuantizer::quantize (src/pq.rs:146-187): f16 reconstruction, one row per input vector."""
+    def quantize(self, vector, return_codes: bool = False, out=None):
+        """ProductQuantizer::quantize (src/pq.rs:146-187): f16 reconstruction, one row per input vector (written to `out`
+        when given: n x dim float16)."""
         x = _Arr(vector, self._ctx)
-        out, optr = x.empty((x.n, x.dim), np.float16)
+        out, optr = x.empty((x.n, x.dim), np.float16, out)
         codes, cptr = (x.empty((x.n, self.shape()[0]), np.uint32) if return_codes else (None, None))
         rc = _lib.load().vqb_pq_quantize(self._h, x.ptr, x.n, x.dim, optr, cptr)
         if rc:
@@ -443,10 +462,10 @@ class ResidualQuantizer:
                 _raise(rc, self._ctx.handle)
         return out
 
-    def quantize(self, vector, return_codes: bool = False):
-        """ResidualQuantizer::quantize (src/rvq.rs:171-215)."""
+    def quantize(self, vector, return_codes: bool = False, out=None):
+        """ResidualQuantizer::quantize (src/rvq.rs:171-215); `out` as in ProductQuantizer.quantize."""
         x = _Arr(vector, self._ctx)
-        out, optr = x.empty((x.n, x.dim), np.float16)
+        out, optr = x.empty((x.n, x.dim), np.float16, out)
         codes, cptr = (x.empty((x.n, self.shape()[0]), np.uint32) if return_codes else (None, None))
         rc = _lib.load().vqb_rvq_quantize(self._h, x.ptr, x.n, x.dim, optr, cptr)
         if rc:
@@ -542,13 +561,13 @@ class OptimizedProductQuantizer:
                 _raise(rc, self._ctx.handle)
         return out
 
-    def quantize(self, vector, return_codes: bool = False):
+    def quantize(self, vector, return_codes: bool = False, out=None):
         """OptimizedProductQuantizer::quantize (src/opq.rs:222-264).  Without codebooks (opq_iters == 0)
-        the result is empty, as in the reference."""
+        the result is empty, as in the reference.  `out` as in ProductQuantizer.quantize."""
         x = _Arr(vector, self._ctx)
         m = self.shape()[0]
         width = x.dim if m else 0
-        out, optr = x.empty((x.n, width), np.float16)
+        out, optr = x.empty((x.n, width), np.float16, out)
         codes, cptr = (x.empty((x.n, m), np.uint32) if return_codes else (None, None))
         rc = _lib.load().vqb_opq_quantize(self._h, x.ptr, x.n, x.dim, optr if width else None,
                                            cptr if (return_codes and m) else None)
@@ -582,11 +601,11 @@ class ScalarQuantizer:
             _raise(rc, None)
         return cls(float(np.float32(min)), float(np.float32(max)), int(levels), float(step.value), ctx)
 
-    def quantize(self, vector):
-        """ScalarQuantizer::quantize (src/sq.rs:89-106); any shape, element-wise."""
+    def quantize(self, vector, out=None):
+        """ScalarQuantizer::quantize (src/sq.rs:89-106); any shape, element-wise (into `out` when given: uint8, the input's shape)."""
         ctx = self._ctx or default_context()
         x = _Arr(vector, ctx, want_2d=False)
-        out, optr = x.empty(x.shape, np.uint8)
+        out, optr = x.empty(x.shape, np.uint8, out)
         rc = _lib.load().vqb_sq_quantize(ctx.handle, self.min, self.max, self.levels, self.step, x.ptr, x.size, optr)
         if rc:
             _raise(rc, ctx.handle)
@@ -605,11 +624,11 @@ class BinaryQuantizer:
             _raise(rc, None)
         return cls(float(np.float32(threshold)), int(low), int(high), ctx)
 
-    def quantize(self, vector):
-        """BinaryQuantizer::quantize (src/bq.rs:75-104); any shape, element-wise."""
+    def quantize(self, vector, out=None):
+        """BinaryQuantizer::quantize (src/bq.rs:75-104); any shape, element-wise (into `out` when given: uint8, the input's shape)."""
         ctx = self._ctx or default_context()
         x = _Arr(vector, ctx, want_2d=False)
-        out, optr = x.empty(x.shape, np.uint8)
+        out, optr = x.empty(x.shape, np.uint8, out)
         rc = _lib.load().vqb_bq_quantize(ctx.handle, self.threshold, self.low, self.high, x.ptr, x.size, optr)
         if rc:
             _raise(rc, ctx.handle)
@@ -644,10 +663,10 @@ class TSVQ:
             _raise(rc, self._ctx.handle)
         return cent, left, right
 
-    def quantize(self, vector, return_leaf: bool = False):
-        """TSVQ::quantize (src/tsvq.rs:231-249): one f16 row per input vector."""
+    def quantize(self, vector, return_leaf: bool = False, out=None):
+        """TSVQ::quantize (src/tsvq.rs:231-249): one f16 row per input vector; `out` as in ProductQuantizer.quantize."""
         x = _Arr(vector, self._ctx)
-        out, optr = x.empty((x.n, x.dim), np.float16)
+        out, optr = x.empty((x.n, x.dim), np.float16, out)
         leaf, lptr = (x.empty((x.n,), np.uint32) if return_leaf else (None, None))
         rc = _lib.load().vqb_tsvq_quantize(self._h, x.ptr, x.n, x.dim, optr, lptr)
         if rc:
