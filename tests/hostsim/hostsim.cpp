@@ -5,6 +5,7 @@
 // callbacks, per-subspace retirement) without GPUs, this file implements Device with plain loops over host memory
 // and Comm with callbacks that the Python test backs with torch.distributed (gloo).  It is built only by the test
 // suite, is never part of libvqb.so, and is not a fallback of the product.
+#include <algorithm>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -147,6 +148,19 @@ class HostDevice : public Device {
         return true;
     }
     size_t moved_passes = 0;
+    // rows that "arrive" in pieces (Device::arriving_pieces): nothing is in flight on the host, the first iteration simply has
+    // to walk the pieces and come out with the same result
+    const float *arriving_x = nullptr;
+    size_t arriving_n = 0, pieces = 0, awaited = 0, pieces_walked = 0;
+    size_t arriving_pieces(const float *x) override { return (pieces && x == arriving_x && awaited == 0) ? pieces : 0; }
+    size_t await_piece(const float *x, size_t i) override
+    {
+        if (x != arriving_x || i != awaited || i >= pieces) throw Error(2, "pieces awaited out of order");
+        awaited = i + 1;
+        ++pieces_walked;
+        const size_t per = (arriving_n + pieces - 1) / pieces;
+        return std::min(arriving_n, (i + 1) * per);
+    }
     void update_centroids(const Shape &sh, const IterBuffers &buf, const uint32_t *active, float *centroids, IterStatus &st, const PeerExchange * = nullptr) override
     {
         const size_t wps = (sh.k + 31) / 32;
@@ -236,7 +250,7 @@ thread_local std::string g_err;
 
 } // namespace
 
-static size_t g_moved_passes = 0;
+static size_t g_moved_passes = 0, g_pieces_walked = 0;
 
 extern "C" {
 
@@ -244,6 +258,7 @@ const char *hs_last_error(void) { return g_err.c_str(); }
 
 // vqb_pq_fit with a host Device; x = this rank's rows.  Euclidean metric (2 = error code for InvalidParameter etc.).
 size_t hs_moved_passes() { return g_moved_passes; }
+size_t hs_pieces_walked() { return g_pieces_walked; }
 
 int hs_pq_fit(const float *x, size_t n_local, size_t dim, size_t m, size_t k, size_t max_iters, const uint64_t *init_idx,
               DrawFn draw, void *user, hs_allreduce_fn ar, void *ar_user, int rank, int world, float *codebooks, size_t *iterations)
@@ -259,8 +274,14 @@ int hs_pq_fit(const float *x, size_t n_local, size_t dim, size_t m, size_t k, si
         sh.k = k;
         // accumulation mode: ordered (1) unless the test asks for the unordered one (2), whose later iterations only move changed rows
         const char *mode = std::getenv("HOSTSIM_ACCUM");
+        if (const char *pc = std::getenv("HOSTSIM_PIECES")) { // the rows count as still arriving, in that many pieces
+            dev.arriving_x = x;
+            dev.arriving_n = n_local;
+            dev.pieces = std::min<size_t>((size_t)std::atoi(pc), n_local);
+        }
         lbg_fit(dev, world > 1 ? &comm : nullptr, sh, x, max_iters, init_idx, draw, user, 0, mode ? std::atoi(mode) : 1, codebooks, iterations);
         g_moved_passes = dev.moved_passes;
+        g_pieces_walked = dev.pieces_walked;
         return 0;
     } catch (const Error &e) {
         g_err = e.what();

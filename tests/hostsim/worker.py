@@ -77,7 +77,9 @@ def main():
                            C.c_size_t(iters), C.c_void_p(init.ctypes.data), dcb, None, ar, None, rank, world,
                            C.c_void_p(cb.ctypes.data), C.c_void_p(its.ctypes.data))
         lib.hs_moved_passes.restype = C.c_size_t
-        result = {"codebooks": cb, "iterations": its, "moved_passes": np.array(int(lib.hs_moved_passes()))}
+        lib.hs_pieces_walked.restype = C.c_size_t
+        result = {"codebooks": cb, "iterations": its, "moved_passes": np.array(int(lib.hs_moved_passes())),
+                  "pieces_walked": np.array(int(lib.hs_pieces_walked()))}
     elif kind == "rvq":
         stages = int(case["stages"])
 

@@ -104,6 +104,25 @@ def test_unordered_mode_keeps_running_sums_and_moves_only_changed_rows(hostsim, 
         assert ((calls[calls[:, 0] == 0, 1]) == m * k * (dim // m) + m * k + m).all() and (calls[:, 0] == 2).sum() == 0
 
 
+@pytest.mark.parametrize("world,accum", [(1, "1"), (1, "2"), (2, "2")])
+def test_first_iteration_follows_rows_that_arrive_in_pieces(hostsim, oracle, tmp_path, world, accum):
+    """A fit handed a host buffer starts while the rows are still being copied in: the first iteration of lbg_fit assigns
+    (and, unordered, adds up) one piece at a time (Device::arriving_pieces / await_piece).  Here the pieces are only a way of
+    walking the rows (seven of them, the last one short), so the result must be the oracle's bit for bit in both
+    accumulation modes, sharded or not, and every piece must have been awaited exactly once."""
+    n, dim, m, k, iters, seed = 1501, 8, 2, 24, 6, 7
+    x = _int_rows(n, dim, 4, distinct=70)
+    so = RecordingSeeder(seed)
+    cb_o, it_o = oracle.pq_fit(x, m, k, iters, so.init_pq(n, m, k), so.draw)
+    res = run_ranks(str(tmp_path), world, extra_env={"HOSTSIM_ACCUM": accum, "HOSTSIM_PIECES": "7"}, kind="pq", x=x, m=m, k=k,
+                    iters=iters, seed=seed)
+    for r in res:
+        assert int(r["rc"]) == 0, str(r["error"])
+        assert np.array_equal(r["codebooks"], cb_o) and np.array_equal(r["iterations"], it_o)
+        assert by_stream(_draw_pairs(r)) == by_stream(so.draws)
+        assert int(r["pieces_walked"]) == 7
+
+
 def test_single_rank_host_loop_equals_oracle_on_float_rows(hostsim, oracle, tmp_path):
     """world = 1: the product's loop (ordered sums) against the oracle on ordinary float data, bit for bit."""
     from vq_b200 import synth
