@@ -1359,8 +1359,14 @@ __global__ void __launch_bounds__(256) update_centroids_kernel(float *sums, uint
             const size_t cj = (size_t)s * k + j;
             float cf;
             if (direct) {
+                // all peer loads are issued before the first is used (a warp stops at the first use of a pending load, so a
+                // load-then-add loop would pay one NVLink round trip per rank)
+                uint32_t pc[VQB_MAX_PEERS];
+#pragma unroll
+                for (int r = 0; r < VQB_MAX_PEERS; ++r) pc[r] = r < pv.world ? peer_ld(pv.words[r] + pv.off_counts + cj) : 0u;
                 uint32_t cnt = 0;
-                for (int r = 0; r < pv.world; ++r) cnt += peer_ld(pv.words[r] + pv.off_counts + cj);
+#pragma unroll
+                for (int r = 0; r < VQB_MAX_PEERS; ++r) cnt += pc[r];
                 cf = __uint2float_rn(cnt);
             } else {
                 const uint32_t cw = counts[cj];
@@ -1400,7 +1406,11 @@ __global__ void __launch_bounds__(256) update_centroids_kernel(float *sums, uint
         if (word == 0) {
             uint32_t mv = 0u;
             if (direct) {
-                for (int r = 0; r < pv.world; ++r) mv |= peer_ld(pv.words[r] + pv.off_moved + s);
+                uint32_t part[VQB_MAX_PEERS];
+#pragma unroll
+                for (int r = 0; r < VQB_MAX_PEERS; ++r) part[r] = r < pv.world ? peer_ld(pv.words[r] + pv.off_moved + s) : 0u;
+#pragma unroll
+                for (int r = 0; r < VQB_MAX_PEERS; ++r) mv |= part[r];
                 pv.stale[pv.off_moved + s] = 0u;
             } else {
                 mv = moved[s];
