@@ -123,15 +123,17 @@ class HostDevice : public Device {
         }
     }
     // the running totals follow the rows whose code changed (the driver's short cut after the first iteration)
-    bool accumulate_moved(const Shape &sh, const float *x, const void *prev_v, const void *codes_v, const uint32_t *active, const IterBuffers &local) override
+    bool accumulate_moved(const Shape &sh, const float *x, void *prev_v, const void *codes_v, const uint32_t *active, const IterBuffers &local) override
     {
-        const uint32_t *prev = (const uint32_t *)prev_v, *codes = (const uint32_t *)codes_v;
+        uint32_t *prev = (uint32_t *)prev_v;
+        const uint32_t *codes = (const uint32_t *)codes_v;
         ++moved_passes;
         for (size_t s = 0; s < sh.m; ++s) {
             if (active && !active[s]) continue;
             for (size_t i = 0; i < sh.n_local; ++i) {
                 const size_t was = prev[i * sh.m + s], now = codes[i * sh.m + s];
                 if (was == now) continue;
+                prev[i * sh.m + s] = (uint32_t)now; // the contract: equal to codes on return
                 const float *v = x + i * sh.ld + s * sh.sd;
                 float *add = local.sums + (s * sh.k + now) * sh.sd, *sub = local.sums + (s * sh.k + was) * sh.sd;
                 for (size_t c = 0; c < sh.sd; ++c) add[c] = add[c] + v[c], sub[c] = sub[c] - v[c];

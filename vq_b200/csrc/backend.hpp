@@ -169,9 +169,10 @@ class Device {
     // assignment codes_prev; bring it up to date with `codes` by moving only the rows whose code changed (add to the new
     // cluster, subtract from the old one; counts likewise).  After a few iterations a small part of the rows still moves,
     // so this touches a fraction of what a full pass adds up.  The order of the additions is as unspecified as in the full
-    // pass (src/vector.rs:298-304 for the clusters this mode is used on).  Returns false when the device does not take the
-    // shape; the caller then clears `local` and accumulates all rows.
-    virtual bool accumulate_moved(const Shape &sh, const float *x, const void *codes_prev, const void *codes, const uint32_t *active,
+    // pass (src/vector.rs:298-304 for the clusters this mode is used on).  On return codes_prev equals codes in every active
+    // subspace, so the next iteration needs no copy of the assignments.  Returns false, having changed nothing, when the device
+    // does not take the shape; the caller then clears `local` and accumulates all rows.
+    virtual bool accumulate_moved(const Shape &sh, const float *x, void *codes_prev, const void *codes, const uint32_t *active,
                                   const IterBuffers &local)
     {
         (void)sh, (void)x, (void)codes_prev, (void)codes, (void)active, (void)local;

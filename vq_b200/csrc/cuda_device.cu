@@ -909,7 +909,7 @@ __global__ void accum_wide_kernel(const float *x, unsigned long long n, unsigned
 // per-CTA shared-memory sums as accum_small_kernel; the flush adds the CTA's net changes to the running totals.
 template <typename CodeT>
 __global__ void accum_moved_kernel(const float *x, unsigned long long n, unsigned long long ld, int m, int k, int sd, int group,
-                                   const CodeT *codes_prev, const CodeT *codes, const uint32_t *active, float *sums, uint32_t *counts, int counts_f32)
+                                   CodeT *codes_prev, const CodeT *codes, const uint32_t *active, float *sums, uint32_t *counts, int counts_f32)
 {
     const bool vec4 = (sd % 4 == 0) && (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15u) == 0);
     extern __shared__ __align__(16) float smem[];
@@ -950,6 +950,7 @@ __global__ void accum_moved_kernel(const float *x, unsigned long long n, unsigne
             const unsigned long long was8 = *reinterpret_cast<const unsigned long long *>(codes_prev + row * m + g0);
             const unsigned long long now8 = *reinterpret_cast<const unsigned long long *>(codes + row * m + g0);
             unsigned long long diff = was8 ^ now8;
+            if (diff) *reinterpret_cast<unsigned long long *>(codes_prev + row * m + g0) = now8; // up to date for the next iteration
             while (diff) {
                 const int sl = (__ffsll((long long)diff) - 1) >> 3;
                 diff &= ~(0xFFull << (8 * sl));
@@ -965,6 +966,7 @@ __global__ void accum_moved_kernel(const float *x, unsigned long long n, unsigne
             const int s = g0 + sl;
             const int was = (int)codes_prev[row * m + s], now = (int)codes[row * m + s];
             if (was == now || (active && active[s] == 0)) continue;
+            codes_prev[row * m + s] = (CodeT)now;
             move_pair(row, sl, was, now);
         }
     }
@@ -1073,7 +1075,7 @@ __global__ void __launch_bounds__(32 * AO_WARPS) accum_owner_kernel(const float 
 // the new cluster's running sums and subtracts it from the old one's with two 128-bit atomics each, straight on global memory.
 // No per-CTA sums to clear and flush, so the cost follows the number of moved pairs (and shrinks with the shard).
 __global__ void __launch_bounds__(256) accum_pairs_moved_kernel(const float *__restrict__ x, unsigned long long n, unsigned long long ld, int m, int k,
-                                                                const uint8_t *__restrict__ codes_prev, const uint8_t *__restrict__ codes,
+                                                                uint8_t *codes_prev, const uint8_t *codes,
                                                                 const uint32_t *active, float *sums, uint32_t *counts, int counts_f32)
 {
     const int words = m >> 3; // 64-bit code words per row
@@ -1084,6 +1086,7 @@ __global__ void __launch_bounds__(256) accum_pairs_moved_kernel(const float *__r
         const unsigned long long was8 = *reinterpret_cast<const unsigned long long *>(codes_prev + row * m + g0);
         const unsigned long long now8 = *reinterpret_cast<const unsigned long long *>(codes + row * m + g0);
         unsigned long long diff = was8 ^ now8;
+        if (diff) *reinterpret_cast<unsigned long long *>(codes_prev + row * m + g0) = now8; // up to date for the next iteration
         while (diff) {
             const int sl = (__ffsll((long long)diff) - 1) >> 3;
             diff &= ~(0xFFull << (8 * sl));
@@ -1112,7 +1115,7 @@ __global__ void __launch_bounds__(256) accum_pairs_moved_kernel(const float *__r
 // nor an ownership split are worth their fixed cost here.
 template <typename CodeT>
 __global__ void __launch_bounds__(256) accum_rows_moved_kernel(const float *__restrict__ x, unsigned long long n, unsigned long long ld, int m, int k, int sd,
-                                                               const CodeT *__restrict__ codes_prev, const CodeT *__restrict__ codes,
+                                                               CodeT *codes_prev, const CodeT *codes,
                                                                const uint32_t *active, float *sums, uint32_t *counts, int counts_f32)
 {
     const int s = blockIdx.y;
@@ -1126,6 +1129,7 @@ __global__ void __launch_bounds__(256) accum_rows_moved_kernel(const float *__re
         const unsigned long long row = r0 + lane;
         uint32_t was = 0, now = 0;
         if (row < n) was = (uint32_t)codes_prev[row * m + s], now = (uint32_t)codes[row * m + s];
+        if (was != now) codes_prev[row * m + s] = (CodeT)now; // up to date for the next iteration
         unsigned moved = __ballot_sync(0xffffffffu, was != now);
         while (moved) {
             const int src = __ffs(moved) - 1;
@@ -1260,7 +1264,7 @@ static void accumulate_t(CudaDevice &dev, const Shape &sh, const float *x, const
 }
 
 template <typename CodeT>
-static bool accumulate_moved_t(CudaDevice &dev, const Shape &sh, const float *x, const CodeT *codes_prev, const CodeT *codes, const uint32_t *active,
+static bool accumulate_moved_t(CudaDevice &dev, const Shape &sh, const float *x, CodeT *codes_prev, const CodeT *codes, const uint32_t *active,
                                float *sums, uint32_t *counts, int counts_f32)
 {
     const int m = (int)sh.m, k = (int)sh.k, sd = (int)sh.sd;
@@ -1284,7 +1288,7 @@ static bool accumulate_moved_t(CudaDevice &dev, const Shape &sh, const float *x,
         const unsigned long long total = (unsigned long long)sh.n_local * (m / 8);
         const unsigned gx = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((total + 255) / 256, (unsigned long long)dev.sm_count() * 32));
         KernelScope ks(dev, "accumulate_moved");
-        accum_pairs_moved_kernel<<<gx, 256, 0, dev.stream()>>>(x, sh.n_local, sh.ld, m, k, reinterpret_cast<const uint8_t *>(codes_prev),
+        accum_pairs_moved_kernel<<<gx, 256, 0, dev.stream()>>>(x, sh.n_local, sh.ld, m, k, reinterpret_cast<uint8_t *>(codes_prev),
                                                                reinterpret_cast<const uint8_t *>(codes), active, sums, counts, counts_f32);
         VQB_CUDA_CHECK(cudaGetLastError());
         dev.count_launch();
@@ -1311,16 +1315,16 @@ static bool accumulate_moved_t(CudaDevice &dev, const Shape &sh, const float *x,
     return true;
 }
 
-bool CudaDevice::accumulate_moved(const Shape &sh, const float *x, const void *codes_prev, const void *codes, const uint32_t *active,
+bool CudaDevice::accumulate_moved(const Shape &sh, const float *x, void *codes_prev, const void *codes, const uint32_t *active,
                                   const IterBuffers &local)
 {
     static const bool off = std::getenv("VQB_ACCUM_FULL") != nullptr; // A/B switch: add up all rows in every iteration
     if (off || sh.n_local == 0) return !off;
     const size_t cb = code_bytes(sh.k);
     const int cf = local.counts_f32 ? 1 : 0;
-    if (cb == 1) return accumulate_moved_t<uint8_t>(*this, sh, x, (const uint8_t *)codes_prev, (const uint8_t *)codes, active, local.sums, local.counts, cf);
-    if (cb == 2) return accumulate_moved_t<uint16_t>(*this, sh, x, (const uint16_t *)codes_prev, (const uint16_t *)codes, active, local.sums, local.counts, cf);
-    return accumulate_moved_t<uint32_t>(*this, sh, x, (const uint32_t *)codes_prev, (const uint32_t *)codes, active, local.sums, local.counts, cf);
+    if (cb == 1) return accumulate_moved_t<uint8_t>(*this, sh, x, (uint8_t *)codes_prev, (const uint8_t *)codes, active, local.sums, local.counts, cf);
+    if (cb == 2) return accumulate_moved_t<uint16_t>(*this, sh, x, (uint16_t *)codes_prev, (const uint16_t *)codes, active, local.sums, local.counts, cf);
+    return accumulate_moved_t<uint32_t>(*this, sh, x, (uint32_t *)codes_prev, (const uint32_t *)codes, active, local.sums, local.counts, cf);
 }
 
 void CudaDevice::accumulate(const Shape &sh, const float *x, const void *codes, const uint32_t *active, bool ordered,

@@ -52,7 +52,7 @@ class CudaDevice : public Device {
                       const IterBuffers &buf) override;
     void accumulate(const Shape &sh, const float *x, const void *codes, const uint32_t *active, bool ordered,
                     const IterBuffers &buf) override;
-    bool accumulate_moved(const Shape &sh, const float *x, const void *codes_prev, const void *codes, const uint32_t *active,
+    bool accumulate_moved(const Shape &sh, const float *x, void *codes_prev, const void *codes, const uint32_t *active,
                           const IterBuffers &local) override;
     void update_centroids(const Shape &sh, const IterBuffers &buf, const uint32_t *active, float *centroids,
                           IterStatus &status, const PeerExchange *px = nullptr) override;

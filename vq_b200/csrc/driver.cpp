@@ -151,6 +151,7 @@ void lbg_fit(Device &dev, Comm *comm, const Shape &sh, const float *x, size_t ma
     lay_out(local, local_mem.as<uint32_t>());
     local.moved = nullptr;
     bool local_valid = false;
+    bool prev_current = false; // codes_prev already equals codes (accumulate_moved leaves it so)
 
     for (size_t it = 0; it < max_iters; ++it) {
         bool any = false;
@@ -189,11 +190,14 @@ void lbg_fit(Device &dev, Comm *comm, const Shape &sh, const float *x, size_t ma
                 dev.copy(buf.sums, local.sums, sizeof(uint32_t) * sum_words);
             }
         } else {
-            if (moved_only) dev.copy(codes_prev.p, codes.p, sh.n_local * m * cb);
+            if (moved_only && !prev_current) dev.copy(codes_prev.p, codes.p, sh.n_local * m * cb);
             dev.assign_train(sh, x, centroids, codes.p, act.as<uint32_t>(), buf);          // 59-80
             if (incremental) {                                                             // 83-92
                 local.counts_f32 = buf.counts_f32;
-                if (moved_only && !dev.accumulate_moved(sh, x, codes_prev.p, codes.p, act.as<uint32_t>(), local)) incremental = false;
+                if (moved_only) {
+                    prev_current = dev.accumulate_moved(sh, x, codes_prev.p, codes.p, act.as<uint32_t>(), local);
+                    if (!prev_current) incremental = false;
+                }
                 if (incremental && !moved_only) {
                     dev.zero(local_mem.p, sizeof(uint32_t) * sum_words);
                     dev.accumulate(sh, x, codes.p, act.as<uint32_t>(), false, local);
